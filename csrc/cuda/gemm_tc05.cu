@@ -1,0 +1,639 @@
+// gemm_tc05: bf16 / fp16 GEMM on the 5th-generation tensor cores (sm_100a).
+//
+//   D[b] = epilogue( op(A[b]) @ op(B[b]) )        fp32 accumulation in tensor memory
+//
+// Design
+//  * Persistent kernel, one CTA per SM, tiles of 128 x BN (BN = 256 or 128) x 64.
+//  * Warp-specialised: warp 0 issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle, no
+//    cluster multicast) into a multi-stage shared-memory ring guarded by mbarriers; warp 1
+//    issues tcgen05.mma (one elected thread) with the accumulator in TMEM and releases ring
+//    slots with tcgen05.commit; warps 2-5 drain the accumulator with tcgen05.ld and run the
+//    fused epilogue (bias, ReLU/GELU, residual add, optional pre-activation copy, dtype
+//    conversion) straight to global memory.  Two TMEM accumulators (2 x BN columns) let the
+//    epilogue of tile i overlap the main loop of tile i+1.
+//  * Both operands may be K-major or MN-major: transposed operands (the backward GEMMs) are
+//    described by shared-memory descriptors instead of being packed, and up to two batch
+//    dimensions with arbitrary strides go through rank-4 tensor maps, so attention heads are
+//    read in place from a packed QKV activation.
+//  * Every mbarrier wait is bounded by a clock budget; on expiry the kernel raises an error
+//    word and unwinds (TMEM is always released), so a logic error can never hang the GPU.
+//
+// A SIMT kernel handles float32 (exact, for parity tests) and operands that violate TMA
+// alignment rules.
+//
+// Replaces (reference project paths): src/backends/cuda/matmul_kernels.cu:51-134 (cuBLAS
+// routes), :138-400 (16x16 SIMT tiles), src/backends/cuda/fusion_kernels.cu:42-86.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "ob/cuda_common.cuh"
+#include "ob/ops.h"
+
+namespace ob {
+namespace cu {
+
+void strided_copy_cuda(const Tensor& src, Tensor& dst, cudaStream_t st);
+
+namespace {
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+constexpr long long kWaitBudgetCycles = 4000000000LL;  // about two seconds at 1.9 GHz
+
+// Bounded wait.  Returns false (and records `code`) when the budget runs out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > kWaitBudgetCycles) {
+      atomicExch(err, code);
+      return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_4d(void* smem, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor for a 128-byte-swizzled operand tile.
+//   K-major : rows of 64 elements (128 B), 8-row groups 1024 B apart (SBO); LBO unused (1).
+//   MN-major: rows of 64 MN elements per K index, 8-K-row groups 1024 B apart (SBO), next
+//             64-wide MN chunk `lbo_bytes` further (LBO).
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;  // descriptor version for sm_100
+  d |= 2ull << 61;  // SWIZZLE_128B
+  return d;
+}
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int kEpilogueWarps = 4;
+constexpr int kGemmThreads = 32 * (2 + kEpilogueWarps);
+
+enum : int { kErrProducer = 1, kErrMma = 2, kErrEpilogue = 3 };
+
+struct GemmParams {
+  int M, N, K;
+  int nb0, nb1;                 // batch extents (outer, inner)
+  int a_mn, b_mn;               // operand majors (0 = K-major, 1 = MN-major)
+  void* C; long long ldc, c_bs0, c_bs1;
+  const void* bias;             // [N] or null
+  const void* residual; long long ldr, r_bs0, r_bs1;
+  void* preact;                 // same layout as C, or null
+  int act;                      // 0 none, 1 relu, 2 gelu
+  int* err;
+};
+
+template <int BN>
+struct SmemLayout {
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // +1024 for manual alignment
+};
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+  if (act == 1) return v > 0.f ? v : 0.f;
+  if (act == 2) return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+  return v;
+}
+
+template <class T, int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+  using L = SmemLayout<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kStages * L::kStageBytes);
+  uint64_t* empty_bar = full_bar + L::kStages;
+  uint64_t* tmem_full = empty_bar + L::kStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+  const int tiles_per_batch = tiles_m * tiles_n;
+  const long long total_tiles = static_cast<long long>(tiles_per_batch) * p.nb0 * p.nb1;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < L::kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], kEpilogueWarps); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 2 * BN);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // Tile order: groups of 8 M-tiles sweep N together so concurrently resident CTAs share
+  // operand panels in L2.
+  auto decode_tile = [&](long long t, int& bidx, int& tm, int& tn) {
+    bidx = static_cast<int>(t / tiles_per_batch);
+    const int r = static_cast<int>(t - static_cast<long long>(bidx) * tiles_per_batch);
+    constexpr int G = 8;
+    const int group = r / (G * tiles_n);
+    const int first_m = group * G;
+    const int gsize = min(G, tiles_m - first_m);
+    const int in_group = r - group * G * tiles_n;
+    tm = first_m + in_group % gsize;
+    tn = in_group / gsize;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int bidx, tm, tn;
+        decode_tile(t, bidx, tm, tn);
+        const int b0 = bidx / p.nb1, b1 = bidx - b0 * p.nb1;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.err, kErrProducer)) { ok = false; break; }
+          mbar_expect_tx(&full_bar[stage], L::kStageBytes);
+          uint8_t* sa = smem + stage * L::kStageBytes;
+          uint8_t* sb = sa + L::kABytes;
+          const int k0 = kb * BK;
+          if (!p.a_mn) {
+            tma_load_4d(sa, &map_a, &full_bar[stage], k0, tm * BM, b1, b0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c) tma_load_4d(sa + c * (BK * 128), &map_a, &full_bar[stage], tm * BM + c * 64, k0, b1, b0);
+          }
+          if (!p.b_mn) {
+            tma_load_4d(sb, &map_b, &full_bar[stage], k0, tn * BN, b1, b0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_4d(sb + c * (BK * 128), &map_b, &full_bar[stage], tn * BN + c * 64, k0, b1, b0);
+          }
+          if (++stage == L::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // --------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      // Instruction descriptor: fp32 accumulate, A/B format, majors, N>>3, M>>4.
+      const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+      const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(p.a_mn) << 15) |
+                             (static_cast<uint32_t>(p.b_mn) << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                             (static_cast<uint32_t>(BM >> 4) << 24);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+        const int acc = it & 1;
+        if (!mbar_wait(&tmem_empty[acc], ((it >> 1) & 1) ^ 1, p.err, kErrMma)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, p.err, kErrMma)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
+          const uint32_t sb = sa + L::kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t da = p.a_mn ? make_desc(sa + k * 2048, BK * 128, 1024) : make_desc(sa + k * 32, 16, 1024);
+            const uint64_t db = p.b_mn ? make_desc(sb + k * 2048, BK * 128, 1024) : make_desc(sb + k * 32, 16, 1024);
+            umma_f16(tmem_d, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // frees the slot once these MMAs have read it
+          if (++stage == L::kStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&tmem_full[acc]);
+      }
+    }
+  } else {
+    // ----------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    bool ok = true;
+    int it = 0;
+    T* Cb = static_cast<T*>(p.C);
+    const T* Rb = static_cast<const T*>(p.residual);
+    T* Zb = static_cast<T*>(p.preact);
+    const T* bias = static_cast<const T*>(p.bias);
+    const bool vec_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0) &&
+                        (p.c_bs0 % 8 == 0) && (p.c_bs1 % 8 == 0) &&
+                        (!Rb || ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(Rb) & 15u) == 0) && (p.r_bs0 % 8 == 0) && (p.r_bs1 % 8 == 0))) &&
+                        (!Zb || ((reinterpret_cast<uintptr_t>(Zb) & 15u) == 0)) &&
+                        (!bias || ((reinterpret_cast<uintptr_t>(bias) & 15u) == 0));
+    for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+      int bidx, tm, tn;
+      decode_tile(t, bidx, tm, tn);
+      const int b0 = bidx / p.nb1, b1 = bidx - b0 * p.nb1;
+      const int acc = it & 1;
+      if (!mbar_wait(&tmem_full[acc], (it >> 1) & 1, p.err, kErrEpilogue)) { ok = false; break; }
+      tc_fence_after();
+      const int row = tm * BM + quarter * 32 + lane;
+      const long long c_off = b0 * p.c_bs0 + b1 * p.c_bs1 + static_cast<long long>(row) * p.ldc;
+      const long long r_off = b0 * p.r_bs0 + b1 * p.r_bs1 + static_cast<long long>(row) * p.ldr;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int ch = 0; ch < BN / 32; ++ch) {
+        const int col0 = tn * BN + ch * 32;
+        if (col0 >= p.N) break;  // uniform across the warp
+        float v[32];
+        tmem_ld32(taddr + ch * 32, v);
+        if (row < p.M) {
+          const bool full = vec_ok && (col0 + 32 <= p.N);
+          if (full) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (bias) {
+                Pack<T> pb = load_pack(bias + col0 + q * 8);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[q * 8 + j] += to_f(pb.v[j]);
+              }
+              if (Zb) {
+                Pack<T> pz;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) pz.v[j] = from_f<T>(v[q * 8 + j]);
+                store_pack(Zb + c_off + col0 + q * 8, pz);
+              }
+              Pack<T> po;
+              if (Rb) {
+                Pack<T> pr = load_pack(Rb + r_off + col0 + q * 8);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) po.v[j] = from_f<T>(apply_act(v[q * 8 + j], p.act) + to_f(pr.v[j]));
+              } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) po.v[j] = from_f<T>(apply_act(v[q * 8 + j], p.act));
+              }
+              store_pack(Cb + c_off + col0 + q * 8, po);
+            }
+          } else {
+            for (int j = 0; j < 32; ++j) {
+              const int col = col0 + j;
+              if (col >= p.N) break;
+              float x = v[j];
+              if (bias) x += to_f(bias[col]);
+              if (Zb) Zb[c_off + col] = from_f<T>(x);
+              x = apply_act(x, p.act);
+              if (Rb) x += to_f(Rb[r_off + col]);
+              Cb[c_off + col] = from_f<T>(x);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
+}
+
+// ------------------------------------------------------------- SIMT fallback
+// 64x64 output tile, 16x16 threads, 4x4 outputs per thread; arbitrary element strides.
+template <class T>
+__global__ void gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C, int M, int N, int K,
+                                 long long a_sm, long long a_sk, long long b_sk, long long b_sn, long long ldc,
+                                 int nb1, long long a_bs0, long long a_bs1, long long b_bs0, long long b_bs1,
+                                 long long c_bs0, long long c_bs1, const T* __restrict__ bias, const T* __restrict__ residual,
+                                 long long ldr, long long r_bs0, long long r_bs1, T* __restrict__ preact, int act) {
+  __shared__ float As[16][64 + 1];
+  __shared__ float Bs[16][64 + 1];
+  const int b0 = blockIdx.z / nb1, b1 = blockIdx.z % nb1;
+  A += b0 * a_bs0 + b1 * a_bs1;
+  B += b0 * b_bs0 + b1 * b_bs1;
+  const long long c_base = b0 * c_bs0 + b1 * c_bs1;
+  const long long r_base = b0 * r_bs0 + b1 * r_bs1;
+  const int tx = threadIdx.x, ty = threadIdx.y, tid = ty * 16 + tx;
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    for (int i = tid; i < 64 * 16; i += 256) {
+      const int kk = i % 16, mm = i / 16;
+      const int gm = m0 + mm, gk = k0 + kk;
+      As[kk][mm] = (gm < M && gk < K) ? to_f(A[gm * a_sm + gk * a_sk]) : 0.f;
+      const int nn = i % 64, kb = i / 64;
+      const int gn = n0 + nn, gk2 = k0 + kb;
+      Bs[kb][nn] = (gn < N && gk2 < K) ? to_f(B[gk2 * b_sk + gn * b_sn]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { a[i] = As[kk][ty * 4 + i]; b[i] = Bs[kk][tx * 4 + i]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gm = m0 + ty * 4 + i, gn = n0 + tx * 4 + j;
+      if (gm < M && gn < N) {
+        float x = acc[i][j];
+        if (bias) x += to_f(bias[gn]);
+        if (preact) preact[c_base + gm * ldc + gn] = from_f<T>(x);
+        x = apply_act(x, act);
+        if (residual) x += to_f(residual[r_base + gm * ldr + gn]);
+        C[c_base + gm * ldc + gn] = from_f<T>(x);
+      }
+    }
+}
+
+// ---------------------------------------------------------------- host side
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || p == nullptr)
+      throw std::runtime_error("cuTensorMapEncodeTiled is unavailable in this driver");
+    return reinterpret_cast<EncodeFn>(p);
+  }();
+  return fn;
+}
+
+// Logical operand of the GEMM: `mn` x `k` elements with element strides, plus batch strides.
+struct OperandView {
+  const void* ptr;
+  long long mn, k, s_mn, s_k, bs0, bs1;
+};
+
+bool tma_compatible(const OperandView& o, int nb0, int nb1) {
+  if ((reinterpret_cast<uintptr_t>(o.ptr) & 15u) != 0) return false;
+  const bool k_major = o.s_k == 1 || o.k == 1;
+  const bool mn_major = o.s_mn == 1 || o.mn == 1;
+  if (!k_major && !mn_major) return false;
+  const long long other = (o.s_k == 1 || (o.k == 1 && o.s_mn != 1)) ? o.s_mn : o.s_k;
+  if (other % 8 != 0 || other <= 0) return false;
+  if (nb1 > 1 && (o.bs1 % 8 != 0 || o.bs1 <= 0)) return false;
+  if (nb0 > 1 && (o.bs0 % 8 != 0 || o.bs0 <= 0)) return false;
+  return true;
+}
+
+// Builds a rank-4 tensor map {inner, rows, batch1, batch0}.  K-major: inner = K and the box
+// is 64 x box_rows; MN-major: inner = MN and the box is 64 (MN) x 64 (K rows).
+CUtensorMap make_map(const OperandView& o, bool mn_major, int box_rows, int nb0, int nb1, DType dt) {
+  CUtensorMap m;
+  const cuuint64_t inner = mn_major ? o.mn : o.k;
+  const cuuint64_t rows = mn_major ? o.k : o.mn;
+  const long long row_stride = mn_major ? o.s_k : o.s_mn;
+  cuuint64_t dims[4] = {inner, rows, static_cast<cuuint64_t>(nb1), static_cast<cuuint64_t>(nb0)};
+  // Strides of unit dims still have to be valid multiples of 16 bytes.
+  const long long rs = rows > 1 ? row_stride : static_cast<long long>((inner + 7) / 8 * 8);
+  const long long s1 = nb1 > 1 ? o.bs1 : rs * static_cast<long long>(rows);
+  const long long s0 = nb0 > 1 ? o.bs0 : s1 * nb1;
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(rs) * 2, static_cast<cuuint64_t>(s1) * 2, static_cast<cuuint64_t>(s0) * 2};
+  cuuint32_t box[4] = {64, static_cast<cuuint32_t>(mn_major ? 64 : box_rows), 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = encode_fn()(&m, dt == DType::BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                                 const_cast<void*>(o.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r)));
+  return m;
+}
+
+std::mutex g_err_mu;
+int* g_err_flag[64] = {};
+
+int* error_flag(int device) {
+  std::lock_guard<std::mutex> lock(g_err_mu);
+  if (!g_err_flag[device]) {
+    OB_CUDA(cudaMalloc(&g_err_flag[device], sizeof(int)));
+    OB_CUDA(cudaMemset(g_err_flag[device], 0, sizeof(int)));
+  }
+  return g_err_flag[device];
+}
+
+struct Epilogue {
+  Tensor bias, residual, preact;
+  int act = 0;
+};
+
+template <class T>
+void launch_simt(const OperandView& a, const OperandView& b, Tensor& C, int M, int N, int K, int nb0, int nb1,
+                 long long ldc, long long c_bs0, long long c_bs1, const Epilogue& ep, cudaStream_t st) {
+  dim3 grid((N + 63) / 64, (M + 63) / 64, nb0 * nb1);
+  const long long ldr = ep.residual.defined() ? ldc : 0;
+  gemm_simt_kernel<T><<<grid, dim3(16, 16), 0, st>>>(
+      static_cast<const T*>(a.ptr), static_cast<const T*>(b.ptr), C.data_as<T>(), M, N, K, a.s_mn, a.s_k, b.s_k, b.s_mn, ldc,
+      nb1, a.bs0, a.bs1, b.bs0, b.bs1, c_bs0, c_bs1, ep.bias.defined() ? ep.bias.data_as<T>() : nullptr,
+      ep.residual.defined() ? ep.residual.data_as<T>() : nullptr, ldr, c_bs0, c_bs1,
+      ep.preact.defined() ? ep.preact.data_as<T>() : nullptr, ep.act);
+  check_launch("gemm (SIMT)");
+}
+
+template <class T, int BN>
+void launch_tc05(const OperandView& a, const OperandView& b, bool a_mn, bool b_mn, Tensor& C, int M, int N, int K,
+                 int nb0, int nb1, long long ldc, long long c_bs0, long long c_bs1, const Epilogue& ep, cudaStream_t st) {
+  using L = SmemLayout<BN>;
+  const DType dt = C.dtype();
+  const CUtensorMap ma = make_map(a, a_mn, BM, nb0, nb1, dt);
+  const CUtensorMap mb = make_map(b, b_mn, BN, nb0, nb1, dt);
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.nb0 = nb0; p.nb1 = nb1; p.a_mn = a_mn; p.b_mn = b_mn;
+  p.C = C.data(); p.ldc = ldc; p.c_bs0 = c_bs0; p.c_bs1 = c_bs1;
+  p.bias = ep.bias.defined() ? ep.bias.data() : nullptr;
+  p.residual = ep.residual.defined() ? ep.residual.data() : nullptr;
+  p.ldr = ldc; p.r_bs0 = c_bs0; p.r_bs1 = c_bs1;
+  p.preact = ep.preact.defined() ? ep.preact.data() : nullptr;
+  p.act = ep.act;
+  p.err = error_flag(C.device().index);
+  static std::once_flag once;
+  std::call_once(once, [] {
+    OB_CUDA(cudaFuncSetAttribute(gemm_tc05_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+  });
+  const long long tiles = static_cast<long long>((M + BM - 1) / BM) * ((N + BN - 1) / BN) * nb0 * nb1;
+  const int grid = static_cast<int>(std::min<long long>(tiles, sm_count_for(C)));
+  gemm_tc05_kernel<T, BN><<<grid, kGemmThreads, L::kTotal, st>>>(ma, mb, p);
+  check_launch("gemm_tc05");
+}
+
+// Shared driver for Matmul and Linear.  `A`/`B` are the stored tensors, flags select op().
+void gemm_dispatch(const Tensor& A_in, bool ta, const Tensor& B_in, bool tb, Tensor& C, const Epilogue& ep, cudaStream_t st) {
+  Tensor A = A_in, B = B_in;
+  const int nd = A.ndim();
+  const int nbd = nd - 2;
+  const int nb0 = nbd == 2 ? static_cast<int>(A.shape()[0]) : 1;
+  const int nb1 = nbd >= 1 ? static_cast<int>(A.shape()[nbd - 1]) : 1;
+  auto view_of = [&](const Tensor& t, bool trans, bool is_a) {
+    OperandView o{};
+    o.ptr = t.data();
+    const long long rs = t.strides()[nbd], cs = t.strides()[nbd + 1];
+    const long long r = t.shape()[nbd], c = t.shape()[nbd + 1];
+    // op(t) logical: A' is [M, K]; B' is [K, N].
+    const long long lr = trans ? c : r, lc = trans ? r : c, lrs = trans ? cs : rs, lcs = trans ? rs : cs;
+    if (is_a) { o.mn = lr; o.k = lc; o.s_mn = lrs; o.s_k = lcs; }
+    else { o.k = lr; o.mn = lc; o.s_k = lrs; o.s_mn = lcs; }
+    o.bs0 = nbd == 2 ? t.strides()[0] : 0;
+    o.bs1 = nbd >= 1 ? t.strides()[nbd - 1] : 0;
+    return o;
+  };
+  OperandView a = view_of(A, ta, true), b = view_of(B, tb, false);
+  const int M = static_cast<int>(a.mn), N = static_cast<int>(b.mn), K = static_cast<int>(a.k);
+  const long long ldc = C.strides()[nbd];
+  const long long c_bs0 = nbd == 2 ? C.strides()[0] : 0, c_bs1 = nbd >= 1 ? C.strides()[nbd - 1] : 0;
+  const DType dt = C.dtype();
+
+  if (dt == DType::F32) {
+    launch_simt<float>(a, b, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);
+    return;
+  }
+  // Operands that TMA cannot describe are packed once (the packed copy is K-major).
+  const bool tiny = static_cast<long long>(M) * N * K < (1LL << 18);
+  bool use_tc = !tiny && Runtime::instance().cuda(C.device().index).supports_tcgen05();
+  if (use_tc) {
+    if (!tma_compatible(a, nb0, nb1)) {
+      A = Tensor::empty(A.shape(), A.dtype(), A.device());
+      strided_copy_cuda(A_in, A, st);
+      a = view_of(A, ta, true);
+    }
+    if (!tma_compatible(b, nb0, nb1)) {
+      B = Tensor::empty(B.shape(), B.dtype(), B.device());
+      strided_copy_cuda(B_in, B, st);
+      b = view_of(B, tb, false);
+    }
+    use_tc = tma_compatible(a, nb0, nb1) && tma_compatible(b, nb0, nb1);
+  }
+  if (!use_tc) {
+    if (dt == DType::BF16) launch_simt<__nv_bfloat16>(a, b, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);
+    else launch_simt<__half>(a, b, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);
+    return;
+  }
+  const bool a_mn = !(a.s_k == 1 || (a.k == 1 && a.s_mn != 1));
+  const bool b_mn = !(b.s_k == 1 || (b.k == 1 && b.s_mn != 1));
+  const bool wide = N > 128;
+  if (dt == DType::BF16) {
+    if (wide) launch_tc05<__nv_bfloat16, 256>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);
+    else launch_tc05<__nv_bfloat16, 128>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);
+  } else {
+    if (wide) launch_tc05<__half, 256>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);
+    else launch_tc05<__half, 128>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);
+  }
+}
+
+void k_matmul(OpCall& c) {
+  Epilogue ep;
+  gemm_dispatch(c.in[0], c.i[0] != 0, c.in[1], c.i[1] != 0, c.out[0], ep, stream_of(c));
+}
+
+void k_linear(OpCall& c) {
+  Epilogue ep;
+  ep.bias = c.in[2];
+  ep.residual = c.in[3];
+  ep.preact = c.out[1];
+  ep.act = static_cast<int>(c.i[0]);
+  gemm_dispatch(c.in[0], false, c.in[1], false, c.out[0], ep, stream_of(c));
+}
+
+}  // namespace
+
+// Reads and clears the GEMM error word of a device (0 = no error).  Synchronizes the device.
+int take_gemm_error(int device) {
+  int* flag;
+  {
+    std::lock_guard<std::mutex> lock(g_err_mu);
+    flag = g_err_flag[device];
+  }
+  if (!flag) return 0;
+  int host = 0;
+  OB_CUDA(cudaMemcpy(&host, flag, sizeof(int), cudaMemcpyDeviceToHost));
+  if (host) OB_CUDA(cudaMemset(flag, 0, sizeof(int)));
+  return host;
+}
+
+void register_cuda_gemm(KernelRegistry& r) {
+  const uint8_t any = kContiguous | kStrided | kEmpty;
+  r.add_kernel(OperatorId::Matmul, Constraints{Backend::CUDA, kMaskF32, any, Capability::None}, k_matmul, "sm100_gemm_simt_f32");
+  r.add_kernel(OperatorId::Matmul, Constraints{Backend::CUDA, dtype_bit(DType::F16), any, Capability::None}, k_matmul, "sm100_gemm_tc05_f16");
+  r.add_kernel(OperatorId::Matmul, Constraints{Backend::CUDA, dtype_bit(DType::BF16), any, Capability::Bf16}, k_matmul, "sm100_gemm_tc05_bf16");
+  r.add_kernel(OperatorId::Linear, Constraints{Backend::CUDA, kMaskF32, any, Capability::None}, k_linear, "sm100_linear_simt_f32");
+  r.add_kernel(OperatorId::Linear, Constraints{Backend::CUDA, dtype_bit(DType::F16), any, Capability::None}, k_linear, "sm100_linear_tc05_f16");
+  r.add_kernel(OperatorId::Linear, Constraints{Backend::CUDA, dtype_bit(DType::BF16), any, Capability::Bf16}, k_linear, "sm100_linear_tc05_bf16");
+}
+
+}  // namespace cu
+}  // namespace ob

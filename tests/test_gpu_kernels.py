@@ -1,0 +1,238 @@
+"""sm_100a kernels against a plain PyTorch float32 reference of the same op."""
+import numpy as np
+import pytest
+import torch
+
+import orthon_b200 as ob
+from orthon_b200 import _C
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"float32": 2e-5, "float16": 5e-3, "bfloat16": 4e-2}
+
+
+def dev_tensor(arr, dtype, requires_grad=False):
+    t = _C.from_numpy(np.ascontiguousarray(arr, dtype=np.float32), dtype).to("cuda:0")
+    if requires_grad:
+        t.requires_grad_(True)
+    return t
+
+
+def ref_round(arr, dtype):
+    """float32 values after a round trip through `dtype` (what the kernel actually sees)."""
+    t = torch.tensor(np.asarray(arr, dtype=np.float32))
+    if dtype == "float16":
+        t = t.half().float()
+    elif dtype == "bfloat16":
+        t = t.bfloat16().float()
+    return t
+
+
+def close(actual, expected, dtype, scale=1.0):
+    a = torch.tensor(actual.numpy().astype(np.float32))
+    e = expected.detach().float().reshape(a.shape)
+    tol = TOL[dtype] * scale
+    err = (a - e).abs().max().item()
+    ref = e.abs().max().item()
+    assert err <= tol * max(1.0, ref), f"max err {err} vs tol {tol * max(1.0, ref)}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+def test_elementwise_and_broadcast(dtype):
+    rng = np.random.default_rng(0)
+    a = rng.standard_normal((37, 65)); b = rng.standard_normal((65,))
+    ta, tb = ref_round(a, dtype), ref_round(b, dtype)
+    x, y = dev_tensor(a, dtype), dev_tensor(b, dtype)
+    close(x + y, ta + tb, dtype)
+    close(x * y, ta * tb, dtype)
+    close(x.relu(), ta.relu(), dtype)
+    close(x.gelu(), torch.nn.functional.gelu(ta), dtype)
+    close(x.sigmoid(), ta.sigmoid(), dtype)
+    close(x.tanh(), ta.tanh(), dtype)
+    close(x.exp(), ta.exp(), dtype, 4)
+    close(x * 2.5 + 1.0, ta * 2.5 + 1.0, dtype)
+    close(x.transpose(0, 1).contiguous(), ta.t(), dtype)
+    big = rng.standard_normal((1 << 20) + 3)
+    close(dev_tensor(big, dtype) + dev_tensor(big, dtype), 2 * ref_round(big, dtype), dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_unary_backward(dtype):
+    rng = np.random.default_rng(1)
+    a = rng.standard_normal((33, 40))
+    for name in ["relu", "gelu", "sigmoid", "tanh"]:
+        x = dev_tensor(a, dtype, True)
+        getattr(x, name)().sum().backward()
+        t = ref_round(a, dtype).requires_grad_(True)
+        getattr(torch.nn.functional, name)(t).sum().backward() if name != "tanh" else t.tanh().sum().backward()
+        close(x.grad, t.grad, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+def test_reductions(dtype):
+    rng = np.random.default_rng(2)
+    a = rng.standard_normal((6, 50, 33))
+    t = ref_round(a, dtype); x = dev_tensor(a, dtype)
+    close(x.sum(), t.sum(), dtype, 50)
+    close(x.mean(), t.mean(), dtype)
+    for d in range(3):
+        close(x.sum(d), t.sum(d), dtype, 8)
+        close(x.mean(d, True), t.mean(d, True), dtype)
+        v, i = x.max(d)
+        tv, ti = t.max(d)
+        close(v, tv, dtype)
+        assert i.tolist() == ti.flatten().tolist()
+    big = rng.standard_normal((3, 200000))
+    close(dev_tensor(big, dtype).sum(1), ref_round(big, dtype).sum(1), dtype, 200)
+    close(dev_tensor(big, dtype).sum(0), ref_round(big, dtype).sum(0), dtype, 4)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_bias_grad_unbroadcast(dtype):
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal((300, 96)); b = rng.standard_normal((96,))
+    x = dev_tensor(a, dtype, True); y = dev_tensor(b, dtype, True)
+    (x + y).sum().backward()
+    close(y.grad, torch.full((96,), 300.0), dtype)
+    close(x.grad, torch.ones(300, 96), dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+def test_softmax_family_and_losses(dtype):
+    rng = np.random.default_rng(4)
+    a = rng.standard_normal((64, 1000)) * 3
+    tgt = rng.integers(0, 1000, size=64)
+    t = ref_round(a, dtype).requires_grad_(True)
+    x = dev_tensor(a, dtype, True)
+    close(x.softmax(-1), t.softmax(-1), dtype)
+    close(x.log_softmax(-1), t.log_softmax(-1), dtype, 8)
+    loss = _C.cross_entropy(x, tgt.tolist())
+    tl = torch.nn.functional.cross_entropy(t, torch.tensor(tgt))
+    close(loss, tl, "float32" if dtype != "float32" else dtype, 50)
+    loss.backward(); tl.backward()
+    close(x.grad, t.grad, dtype, 0.05)
+    x2 = dev_tensor(a, dtype, True); t2 = ref_round(a, dtype).requires_grad_(True)
+    l2 = _C.nll_loss(x2.log_softmax(-1), _C.from_numpy(tgt.astype(np.int64)).to("cuda:0"))
+    tl2 = torch.nn.functional.nll_loss(t2.log_softmax(-1), torch.tensor(tgt))
+    close(l2, tl2, dtype, 8)
+    l2.backward(); tl2.backward()
+    close(x2.grad, t2.grad, dtype, 0.05)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layer_norm(dtype):
+    rng = np.random.default_rng(5)
+    for D in (512, 100):
+        a = rng.standard_normal((70, D)) * 2 + 0.5; w = rng.standard_normal((D,)); b = rng.standard_normal((D,))
+        g = rng.standard_normal((70, D))
+        x, ww, bb = dev_tensor(a, dtype, True), dev_tensor(w, dtype, True), dev_tensor(b, dtype, True)
+        t, tw, tb = (ref_round(v, dtype).requires_grad_(True) for v in (a, w, b))
+        y = _C._layer_norm(x, ww, bb, 1e-5)
+        ty = torch.nn.functional.layer_norm(t, (D,), tw, tb, 1e-5)
+        close(y, ty, dtype)
+        (y * dev_tensor(g, dtype)).sum().backward()
+        (ty * ref_round(g, dtype)).sum().backward()
+        close(x.grad, t.grad, dtype, 2)
+        close(ww.grad, tw.grad, dtype, 8)
+        close(bb.grad, tb.grad, dtype, 8)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embedding(dtype):
+    rng = np.random.default_rng(6)
+    w = rng.standard_normal((50, 64)); idx = rng.integers(0, 50, size=(4, 9))
+    ww = dev_tensor(w, dtype, True); tw = ref_round(w, dtype).requires_grad_(True)
+    ii = _C.from_numpy(idx.astype(np.int64)).to("cuda:0")
+    y = _C.embedding(ii, ww); ty = torch.nn.functional.embedding(torch.tensor(idx), tw)
+    close(y, ty, dtype)
+    y.sum().backward(); ty.sum().backward()
+    close(ww.grad, tw.grad, dtype)
+
+
+GEMM_SHAPES = [(128, 256, 64), (256, 512, 128), (200, 136, 72), (384, 1024, 512), (1024, 1024, 1024), (130, 96, 200)]
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16", "float32"])
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+def test_gemm_all_majors(dtype, ta, tb):
+    rng = np.random.default_rng(7)
+    for (M, N, K) in GEMM_SHAPES:
+        a = rng.standard_normal((K, M) if ta else (M, K)); b = rng.standard_normal((N, K) if tb else (K, N))
+        x, y = dev_tensor(a, dtype), dev_tensor(b, dtype)
+        t, u = ref_round(a, dtype), ref_round(b, dtype)
+        out = _C._gemm(x, ta, y, tb)
+        ref = (t.t() if ta else t) @ (u.t() if tb else u)
+        close(out, ref, dtype, 0.5 if dtype != "float32" else 20)
+    _C.cuda_synchronize()
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+def test_linear_epilogues(dtype):
+    rng = np.random.default_rng(8)
+    M, K, N = 300, 256, 512
+    a, w, b, r = rng.standard_normal((M, K)), rng.standard_normal((K, N)) * 0.1, rng.standard_normal((N,)), rng.standard_normal((M, N))
+    for act in ("none", "relu", "gelu"):
+        x, ww, bb = dev_tensor(a, dtype, True), dev_tensor(w, dtype, True), dev_tensor(b, dtype, True)
+        t, tw, tb = (ref_round(v, dtype).requires_grad_(True) for v in (a, w, b))
+        res = None if act == "relu" else dev_tensor(r, dtype)
+        y = _C.linear(x, ww, bb, act, res)
+        z = t @ tw + tb
+        ty = {"none": z, "relu": z.relu(), "gelu": torch.nn.functional.gelu(z)}[act]
+        if res is not None:
+            ty = ty + ref_round(r, dtype)
+        close(y, ty, dtype)
+        y.sum().backward(); ty.sum().backward()
+        close(x.grad, t.grad, dtype, 2)
+        close(ww.grad, tw.grad, dtype, 2)
+        close(bb.grad, tb.grad, dtype, 8)
+    _C.cuda_synchronize()
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_batched_gemm_and_attention(dtype):
+    rng = np.random.default_rng(9)
+    B, H, T, D = 2, 3, 128, 64
+    q, k, v = (rng.standard_normal((B, H, T, D)) for _ in range(3))
+    xq, xk, xv = (dev_tensor(t_, dtype, True) for t_ in (q, k, v))
+    tq, tk, tv = (ref_round(t_, dtype).requires_grad_(True) for t_ in (q, k, v))
+    out = _C._attention(xq, xk, xv, None, True, D ** -0.5)
+    ref = torch.nn.functional.scaled_dot_product_attention(tq, tk, tv, is_causal=True)
+    close(out, ref, dtype)
+    out.sum().backward(); ref.sum().backward()
+    for g, tg in ((xq, tq), (xk, tk), (xv, tv)):
+        close(g.grad, tg.grad, dtype, 2)
+    _C.cuda_synchronize()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_conv_and_pool(dtype):
+    rng = np.random.default_rng(10)
+    x = rng.standard_normal((3, 5, 12, 12)); w = rng.standard_normal((7, 5, 3, 3)) * 0.2; b = rng.standard_normal((7,))
+    for stride in (1, 2):
+        xx, ww, bb = dev_tensor(x, dtype, True), dev_tensor(w, dtype, True), dev_tensor(b, dtype, True)
+        t, tw, tb = (ref_round(v_, dtype).requires_grad_(True) for v_ in (x, w, b))
+        y = _C.conv2d(xx, ww, bb, stride, stride, 1, 1)
+        ty = torch.nn.functional.conv2d(t, tw, tb, stride=stride, padding=1)
+        close(y, ty, dtype)
+        y.sum().backward(); ty.sum().backward()
+        close(xx.grad, t.grad, dtype, 2); close(ww.grad, tw.grad, dtype, 8); close(bb.grad, tb.grad, dtype, 8)
+    xx = dev_tensor(x, dtype, True); t = ref_round(x, dtype).requires_grad_(True)
+    y = _C.maxpool2d(xx, 2, 2, 2, 2); ty = torch.nn.functional.max_pool2d(t, 2, 2)
+    close(y, ty, dtype)
+    y.sum().backward(); ty.sum().backward()
+    close(xx.grad, t.grad, dtype)
+
+
+def test_adam_fused_matches_formula():
+    rng = np.random.default_rng(11)
+    p0, g = rng.standard_normal(1000), rng.standard_normal(1000)
+    p = dev_tensor(p0, "float32"); m = _C._zeros_on([1000], "float32", "cuda:0"); v = _C._zeros_on([1000], "float32", "cuda:0")
+    model = _C._zeros_on([1000], "bfloat16", "cuda:0")
+    gg = dev_tensor(g * 128, "bfloat16")
+    _C._adam_step_(p, m, v, gg, model, 1e-3, 0.9, 0.999, 1e-8, 0.0, 1 - 0.9, 1 - 0.999, 1.0 / 128)
+    tp = torch.tensor(p0, dtype=torch.float32).requires_grad_(True)
+    opt = torch.optim.Adam([tp], lr=1e-3)
+    tp.grad = (torch.tensor(g * 128, dtype=torch.float32).bfloat16().float() / 128)
+    opt.step()
+    close(p, tp, "float32", 10)
+    close(model, tp, "bfloat16")
