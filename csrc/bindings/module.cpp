@@ -463,6 +463,7 @@ PYBIND11_MODULE(_C, m) {
     auto r = ops::amp_unscale_to_f32_and_check(g, inv);
     return py::make_tuple(r.first, r.second);
   });
+  m.def("_amp_unscale_into", [](const Tensor& g, double inv, Tensor& flag) { return ops::amp_unscale_into(g, inv, flag); });
   m.def("_amp_copy_master_to_model_", [](Tensor& model, const Tensor& master) { ops::amp_copy_master_to_model_(model, master); });
   m.def("_adam_step_", [](Tensor& master, Tensor& mm, Tensor& vv, const Tensor& grad, const py::object& model, double lr, double b1,
                           double b2, double eps, double wd, double bc1, double bc2, double gs) {
@@ -496,6 +497,23 @@ PYBIND11_MODULE(_C, m) {
     d["total_memory"] = c.total_memory();
     return d;
   });
+  // Timing event recorded on a device's current stream (CUDA events under the hood).
+  py::class_<CompletionToken>(m, "CudaEvent")
+      .def_static("record", [](int device) {
+        CudaContext& c = Runtime::instance().cuda(device);
+        DeviceGuard g(device);
+        return CompletionToken::record_on(device, c.current_stream(), true);
+      }, py::arg("device") = 0)
+      .def("ready", &CompletionToken::ready)
+      .def("synchronize", &CompletionToken::wait_host)
+      .def("elapsed_ms_since", &CompletionToken::elapsed_ms_since);
+  m.def("_flush_l2", [](int device) {
+    // Overwrites a buffer larger than the 126 MB L2 so the next kernel starts cold.
+    static Tensor scratch;
+    if (!scratch.defined() || scratch.device().index != device)
+      scratch = Tensor::empty({256LL << 20}, DType::U8, Device(DeviceType::CUDA, device));
+    ops::fill_raw(scratch, 1.0);
+  }, py::arg("device") = 0);
   m.def("is_grad_enabled", &grad_enabled);
   m.def("set_grad_enabled", &set_grad_enabled);
   m.def("_memory_pool_stats", [] {

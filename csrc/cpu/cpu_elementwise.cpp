@@ -241,6 +241,7 @@ void amp_unscale_cpu(OpCall& c) {
     if (!std::isfinite(v)) ok = false;
     po[o] = v;
   });
+  if (c.in[1].defined() && !ok) c.in[1].data_as<int32_t>()[0] = 1;
   c.i[0] = ok ? 1 : 0;
 }
 

@@ -567,7 +567,10 @@ void k_amp_unscale(OpCall& c) {
     g = packed;
   }
   Tensor& o = c.out[0];
-  Tensor flag = Tensor::zeros({1}, DType::I32, g.device());
+  // A caller-provided flag (in1) accumulates over many tensors and is read by the caller
+  // once; without it the result is read back here.
+  const bool shared_flag = c.in[1].defined();
+  Tensor flag = shared_flag ? c.in[1] : Tensor::zeros({1}, DType::I32, g.device());
   const int64_t n = g.numel();
   const int grid = ew_grid(n, kThreads, sm_count_for(g));
   cudaStream_t st = stream_of(c);
@@ -580,7 +583,7 @@ void k_amp_unscale(OpCall& c) {
     default: throw std::invalid_argument("amp unscale: gradients must be float32/float16/bfloat16");
   }
   check_launch("amp_unscale");
-  c.i[0] = read_flag(flag, st) ? 0 : 1;
+  c.i[0] = shared_flag ? 1 : (read_flag(flag, st) ? 0 : 1);
 }
 
 void k_amp_copy(OpCall& c) {

@@ -96,6 +96,9 @@ Tensor attention(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor
 
 // ---- AMP / optimizer kernels
 std::pair<Tensor, bool> amp_unscale_to_f32_and_check(const Tensor& grad, double inv_scale);
+// Unscales into a new float32 tensor and ORs "saw a non-finite value" into `flag` (int32 [1]
+// on the same device) without synchronizing the host.
+Tensor amp_unscale_into(const Tensor& grad, double inv_scale, Tensor& flag);
 void amp_copy_master_to_model_(Tensor& model, const Tensor& master);
 struct AdamHyper {
   double lr, beta1, beta2, eps, weight_decay, bias_c1, bias_c2, grad_scale;

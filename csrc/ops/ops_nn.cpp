@@ -684,6 +684,20 @@ std::pair<Tensor, bool> amp_unscale_to_f32_and_check(const Tensor& grad, double 
   return {out, c.i[0] != 0};
 }
 
+Tensor amp_unscale_into(const Tensor& grad, double inv_scale, Tensor& flag) {
+  if (flag.dtype() != DType::I32 || flag.numel() != 1 || flag.device() != grad.device())
+    throw std::invalid_argument("amp unscale: flag must be a one-element int32 tensor on the gradient's device");
+  Tensor out = Tensor::empty(grad.shape(), DType::F32, grad.device());
+  if (grad.numel() == 0) return out;
+  OpCall c;
+  c.in[0] = grad;
+  c.in[1] = flag;
+  c.out[0] = out;
+  c.f[0] = inv_scale;
+  run_kernel(OperatorId::AmpUnscale, grad.device(), grad.dtype(), c, layout_of(grad));
+  return out;
+}
+
 void amp_copy_master_to_model_(Tensor& model, const Tensor& master) {
   if (master.dtype() != DType::F32) throw std::invalid_argument("amp copy: master must be float32");
   if (model.shape() != master.shape()) throw std::invalid_argument("amp copy: shape mismatch");

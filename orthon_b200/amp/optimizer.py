@@ -1,0 +1,270 @@
+"""Mixed-precision optimizer wrapper: float16/bfloat16 model owners are optimised through
+detached float32 masters; float32 owners are their own masters.
+
+Each step transfers gradients to the masters as float32 (unscaling and checking them for
+inf/NaN with a single device flag read for the whole model), optionally averages the master
+gradients across ranks, runs the inner optimizer and refreshes the low-precision model copies.
+With the built-in Adam/SGD the master update and the model refresh are one fused kernel per
+parameter.  Module transforms (`to`, `cast`, `half`, ...) are reconciled lazily because the
+Python owners keep their identity.
+(reference project: python/orthon/amp/optimizer.py:48-284)"""
+from .. import _C
+from .._state import PreparedLoad, commit_prepared
+
+_LOW = {"float16", "bfloat16"}
+_OK = _LOW | {"float32"}
+
+
+def _no_grad():
+    import orthon_b200 as ob
+    return ob.no_grad()
+
+
+class _State:
+    __slots__ = ("parameter", "model_dtype", "master", "model_device")
+
+    def __init__(self, parameter, model_dtype, master, model_device):
+        self.parameter, self.model_dtype, self.master, self.model_device = parameter, model_dtype, master, model_device
+
+
+def _check_param(p):
+    if not isinstance(p, _C.Tensor):
+        raise TypeError("AMP model parameters must be Tensor owners")
+    if p.dtype not in _OK:
+        raise ValueError("AMP model parameters must be float32/float16/bfloat16")
+
+
+def _new_master(value, device):
+    with _no_grad():
+        m = value.to(device)  # always an independent copy
+        if m.dtype != "float32":
+            m = _C.cast(m, "float32")
+    m.requires_grad_(True)
+    return m
+
+
+def _check_sync(p, master):
+    if tuple(p.shape) != tuple(master.shape) or p.device != master.device:
+        raise ValueError("AMP master shape/device must match model owner")
+    if master.dtype != "float32" or p.dtype not in _OK:
+        raise ValueError("AMP synchronization requires an FP32 master")
+    if not p.is_contiguous or not master.is_contiguous:
+        raise RuntimeError("AMP synchronization requires contiguous tensors")
+
+
+class MixedPrecisionOptimizer:
+    def __init__(self, model, optimizer_cls, **optimizer_kwargs):
+        check = getattr(model, "_validate_master_gradient_sync", None)
+        if check is not None:
+            check()
+        from ..distributed import _state as dstate
+        self._group = dstate.get_active() if dstate.is_initialized() else None
+        self._ddp = model if hasattr(model, "_reducer") else None
+        params = tuple(model.parameters())
+        for p in params:
+            _check_param(p)
+        self._states = tuple(_State(p, p.dtype, p if p.dtype == "float32" else _new_master(p, p.device), p.device)
+                             for p in params)
+        self._factory, self._kwargs = optimizer_cls, dict(optimizer_kwargs)
+        self._inner = optimizer_cls((s.master for s in self._states), **optimizer_kwargs)
+
+    # -------------------------------------------------------- reconciliation
+    def _prepare_states(self):
+        fresh, copies, changed = [], [], False
+        for s in self._states:
+            p, master = s.parameter, s.master
+            _check_param(p)
+            if tuple(p.shape) != tuple(master.shape):
+                raise ValueError("AMP transformed parameter shape differs from master")
+            if p.dtype == "float32":
+                if s.model_dtype in _LOW:  # model was promoted: carry the master values over
+                    if master.device != p.device:
+                        master = _new_master(master, p.device)
+                    _check_sync(p, master)
+                    copies.append((p, master))
+                master = p
+            elif s.model_dtype == "float32":
+                master = _new_master(p, p.device)
+            elif master.device != p.device:
+                master = _new_master(master, p.device)
+            if p.dtype in _LOW:
+                _check_sync(p, master)
+            if master is not s.master or p.dtype != s.model_dtype or p.device != s.model_device:
+                changed = True
+            fresh.append(_State(p, p.dtype, master, p.device))
+        return tuple(fresh), copies, changed
+
+    def _publish(self, states, copies, changed):
+        if changed:
+            self._inner._rebind_parameters(s.master for s in states)
+            with _no_grad():
+                for p, master in copies:
+                    _C._amp_copy_master_to_model_(p, master)
+            self._states = states
+
+    def _reconcile(self):
+        self._publish(*self._prepare_states())
+
+    # ----------------------------------------------------------------- steps
+    def zero_grad(self):
+        for s in self._states:
+            s.parameter.zero_grad()
+            if s.master is not s.parameter:
+                s.master.zero_grad()
+
+    def _transfer_gradients(self, inv_scale=None):
+        states, copies, changed = self._prepare_states()
+        grads = tuple(s.parameter.grad for s in states)
+        for s, g in zip(states, grads):
+            if g is None:
+                continue
+            if tuple(g.shape) != tuple(s.parameter.shape) or g.device != s.parameter.device:
+                raise ValueError("AMP gradient shape/device must match model owner")
+            if g.dtype not in _OK:
+                raise ValueError("AMP gradients must be float32/float16/bfloat16")
+        out, found_inf, flag = [], False, None
+        with _no_grad():
+            for s, g in zip(states, grads):
+                if g is not None:
+                    if inv_scale is not None and g.device.is_cuda():
+                        if flag is None:
+                            flag = _C._zeros_on([1], "int32", str(g.device))
+                        g = _C._amp_unscale_into(g, float(inv_scale), flag)  # no host sync per tensor
+                    else:
+                        if g.dtype != "float32":
+                            g = _C.cast(g, "float32")
+                        elif s.model_dtype == "float32":
+                            g = g.to(g.device)
+                        if inv_scale is not None:
+                            g = g * inv_scale
+                            found_inf |= not _C.isfinite_all(g)
+                    if g.requires_grad or not g.is_leaf:
+                        g = g.to(g.device)
+                out.append(g)
+            if flag is not None:
+                found_inf |= bool(flag.tolist()[0])
+        self._publish(states, copies, changed)
+        for s, g in zip(self._states, out):
+            if g is None:
+                s.master.zero_grad()
+            else:
+                s.master.set_grad(g)
+        return found_inf
+
+    def _unscale_and_check(self, inv_scale):
+        return self._transfer_gradients(inv_scale)
+
+    def step(self):
+        self._transfer_gradients()
+        self._step_prepared()
+
+    def sync_to_model(self):
+        self._reconcile()
+        with _no_grad():
+            for s in self._states:
+                if s.master is not s.parameter:
+                    _C._amp_copy_master_to_model_(s.parameter, s.master)
+
+    def _amp_collective_device(self):
+        if self._group is not None:
+            self._group.ensure_open()
+        return self._states[0].master.device if self._states else None
+
+    def _all_reduce_master_grads(self):
+        from ..distributed import _state as dstate
+        from ..parallel.reducer import reduce_master_gradients
+        if self._group is None and dstate.is_initialized():
+            self._group = dstate.get_active()
+        if self._group is None:
+            return
+        self._group.ensure_open()
+        if self._group.world_size > 1:
+            reduce_master_gradients(tuple(s.master for s in self._states), self._group)
+
+    def _step_prepared(self):
+        self._all_reduce_master_grads()
+        fused = getattr(self._inner, "_step_with_model_copies", None)
+        if fused is not None:
+            fused([None if s.master is s.parameter else s.parameter for s in self._states])
+        else:
+            self._inner.step()
+            self.sync_to_model()
+
+    def get_lr(self):
+        return self._inner.get_lr()
+
+    def set_lr(self, lr):
+        self._inner.set_lr(lr)
+
+    # ----------------------------------------------------------------- state
+    def state_dict(self):
+        self._reconcile()
+        return {"version": 1, "orig_dtypes": [s.model_dtype for s in self._states],
+                "masters": [s.master for s in self._states], "inner": self._inner.state_dict()}
+
+    def load_state_dict(self, state, map_location=None):
+        commit_prepared([self._prepare_load_state_dict(state, map_location)])
+
+    def _prepare_load_state_dict(self, state, map_location=None, placement=None):
+        if type(state.get("version")) is not int or state["version"] != 1:
+            raise RuntimeError("MixedPrecisionOptimizer: unsupported state version")
+        dtypes, masters, inner_state = list(state["orig_dtypes"]), list(state["masters"]), state["inner"]
+        if len(dtypes) != len(self._states) or len(masters) != len(self._states):
+            raise ValueError("MixedPrecisionOptimizer state parameter count mismatch")
+        target = _C.Device(map_location) if isinstance(map_location, str) else map_location
+        if target is not None and not isinstance(target, _C.Device):
+            raise TypeError("AMP map_location must be a device string or Device")
+        devices = tuple(placement(s.parameter) if placement else s.parameter.device for s in self._states)
+        for cur, dt, master, dev in zip(self._states, dtypes, masters, devices):
+            p = cur.parameter
+            _check_param(p)
+            if dt != p.dtype:
+                raise ValueError("MixedPrecisionOptimizer dtype mismatch")
+            if not isinstance(master, _C.Tensor):
+                raise TypeError("AMP saved masters must be Tensor values")
+            if tuple(master.shape) != tuple(p.shape):
+                raise ValueError("MixedPrecisionOptimizer master shape mismatch")
+            if target is not None and target != dev:
+                raise ValueError("AMP map_location conflicts with bound model device")
+            if p.dtype in _LOW and not p.is_contiguous and dev == p.device:
+                raise RuntimeError("AMP synchronization requires contiguous tensors")
+        fresh = tuple(_State(s.parameter, dt, s.parameter if dt == "float32" else _new_master(master, dev), dev)
+                      for s, dt, master, dev in zip(self._states, dtypes, masters, devices))
+        temp = self._factory((s.master for s in fresh), **self._kwargs)
+        where = {id(s.master): dev for s, dev in zip(fresh, devices)}
+        prep = getattr(temp, "_prepare_load_state_dict", None)
+        if prep is not None:
+            prep(inner_state, map_location=target, placement=lambda p: where[id(p)]).commit()
+        else:
+            temp.load_state_dict(inner_state, map_location=target)
+        copies, old_values = [], []
+        with _no_grad():
+            for s in fresh:
+                if s.master is s.parameter:
+                    continue
+                p = s.parameter if s.parameter.device == s.model_device else s.parameter.to(s.model_device)
+                _check_sync(p, s.master)
+                copies.append((s.parameter, s.master))
+                old_values.append(_new_master(s.parameter, s.parameter.device))
+        before = (self._states, self._inner)
+        done = []
+
+        def commit():
+            with _no_grad():
+                for i, (p, master) in enumerate(copies):
+                    done.append(i)
+                    _C._amp_copy_master_to_model_(p, master)
+            self._states, self._inner = fresh, temp
+
+        def rollback():
+            self._states, self._inner = before
+            with _no_grad():
+                for i in reversed(done):
+                    p, _ = copies[i]
+                    v = old_values[i]
+                    if v.device != p.device:
+                        v = v.to(p.device)
+                    _C._amp_copy_master_to_model_(p, v)
+                done.clear()
+
+        return PreparedLoad(commit, rollback)
