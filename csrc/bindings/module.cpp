@@ -21,6 +21,7 @@ void copy_h2d_async(Tensor& dst, const Tensor& src, int stream_kind);
 void copy_d2h_async(Tensor& dst, const Tensor& src);
 unsigned int take_index_errors();
 int take_gemm_error(int device);
+uint64_t kernel_launch_count();
 }  // namespace cu
 void bind_distributed(py::module_& m);
 }  // namespace ob
@@ -457,6 +458,11 @@ PYBIND11_MODULE(_C, m) {
     return ops::attention(q, k, v, mask.is_none() ? Tensor() : mask.cast<Tensor>(), causal, scale, p,
                           seed.attr("__and__")(py::int_(0xFFFFFFFFFFFFFFFFull)).cast<uint64_t>());
   }, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("mask") = py::none(), py::arg("causal") = false, py::arg("scale") = 1.0, py::arg("dropout_p") = 0.0, py::arg("seed") = py::int_(0));
+  m.def("_attention_qkv", [](const Tensor& qkv, int64_t heads, const py::object& mask, bool causal, double scale, double p, const py::int_& seed) {
+    return ops::attention_packed(qkv, heads, mask.is_none() ? Tensor() : mask.cast<Tensor>(), causal, scale, p,
+                                 seed.attr("__and__")(py::int_(0xFFFFFFFFFFFFFFFFull)).cast<uint64_t>());
+  }, py::arg("qkv"), py::arg("heads"), py::arg("mask") = py::none(), py::arg("causal") = false, py::arg("scale") = 1.0,
+     py::arg("dropout_p") = 0.0, py::arg("seed") = py::int_(0));
   m.def("_gemm", &ops::gemm, py::arg("a"), py::arg("trans_a"), py::arg("b"), py::arg("trans_b"));
   m.def("isfinite_all", &ops::isfinite_all);
   m.def("_amp_unscale_to_float32_and_check", [](const Tensor& g, double inv) {
@@ -487,6 +493,7 @@ PYBIND11_MODULE(_C, m) {
       if (e) throw std::runtime_error("device cuda:" + std::to_string(d) + " reported a kernel wait timeout (code " + std::to_string(e) + ")");
     }
   });
+  m.def("_kernel_launch_count", [] { return cu::kernel_launch_count(); });
   m.def("_cuda_index_errors", [] { return cu::take_index_errors(); });
   m.def("_cuda_device_facts", [](int idx) {
     CudaContext& c = Runtime::instance().cuda(idx);

@@ -6,6 +6,7 @@
 //
 // Replaces (reference project paths): src/backends/cuda/{binary_kernels,unary_kernels,
 // cast_kernels}.cu and the transfer helpers in src/backends/cuda/adapters.cpp.
+#include <atomic>
 #include <type_traits>
 #include <vector>
 
@@ -16,7 +17,13 @@ namespace cu {
 
 int sm_count_for(const Tensor& t) { return Runtime::instance().cuda(t.device().index).sm_count(); }
 
+static std::atomic<uint64_t> g_launches{0};
+uint64_t kernel_launch_count() { return g_launches.load(); }
+
+// Called once per kernel wrapper after its launches; also counts the wrapper for the
+// launch statistics the benchmarks report.
 void check_launch(const char* what) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string("CUDA launch failed in ") + what + ": " + cudaGetErrorString(e));
 }

@@ -94,6 +94,12 @@ Tensor layer_norm(const Tensor& x, const Tensor& w, const Tensor& b, double eps)
 Tensor attention(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& mask, bool causal,
                  double scale, double dropout_p, uint64_t seed);
 
+// Self-attention over a packed projection [B, T, 3*E] (q | k | v along the last dim).  Heads are
+// read in place through strided views and the result is written straight into [B, T, E]; the
+// backward writes dq/dk/dv into one packed [B, T, 3*E] gradient.  No head transposes are copied.
+Tensor attention_packed(const Tensor& qkv, int64_t heads, const Tensor& mask, bool causal, double scale,
+                        double dropout_p, uint64_t seed);
+
 // ---- AMP / optimizer kernels
 std::pair<Tensor, bool> amp_unscale_to_f32_and_check(const Tensor& grad, double inv_scale);
 // Unscales into a new float32 tensor and ORs "saw a non-finite value" into `flag` (int32 [1]

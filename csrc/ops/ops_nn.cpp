@@ -743,3 +743,114 @@ void sgd_step_(Tensor& master, const Tensor& grad, Tensor& model, double lr, dou
 
 }  // namespace ops
 }  // namespace ob
+
+// ------------------------------------------------- packed-QKV self-attention
+namespace ob {
+namespace ops {
+namespace {
+
+// C = op(A) @ op(B) written into a preallocated (possibly strided) output.
+void gemm_out(const Tensor& a, bool ta, const Tensor& b, bool tb, Tensor& out) {
+  OpCall c;
+  c.in[0] = a;
+  c.in[1] = b;
+  c.out[0] = out;
+  c.i[0] = ta;
+  c.i[1] = tb;
+  run_kernel(OperatorId::Matmul, a.device(), a.dtype(), c, kStrided);
+}
+
+// [B, H, T, dh] view of slot `slot` (0 = q, 1 = k, 2 = v) of a packed [B, T, slots*E] tensor.
+Tensor head_view(const Tensor& packed, int slots, int slot, int64_t heads) {
+  const int64_t B = packed.shape()[0], T = packed.shape()[1], E = packed.shape()[2] / slots, dh = E / heads;
+  const int64_t row = slots * E;
+  return Tensor::view_of(packed, Layout(Shape{B, heads, T, dh}, Shape{T * row, dh, row, 1}, packed.offset() + slot * E));
+}
+
+Tensor softmax_probs(const Tensor& scores, const Tensor& mask, bool causal, double scale) {
+  const int64_t Tq = scores.shape()[2], Tk = scores.shape()[3];
+  Tensor out = Tensor::empty(scores.shape(), scores.dtype(), scores.device());
+  OpCall c;
+  c.in[0] = Tensor::view_of(scores, Layout(Shape{scores.numel() / (Tq * Tk), Tq, Tk}));
+  if (mask.defined()) c.in[1] = mask;
+  c.out[0] = Tensor::view_of(out, Layout(Shape{scores.numel() / (Tq * Tk), Tq, Tk}));
+  c.f[0] = scale;
+  c.i[0] = causal;
+  run_kernel(OperatorId::CausalSoftmax, scores.device(), scores.dtype(), c);
+  return out;
+}
+
+struct PackedAttentionNode : Node {
+  Tensor qkv, probs, keep;  // keep: dropout mask (scaled) or undefined
+  int64_t heads;
+  double scale;
+  const char* name() const override { return "PackedAttentionNode"; }
+  std::vector<Tensor> backward(const Tensor& g_in) override {
+    Tensor g = contiguous(g_in);
+    Tensor q = head_view(qkv, 3, 0, heads), k = head_view(qkv, 3, 1, heads), v = head_view(qkv, 3, 2, heads);
+    Tensor g4 = head_view(g, 1, 0, heads);
+    Tensor dqkv = Tensor::empty(qkv.shape(), qkv.dtype(), qkv.device());
+    Tensor dq = head_view(dqkv, 3, 0, heads), dk = head_view(dqkv, 3, 1, heads), dv = head_view(dqkv, 3, 2, heads);
+    Tensor p_used = keep.defined() ? mul(probs, keep) : probs;
+    gemm_out(p_used, true, g4, false, dv);            // dV = Pᵀ dO
+    Tensor dp = gemm(g4, false, v, true);              // dP = dO Vᵀ   (no graph: engine runs under no_grad)
+    if (keep.defined()) dp = mul(dp, keep);
+    Tensor ds = Tensor::empty(probs.shape(), probs.dtype(), probs.device());
+    {
+      const int64_t Tq = probs.shape()[2], Tk = probs.shape()[3];
+      OpCall c;
+      c.in[0] = Tensor::view_of(probs, Layout(Shape{probs.numel() / (Tq * Tk), Tq, Tk}));
+      c.in[1] = Tensor::view_of(dp, Layout(Shape{probs.numel() / (Tq * Tk), Tq, Tk}));
+      c.out[0] = Tensor::view_of(ds, Layout(Shape{probs.numel() / (Tq * Tk), Tq, Tk}));
+      c.f[0] = scale;
+      run_kernel(OperatorId::CausalSoftmaxBackward, probs.device(), probs.dtype(), c);
+    }
+    gemm_out(ds, false, k, false, dq);                 // dQ = dS K
+    gemm_out(ds, true, q, false, dk);                  // dK = dSᵀ Q
+    return {dqkv};
+  }
+  void release_saved() override { qkv = Tensor(); probs = Tensor(); keep = Tensor(); }
+};
+
+}  // namespace
+
+Tensor attention_packed(const Tensor& qkv_in, int64_t heads, const Tensor& mask, bool causal, double scale,
+                        double dropout_p, uint64_t seed) {
+  if (qkv_in.ndim() != 3 || qkv_in.shape()[2] % 3 != 0)
+    throw std::invalid_argument("attention_packed: expected a [B, T, 3*E] tensor");
+  const int64_t B = qkv_in.shape()[0], T = qkv_in.shape()[1], E = qkv_in.shape()[2] / 3;
+  if (heads < 1 || E % heads != 0) throw std::invalid_argument("attention_packed: E must be divisible by the head count");
+  if (mask.defined() && (mask.ndim() != 2 || mask.shape()[0] != T || mask.shape()[1] != T))
+    throw std::invalid_argument("attention_packed: mask must have shape [T, T]");
+  Tensor qkv = contiguous(qkv_in.detach());
+  Tensor q = head_view(qkv, 3, 0, heads), k = head_view(qkv, 3, 1, heads), v = head_view(qkv, 3, 2, heads);
+  Tensor scores, probs, keep;
+  {
+    NoGradGuard ng;
+    scores = gemm(q, false, k, true);  // [B, H, T, T]
+    probs = softmax_probs(scores, mask.defined() ? contiguous(mask.detach()) : Tensor(), causal, scale);
+    if (dropout_p > 0.0) keep = dropout_mask(probs.shape(), dropout_p, seed, probs.dtype(), probs.device());
+  }
+  Tensor out = Tensor::empty({B, T, E}, qkv.dtype(), qkv.device());
+  {
+    NoGradGuard ng;
+    Tensor out4 = head_view(out, 1, 0, heads);
+    Tensor p_used = keep.defined() ? mul(probs, keep) : probs;
+    gemm_out(p_used, false, v, false, out4);
+  }
+  if (needs_graph({qkv_in})) {
+    auto n = std::make_shared<PackedAttentionNode>();
+    n->qkv = qkv;
+    n->probs = probs;
+    n->keep = keep;
+    n->heads = heads;
+    n->scale = scale;
+    n->watch_version(qkv_in, "qkv");
+    n->set_inputs({qkv_in});
+    attach(out, n);
+  }
+  return out;
+}
+
+}  // namespace ops
+}  // namespace ob
