@@ -100,6 +100,7 @@ struct GraphTask {
   std::unordered_map<Node*, int> deps;
   std::vector<std::shared_ptr<TensorImpl>> leaves;  // discovery order, unique
   std::unordered_set<TensorImpl*> leaf_set;
+  std::unordered_map<TensorImpl*, int> leaf_edges;  // graph edges that still owe this leaf a gradient
   std::vector<std::pair<uint64_t, std::function<void()>>> finalizers;
   std::unordered_set<uint64_t> finalizer_keys;
 
@@ -136,6 +137,7 @@ struct GraphTask {
       if (e.kind == GraphEdge::Released) throw std::runtime_error(kFreedGraph);
       if (e.kind == GraphEdge::Leaf) {
         add_leaf(e.leaf);
+        ++leaf_edges[e.leaf.get()];
       } else if (e.kind == GraphEdge::Producer) {
         if (e.node->released()) throw std::runtime_error(kFreedGraph);
         ++deps[e.node.get()];
@@ -224,11 +226,30 @@ void AutogradEngine::backward(const Tensor& root, bool retain_graph) {
         const GraphEdge& e = edges[i];
         const bool has = i < in_grads.size() && in_grads[i].defined();
         if (e.kind == GraphEdge::Leaf) {
-          if (!has) continue;
-          const TensorImpl& L = *e.leaf;
-          check_grad(in_grads[i], L.layout().shape(), L.dtype(), L.device(), node->name());
-          Tensor& slot = leaf_grads[e.leaf.get()];
-          slot = accumulate(slot, in_grads[i]);
+          if (has) {
+            const TensorImpl& L = *e.leaf;
+            check_grad(in_grads[i], L.layout().shape(), L.dtype(), L.device(), node->name());
+            Tensor& slot = leaf_grads[e.leaf.get()];
+            slot = accumulate(slot, in_grads[i]);
+          }
+          // A leaf whose gradient storage was preassigned (reducer bucket slot) is committed
+          // the moment its last consumer has run, so its bucket can start reducing while the
+          // rest of backward is still executing.  Such leaves give up the all-or-nothing
+          // publication of the staged path below.
+          if (--task.leaf_edges[e.leaf.get()] == 0 && e.leaf->ag().grad_slot) {
+            auto it = leaf_grads.find(e.leaf.get());
+            if (it != leaf_grads.end() && it->second.defined()) {
+              AutogradMeta& m = e.leaf->ag();
+              Tensor slot(m.grad_slot);
+              const bool accumulating = m.grad && m.grad->buffer() == m.grad_slot->buffer();
+              if (accumulating) ops::add_(slot, it->second, 1.0);
+              else ops::copy_(slot, it->second);
+              m.grad = m.grad_slot;
+              leaf_grads.erase(it);
+              auto hooks = m.post_accumulate_hooks;
+              for (auto& h : hooks) h();
+            }
+          }
         } else if (e.kind == GraphEdge::Producer) {
           if (has) {
             check_grad(in_grads[i], e.node->out_shape, e.node->out_dtype, e.node->out_device, node->name());

@@ -493,6 +493,10 @@ PYBIND11_MODULE(_C, m) {
       if (e) throw std::runtime_error("device cuda:" + std::to_string(d) + " reported a kernel wait timeout (code " + std::to_string(e) + ")");
     }
   });
+  m.def("_cuda_stream_handle", [](int device) {
+    // cudaStream_t of the device's current stream, as an integer, for foreign callers.
+    return reinterpret_cast<uintptr_t>(Runtime::instance().cuda(device).current_stream());
+  }, py::arg("device") = 0);
   m.def("_kernel_launch_count", [] { return cu::kernel_launch_count(); });
   m.def("_cuda_index_errors", [] { return cu::take_index_errors(); });
   m.def("_cuda_device_facts", [](int idx) {
