@@ -69,7 +69,7 @@ def run_ours(args):
     wrapped = model
     if world > 1:
         wrapped = dist.DDP(model, sync_grads=False, bucket_size_mb=25)
-    opt = ob.amp.MixedPrecisionOptimizer(wrapped, ob.optim.Adam, lr=3e-4)
+    opt = ob.amp.MixedPrecisionOptimizer(wrapped, ob.optim.Adam, fused="update", lr=3e-4)
 
     rng = np.random.default_rng(100 + rank)
     host_ids = _C._pinned_empty([batch, seq], "int64")

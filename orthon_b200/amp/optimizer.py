@@ -53,20 +53,76 @@ def _check_sync(p, master):
 
 
 class MixedPrecisionOptimizer:
-    def __init__(self, model, optimizer_cls, **optimizer_kwargs):
+    def __init__(self, model, optimizer_cls, fused="auto", **optimizer_kwargs):
+        """`fused` only matters when `model` is a DDP wrapper whose reducer keeps gradients in
+        peer-memory buckets: "update" applies the optimizer inside the reduction kernel while
+        backward is still running (no GradScaler), "reduce"/"auto" averages in the kernel and
+        applies one fused update per bucket in `step()`, False keeps the per-parameter path."""
         check = getattr(model, "_validate_master_gradient_sync", None)
         if check is not None:
             check()
         from ..distributed import _state as dstate
         self._group = dstate.get_active() if dstate.is_initialized() else None
         self._ddp = model if hasattr(model, "_reducer") else None
+        self._peer = None
+        self._pending_inv_scale = None
         params = tuple(model.parameters())
         for p in params:
             _check_param(p)
+        if fused is not False and self._try_init_fused(model, params, optimizer_cls, fused, optimizer_kwargs):
+            return
         self._states = tuple(_State(p, p.dtype, p if p.dtype == "float32" else _new_master(p, p.device), p.device)
                              for p in params)
         self._factory, self._kwargs = optimizer_cls, dict(optimizer_kwargs)
         self._inner = optimizer_cls((s.master for s in self._states), **optimizer_kwargs)
+
+    # ------------------------------------------------------------ fused path
+    def _try_init_fused(self, model, params, optimizer_cls, fused, kwargs):
+        from ..optim import SGD, Adam
+        from ..optim.adam import _Moments
+        from ..parallel.peer_reducer import PeerReducer
+        reducer = getattr(model, "_reducer", None)
+        if not isinstance(reducer, PeerReducer) or optimizer_cls not in (Adam, SGD):
+            return False
+        if {id(p) for p in params} != {id(p) for _, p in reducer.parameters}:
+            return False  # frozen parameters: keep the general path
+        low = params[0].dtype in _LOW
+        masters = dict(zip((id(p) for _, p in reducer.parameters), reducer.flatten_state(want_masters=low)))
+        self._states = tuple(_State(p, p.dtype, masters[id(p)] if low else p, p.device) for p in params)
+        self._factory, self._kwargs = optimizer_cls, dict(kwargs)
+        self._inner = optimizer_cls((s.master for s in self._states), **kwargs)
+        self._kind = "adam" if optimizer_cls is Adam else "sgd"
+        if self._kind == "adam":
+            moments = dict(zip((id(p) for _, p in reducer.parameters), reducer.flat_moments()))
+            for s, b in zip(self._states, self._inner._bindings):
+                b.state = _Moments(*moments[id(s.parameter)])
+        by_master = {id(s.parameter): s.master for s in self._states}
+        reducer.set_decay_segments(lambda p: self._inner._weight_decay if self._inner._should_decay(by_master[id(p)]) else 0.0)
+        self._peer = reducer
+        if fused == "update":
+            reducer.mode = self._kind
+            reducer.hyper = self._fused_hyper
+            reducer.on_first_launch = self._begin_fused_step
+        return True
+
+    def _begin_fused_step(self):
+        if self._kind == "adam":
+            self._inner._t += 1
+
+    def _fused_hyper(self, grad_scale=1.0):
+        o = self._inner
+        h = {"lr": float(o._lr), "weight_decay": 0.0, "grad_scale": float(grad_scale)}
+        if self._kind == "adam":
+            h.update(beta1=float(o._beta1), beta2=float(o._beta2), eps=float(o._eps),
+                     bias_c1=1.0 - o._beta1 ** o._t, bias_c2=1.0 - o._beta2 ** o._t)
+        return h
+
+    def _fused_step(self, grad_scale=1.0):
+        peer = self._peer
+        peer.synchronize()
+        if peer.mode == "average":
+            self._begin_fused_step()
+            peer.local_update(self._kind, self._fused_hyper(grad_scale))
 
     # -------------------------------------------------------- reconciliation
     def _prepare_states(self):
@@ -107,6 +163,8 @@ class MixedPrecisionOptimizer:
 
     # ----------------------------------------------------------------- steps
     def zero_grad(self):
+        if self._peer is not None:
+            self._peer.reset()
         for s in self._states:
             s.parameter.zero_grad()
             if s.master is not s.parameter:
@@ -152,13 +210,28 @@ class MixedPrecisionOptimizer:
         return found_inf
 
     def _unscale_and_check(self, inv_scale):
+        if self._peer is not None:
+            if self._peer.mode != "average":
+                raise RuntimeError("GradScaler needs MixedPrecisionOptimizer(fused='reduce'): the update cannot run inside backward")
+            self._peer.synchronize()
+            self._pending_inv_scale = float(inv_scale)
+            return self._peer.found_inf()  # scaled, averaged gradients: same verdict on every rank
         return self._transfer_gradients(inv_scale)
 
     def step(self):
+        if self._peer is not None:
+            self._fused_step()
+            return
         self._transfer_gradients()
         self._step_prepared()
 
     def sync_to_model(self):
+        if self._peer is not None:
+            with _no_grad():
+                for b in self._peer.buckets:
+                    if b.master_flat is not b.param_flat:
+                        _C._amp_copy_master_to_model_(b.param_flat, b.master_flat)
+            return
         self._reconcile()
         with _no_grad():
             for s in self._states:
@@ -182,6 +255,11 @@ class MixedPrecisionOptimizer:
             reduce_master_gradients(tuple(s.master for s in self._states), self._group)
 
     def _step_prepared(self):
+        if self._peer is not None:
+            scale, self._pending_inv_scale = (self._pending_inv_scale or 1.0), None
+            self._begin_fused_step()
+            self._peer.local_update(self._kind, self._fused_hyper(scale))
+            return
         self._all_reduce_master_grads()
         fused = getattr(self._inner, "_step_with_model_copies", None)
         if fused is not None:
@@ -198,7 +276,8 @@ class MixedPrecisionOptimizer:
 
     # ----------------------------------------------------------------- state
     def state_dict(self):
-        self._reconcile()
+        if self._peer is None:
+            self._reconcile()
         return {"version": 1, "orig_dtypes": [s.model_dtype for s in self._states],
                 "masters": [s.master for s in self._states], "inner": self._inner.state_dict()}
 

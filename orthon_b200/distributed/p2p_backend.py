@@ -1,0 +1,197 @@
+"""Peer-memory transport for one node of NVLink/NVSwitch-connected GPUs.
+
+Collectives on tensors run as the peer-memory reduction kernel over a symmetric staging region
+that every rank maps from every other rank (CUDA IPC): no NCCL call is made for all_reduce,
+broadcast or barrier.  NCCL is only created lazily for tensors larger than the staging region.
+The DDP gradient path does not go through these generic collectives at all: PeerReducer keeps
+the gradients inside symmetric buckets and launches the fused kernel on them directly.
+"""
+import struct
+
+from .. import _C
+from ._backend import Backend, _TransportFailure
+from .nccl_backend import RENDEZVOUS_TIMEOUT_SECONDS
+from .store import ManagerStore, Store, store_from_env
+from .work import _CompletedWork
+
+STAGING_BYTES = 64 << 20
+_ESIZE = {"float32": 4, "float16": 2, "bfloat16": 2}
+
+
+def _no_grad():
+    import orthon_b200 as ob
+    return ob.no_grad()
+
+
+class SymmetricRegion:
+    """`ptrs[r]` is rank r's copy of the region as mapped into this process."""
+
+    def __init__(self, nbytes, ptrs, rank):
+        self.nbytes, self.ptrs, self.rank = nbytes, ptrs, rank
+
+    @property
+    def local(self):
+        return self.ptrs[self.rank]
+
+
+class PeerBackend(Backend):
+    supports_peer_reduce = True
+
+    def __init__(self, rank=None, world_size=None, device=None, store=None):
+        if rank is None or world_size is None:
+            raise ValueError("p2p backend requires rank and world_size")
+        if not 1 <= world_size <= _C._PEER_MAX_RANKS or not 0 <= rank < world_size:
+            raise ValueError(f"p2p backend supports 1..{_C._PEER_MAX_RANKS} ranks on one node")
+        self._rank, self._world = int(rank), int(world_size)
+        self._device = int(rank if device is None else device)
+        if self._device >= _C.cuda_device_count():
+            raise ValueError(f"p2p backend: cuda:{self._device} is not visible")
+        self._store = store_from_env(self._rank, self._world) if store is None else (
+            store if isinstance(store, Store) else ManagerStore(store))
+        self._generation = self._store.add(f"p2p/generation/{self._rank}", 1) - 1
+        self._xseq = 0
+        self._closed, self._failure = False, None
+        self._dev = f"cuda:{self._device}"
+        self._status = _C._zeros_on([1], "int32", self._dev)
+        self._found_inf = _C._zeros_on([1], "int32", self._dev)
+        self._epoch = 0
+        # One symmetric region: [staging grads | float32 staging | flags].
+        self._stage = self.allocate_symmetric(STAGING_BYTES * 2 + _C._PEER_FLAG_BYTES)
+        self._nccl = None
+
+    rank = property(lambda self: self._rank)
+    world_size = property(lambda self: self._world)
+    device = property(lambda self: self._device)
+
+    # ---------------------------------------------------------------- plumbing
+    def _open(self):
+        if self._closed:
+            raise RuntimeError("p2p backend has been shut down")
+        if self._failure is not None:
+            raise _TransportFailure("p2p backend failed: " + self._failure)
+
+    def exchange_objects(self, value: bytes):
+        prefix = f"p2p/x/{self._generation}/{self._xseq}"
+        self._xseq += 1
+        self._store.set(f"{prefix}/r{self._rank}", value)
+        keys = [f"{prefix}/r{r}" for r in range(self._world)]
+        self._store.wait_for(keys, RENDEZVOUS_TIMEOUT_SECONDS)
+        out = [self._store.get(k) for k in keys]
+        if self._store.add(f"{prefix}/leave", 1) == self._world:
+            for k in keys + [f"{prefix}/leave"]:
+                self._store.delete(k)
+        return out
+
+    def allocate_symmetric(self, nbytes):
+        """Collective: every rank allocates `nbytes` (zeroed) and maps everybody else's copy."""
+        nbytes = (int(nbytes) + 255) & ~255
+        ptr, handle = _C._peer_alloc(nbytes, self._device)
+        handles = self.exchange_objects(handle)
+        ptrs = [ptr if r == self._rank else _C._peer_open(handles[r], self._device) for r in range(self._world)]
+        self.exchange_objects(b"mapped")  # nobody touches a region before everyone has mapped it
+        return SymmetricRegion(nbytes, ptrs, self._rank)
+
+    def next_epoch(self):
+        self._epoch += 1
+        return self._epoch
+
+    def check_status(self):
+        """Reads the device error word (synchronises); a timeout poisons the group."""
+        code = self._status.tolist()[0]
+        if code:
+            self._failure = f"peer kernel wait timed out (code {code})"
+            raise _TransportFailure("p2p backend failed: " + self._failure)
+
+    def status_tensors(self):
+        return self._status, self._found_inf
+
+    # ------------------------------------------------------------- collectives
+    def _peer_sum(self, tensor):
+        """In-place sum over ranks through the symmetric staging region (compute stream)."""
+        n = int(tensor.numel)
+        esz = _ESIZE[tensor.dtype]
+        padded = (n + 7) & ~7
+        if padded * esz > STAGING_BYTES:
+            return False
+        stage = _C._tensor_from_ptr(self._stage.local, [padded], tensor.dtype, self._device)
+        if padded != n:
+            stage.fill_(0.0)
+        stage._copy_flat_range_from(0, tensor.reshape([-1]), 0, n)
+        grads = list(self._stage.ptrs)
+        staging = [p + STAGING_BYTES for p in self._stage.ptrs]
+        flags = [p + 2 * STAGING_BYTES for p in self._stage.ptrs]
+        _C._peer_reduce(self._rank, self._world, self._device, grads, staging, flags, padded, tensor.dtype, self.next_epoch(),
+                        1.0, "average", padded * esz <= (1 << 20), status=self._status, found_inf=self._found_inf,
+                        stream_kind=0)
+        tensor.reshape([-1])._copy_flat_range_from(0, stage, 0, n)
+        return True
+
+    def _fallback(self):
+        if self._nccl is None:
+            from .nccl_backend import NcclBackend
+            self._nccl = NcclBackend(self._rank, self._world, self._device, self._store)
+        return self._nccl
+
+    def _check(self, tensor):
+        if not tensor.device.is_cuda() or tensor.device.index != self._device:
+            raise RuntimeError(f"p2p collectives require tensors on cuda:{self._device}")
+        if not tensor.is_contiguous:
+            raise RuntimeError("p2p collectives require contiguous tensors")
+        if tensor.dtype not in _ESIZE:
+            raise RuntimeError(f"p2p collectives support {tuple(_ESIZE)}, got {tensor.dtype}")
+
+    def all_reduce(self, tensor, op="sum", async_op=False):
+        self._open()
+        if op != "sum":
+            raise NotImplementedError("p2p backend only supports all_reduce op='sum'")
+        self._check(tensor)
+        with _no_grad():
+            if self._world > 1 and not self._peer_sum(tensor):
+                return self._fallback().all_reduce(tensor, op=op, async_op=async_op)
+        return _CompletedWork() if async_op else tensor
+
+    def broadcast(self, tensor, src=0, async_op=False):
+        self._open()
+        if not 0 <= src < self._world:
+            raise ValueError("broadcast src must be in [0, world_size)")
+        self._check(tensor)
+        with _no_grad():
+            if self._world > 1:
+                # Non-source ranks contribute zeros, so the sum is the source's value.
+                if self._rank != src:
+                    tensor.fill_(0.0)
+                if not self._peer_sum(tensor):
+                    return self._fallback().broadcast(tensor, src=src, async_op=async_op)
+        return _CompletedWork() if async_op else tensor
+
+    def barrier(self):
+        self._open()
+        if self._world > 1:
+            token = _C._zeros_on([8], "float32", self._dev)
+            self._peer_sum(token)
+            _C.cuda_synchronize()
+            self.check_status()
+
+    def _validate_gradient_dtype(self, dtype):
+        if dtype not in _ESIZE:
+            raise RuntimeError(f"p2p gradient synchronization supports {tuple(_ESIZE)}, got {dtype}")
+
+    def shutdown(self):
+        if self._closed:
+            return
+        self._closed = True
+        try:
+            _C.cuda_synchronize()
+        except RuntimeError:
+            pass
+        if self._nccl is not None:
+            self._nccl.shutdown()
+        # Wait until every rank has stopped using the mappings before tearing them down.
+        try:
+            self.exchange_objects(b"bye")
+        except Exception:  # noqa: BLE001
+            pass
+        _C._peer_release_all()
+
+
+__all__ = ["PeerBackend", "SymmetricRegion"]

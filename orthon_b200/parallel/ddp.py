@@ -8,6 +8,7 @@ leaf gradient is committed).  Buffers are not broadcast.
 import weakref
 
 from ..distributed import _state
+from .peer_reducer import PeerReducer
 from .reducer import Reducer
 
 
@@ -31,7 +32,13 @@ class DistributedDataParallel:
             if id(p) not in seen and p.requires_grad:
                 seen.add(id(p))
                 owners.append((name, p))
-        self._reducer = Reducer(owners, group, bucket_size_mb, bool(overlap_grad_sync))
+        for _, p in owners:
+            group.broadcast(p, src=src)
+        if PeerReducer.eligible(owners, group):
+            # Buckets become the gradient storage; reduction starts from the leaf hooks.
+            self._reducer = PeerReducer(owners, group, bucket_size_mb, overlap=True)
+        else:
+            self._reducer = Reducer(owners, group, bucket_size_mb, bool(overlap_grad_sync))
         ref = weakref.ref(self._reducer)
 
         def finalize():
@@ -41,7 +48,6 @@ class DistributedDataParallel:
 
         self._finalizer, self._finalizer_key = finalize, id(self._reducer)
         for _, p in owners:
-            group.broadcast(p, src=src)
 
             def used(owner=id(p), ref=ref):
                 r = ref()

@@ -1,0 +1,236 @@
+"""Peer-memory reducer: the gradient buckets ARE the gradient storage.
+
+Every parameter's `.grad` is a view into a symmetric bucket that all ranks map.  The autograd
+engine writes a parameter's gradient into its slot as soon as its last consumer has run and
+fires the parameter's hook; when a bucket's last slot is filled the fused kernel is queued on
+the communication stream (ordered after the compute stream by an event), so reduction overlaps
+the rest of backward.  Depending on the mode the kernel either averages the bucket in place
+("reduce") or also applies the FP32-master Adam/SGD update and refreshes the low-precision
+parameters ("update"), all in one launch per bucket: no pack/unpack copies, no NCCL call, no
+separate scale / unscale / inf-check / optimizer kernels.
+
+Differences from the generic reducer, by construction: participation consensus is replaced by
+the kernel's flag exchange (every rank must launch the same buckets in the same order, which
+holds for models whose parameters all receive gradients); a parameter without a local gradient
+contributes zeros and receives the average; in "update" mode every parameter must have a
+gradient.
+"""
+from .. import _C
+from .reducer import _ELEMENT_BYTES, make_buckets
+
+
+def _no_grad():
+    import orthon_b200 as ob
+    return ob.no_grad()
+
+
+def _align(n, a):
+    return (n + a - 1) // a * a
+
+
+class _Bucket:
+    __slots__ = ("entries", "offsets", "n", "dtype", "grads", "staging", "flags", "grad_flat", "ready", "launched",
+                 "param_flat", "master_flat", "m_flat", "v_flat", "seg")
+
+
+class PeerReducer:
+    ONESHOT_BYTES = 512 << 10
+
+    @staticmethod
+    def eligible(parameters, group):
+        backend = getattr(group, "backend", None)
+        if not getattr(backend, "supports_peer_reduce", False) or not parameters:
+            return False
+        first = parameters[0][1]
+        return all(p.device.is_cuda() and p.device == first.device and p.dtype == first.dtype and p.is_contiguous
+                   and p.dtype in ("float32", "float16", "bfloat16") for _, p in parameters)
+
+    def __init__(self, parameters, group, bucket_size_mb=None, overlap=True):
+        self.parameters = tuple(parameters)
+        self.group = group
+        self.backend = group.backend
+        self.overlap = bool(overlap)
+        self.world, self.rank, self.device = group.world_size, group.rank, self.backend.device
+        self.dev = f"cuda:{self.device}"
+        self.mode = "average"          # or "adam" / "sgd" once an optimizer is attached in update mode
+        self.hyper = None              # callable -> dict, consulted at launch time
+        self.on_first_launch = None    # optimizer step counter hook
+        self.launch_count = 0
+        self._step_open = False
+        self._bucket_of = {}
+        dtype = self.parameters[0][1].dtype
+        esz = _ELEMENT_BYTES[dtype]
+        groups = make_buckets(self.parameters, 25 if bucket_size_mb is None else bucket_size_mb)
+        self.buckets = []
+        grad_bytes = stage_bytes = 0
+        for entries in groups:
+            b = _Bucket()
+            b.entries, b.offsets, off = entries, [], 0
+            for _, p in entries:
+                b.offsets.append(off)
+                off = _align(off + int(p.numel), 8)
+            b.n, b.dtype, b.ready, b.launched = off, dtype, 0, False
+            b.param_flat = b.master_flat = b.m_flat = b.v_flat = b.seg = None
+            self.buckets.append(b)
+            grad_bytes += _align(b.n * esz, 256)
+            stage_bytes += _align(b.n * 4, 256)
+        flag_bytes = _align(_C._PEER_FLAG_BYTES, 256)
+        region = self.backend.allocate_symmetric(grad_bytes + stage_bytes + flag_bytes * len(self.buckets))
+        g_off, s_off, f_off = 0, grad_bytes, grad_bytes + stage_bytes
+        for i, b in enumerate(self.buckets):
+            b.grads = [ptr + g_off for ptr in region.ptrs]
+            b.staging = [ptr + s_off for ptr in region.ptrs]
+            b.flags = [ptr + f_off for ptr in region.ptrs]
+            b.grad_flat = _C._tensor_from_ptr(b.grads[self.rank], [b.n], dtype, self.device)
+            g_off += _align(b.n * esz, 256)
+            s_off += _align(b.n * 4, 256)
+            f_off += flag_bytes
+            for (name, p), off in zip(b.entries, b.offsets):
+                p._set_grad_slot(_C._view_flat(b.grad_flat, off, list(p.shape)))
+                self._bucket_of[id(p)] = i
+        self._region = region
+
+    # ------------------------------------------------------------- diagnostics
+    def diagnostics(self):
+        return {"buckets": len(self.buckets), "outstanding": sum(1 for b in self.buckets if b.launched),
+                "async_launches": self.launch_count, "mode": self.mode}
+
+    # ------------------------------------------------------------------- hooks
+    def mark(self, owner_id):
+        i = self._bucket_of.get(owner_id)
+        if i is None:
+            return
+        b = self.buckets[i]
+        b.ready += 1
+        if self.overlap and not b.launched and b.ready >= len(b.entries):
+            self._launch(i)
+
+    def _launch(self, i):
+        b = self.buckets[i]
+        if not self._step_open:
+            self._step_open = True
+            if self.on_first_launch is not None:
+                self.on_first_launch()
+        hyper = self.hyper() if (self.hyper is not None and self.mode != "average") else {}
+        scale = hyper.pop("grad_scale", 1.0) / self.world
+        if b.seg is not None and self.mode != "average":
+            hyper["seg_end"], hyper["seg_wd"] = b.seg
+        oneshot = b.n * _ELEMENT_BYTES[b.dtype] <= self.ONESHOT_BYTES
+        status, found_inf = self.backend.status_tensors()
+        _C._stream_fence(self.device, 0, 1)  # communication stream waits for the gradients
+        fused = self.mode != "average"
+        _C._peer_reduce(self.rank, self.world, self.device, b.grads, b.staging, b.flags, b.n, b.dtype,
+                        self.backend.next_epoch(), scale, self.mode, oneshot,
+                        master=b.master_flat if fused else None, m=b.m_flat if self.mode == "adam" else None,
+                        v=b.v_flat if self.mode == "adam" else None,
+                        model=b.param_flat if (fused and b.param_flat is not None and b.master_flat is not b.param_flat) else None,
+                        hyper=hyper, status=status, found_inf=found_inf, stream_kind=1)
+        b.launched = True
+        self.launch_count += 1
+
+    # ------------------------------------------------------------ step control
+    def synchronize(self):
+        """Launches whatever has not been launched yet and orders the compute stream after the
+        communication stream.  No host wait."""
+        self.group.ensure_open()
+        with _no_grad():
+            for i, b in enumerate(self.buckets):
+                if b.launched:
+                    continue
+                for (name, p), off in zip(b.entries, b.offsets):
+                    g = p.grad
+                    slot = _C._view_flat(b.grad_flat, off, list(p.shape))
+                    if g is None:
+                        if self.mode != "average":
+                            raise RuntimeError(f"fused optimizer update needs a gradient for every parameter; '{name}' has none")
+                        slot.fill_(0.0)
+                        p.set_grad(slot)
+                    elif g._data_ptr != slot._data_ptr:
+                        slot._copy_data_(g)  # a gradient assigned by hand
+                        p.set_grad(slot)
+                self._launch(i)
+        _C._stream_fence(self.device, 1, 0)
+        for b in self.buckets:
+            b.ready, b.launched = 0, False
+        self._step_open = False
+
+    def wait(self):
+        _C._stream_fence(self.device, 1, 0)
+
+    def reset(self):
+        for b in self.buckets:
+            b.ready, b.launched = 0, False
+        self._step_open = False
+        self.launch_count = 0
+
+    def found_inf(self, clear=True):
+        """True when any reduced gradient since the last clear was non-finite (one device read)."""
+        _, flag = self.backend.status_tensors()
+        hit = bool(flag.tolist()[0])
+        if hit and clear:
+            flag.fill_(0.0)
+        return hit
+
+    # --------------------------------------------------------- optimizer state
+    def flatten_state(self, want_masters):
+        """Moves every parameter into one flat buffer per bucket (identity preserved) and, when
+        the parameters are low precision, creates flat float32 masters.  Returns, per parameter
+        in `self.parameters` order, (master view or None)."""
+        masters = {}
+        with _no_grad():
+            for b in self.buckets:
+                b.param_flat = _C._zeros_on([b.n], b.dtype, self.dev)
+                if want_masters:
+                    b.master_flat = _C._zeros_on([b.n], "float32", self.dev)
+                else:
+                    b.master_flat = b.param_flat
+                for (name, p), off in zip(b.entries, b.offsets):
+                    view = _C._view_flat(b.param_flat, off, list(p.shape))
+                    view._copy_data_(p)
+                    p._rebind_model_value_(view)
+                    p.requires_grad_(True)
+                    if want_masters:
+                        mv = _C._view_flat(b.master_flat, off, list(p.shape))
+                        mv._copy_data_(p)  # casts to float32
+                        mv.requires_grad_(True)
+                        masters[id(p)] = mv
+        return [masters.get(id(p)) for _, p in self.parameters]
+
+    def flat_moments(self):
+        """Flat zeroed Adam moments per bucket; returns per-parameter (m view, v view)."""
+        out = {}
+        for b in self.buckets:
+            b.m_flat = _C._zeros_on([b.n], "float32", self.dev)
+            b.v_flat = _C._zeros_on([b.n], "float32", self.dev)
+            for (name, p), off in zip(b.entries, b.offsets):
+                out[id(p)] = (_C._view_flat(b.m_flat, off, list(p.shape)), _C._view_flat(b.v_flat, off, list(p.shape)))
+        return [out[id(p)] for _, p in self.parameters]
+
+    def set_decay_segments(self, decay_of):
+        """`decay_of(param) -> weight decay` ; builds the per-bucket segment tables the kernel searches."""
+        import numpy as np
+        for b in self.buckets:
+            ends, wds = [], []
+            for i, ((name, p), off) in enumerate(zip(b.entries, b.offsets)):
+                end = b.offsets[i + 1] if i + 1 < len(b.offsets) else b.n
+                ends.append(end)
+                wds.append(float(decay_of(p)))
+            if any(w != 0.0 for w in wds):
+                b.seg = (_C.from_numpy(np.asarray(ends, dtype=np.int64)).to(self.dev),
+                         _C.from_numpy(np.asarray(wds, dtype=np.float32)).to(self.dev))
+            else:
+                b.seg = None
+
+    def local_update(self, kind, hyper):
+        """Applies the optimizer bucket by bucket from the (already averaged) gradients: one
+        fused kernel per bucket.  Used when the update may not run inside backward (GradScaler)."""
+        with _no_grad():
+            for b in self.buckets:
+                model = b.param_flat if b.master_flat is not b.param_flat else None
+                if kind == "adam":
+                    _C._adam_step_(b.master_flat, b.m_flat, b.v_flat, b.grad_flat, model, hyper["lr"], hyper["beta1"],
+                                   hyper["beta2"], hyper["eps"], hyper.get("weight_decay", 0.0), hyper["bias_c1"],
+                                   hyper["bias_c2"], hyper.get("grad_scale", 1.0))
+                else:
+                    _C._sgd_step_(b.master_flat, b.grad_flat, model, hyper["lr"], hyper.get("weight_decay", 0.0),
+                                  hyper.get("grad_scale", 1.0))
