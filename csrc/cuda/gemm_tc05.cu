@@ -4,8 +4,8 @@
 //
 // Design
 //  * Persistent kernel, one CTA per SM, tiles of 128 x BN (BN = 256 or 128) x 64.
-//  * Warp-specialised: warp 0 issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle, no
-//    cluster multicast) into a multi-stage shared-memory ring guarded by mbarriers; warp 1
+//  * Warp-specialised: warp 0 issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle, every
+//    CTA fetches its own tiles) into a multi-stage shared-memory ring guarded by mbarriers; warp 1
 //    issues tcgen05.mma (one elected thread) with the accumulator in TMEM and releases ring
 //    slots with tcgen05.commit; warps 2-5 drain the accumulator with tcgen05.ld and run the
 //    fused epilogue (bias, ReLU/GELU, residual add, optional pre-activation copy, dtype

@@ -2,7 +2,7 @@
 //
 // Every rank maps every other rank's gradient bucket, float32 staging bucket and flag block
 // (CUDA IPC).  One kernel launch per bucket and per rank then does, with plain peer loads and
-// stores (no NCCL call, no TMA, no multicast):
+// stores (no NCCL call and no bulk-tensor copies):
 //
 //   two-shot   entry barrier -> each rank reduces its 1/world slice by reading that slice from
 //              every peer, multiplies by `scale` (1/world_size x 1/loss_scale), checks for
