@@ -1,0 +1,242 @@
+"""Reference arm: the same causal-LM training step driven through the UNMODIFIED reference
+package (installed under baseline/_ref) and its own public API.
+
+What is stock: every operator, autograd, nn.LayerNorm, nn.Linear.forward,
+MixedPrecisionOptimizer, Adam, DistributedDataParallel, the NCCL backend.  What the harness has
+to do itself, because the reference cannot do it otherwise:
+  * parameters are created with from_numpy + Parameter (the stock module constructors fill
+    weights one element at a time from Python, which is infeasible for 1.3 B parameters);
+  * the embeddings stay float32 and their output is cast, attention scores are cast to float32
+    around the softmax, logits are cast to float32 before log_softmax + nll_loss, because
+    those reference kernels are float32-only on CUDA.
+Timing is wall-clock between cuda_synchronize() calls (the reference exposes no event API).
+"""
+import json
+import os
+import sys
+import time
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF = os.path.join(HERE, "_ref")
+
+
+def _import_reference():
+    if not os.path.isdir(os.path.join(REF, "orthon")):
+        raise RuntimeError("baseline/_ref/orthon is missing (reference not installed)")
+    sys.path.insert(0, REF)
+    import orthon  # noqa: F401
+    return orthon
+
+
+def build_model(ortho, cfg, dtype, device, seed):
+    nn = ortho.nn
+    rng = np.random.default_rng(seed)
+
+    def normal(shape, dt="float32"):
+        arr = (rng.standard_normal(shape, dtype=np.float32) * cfg["init_std"]).astype(np.float32)
+        return ortho.from_numpy(arr) if dt == "float32" else ortho.from_numpy(arr, dtype=dt)
+
+    def const(shape, value):
+        t = ortho.full(shape, value)
+        return t if dtype == "float32" else ortho.cast(t, dtype)
+
+    def linear(i, o):
+        lin = nn.Linear.__new__(nn.Linear)  # stock forward; weights filled in bulk
+        nn.Module.__init__(lin)
+        lin.weight = nn.Parameter(normal((i, o), dtype))
+        lin.bias = nn.Parameter(const([o], 0.0))
+        return lin
+
+    def layer_norm():
+        ln = nn.LayerNorm(cfg["d_model"])
+        if dtype != "float32":
+            ln.weight = nn.Parameter(const([cfg["d_model"]], 1.0))
+            ln.bias = nn.Parameter(const([cfg["d_model"]], 0.0))
+        return ln
+
+    E, H, F, V, T = cfg["d_model"], cfg["n_heads"], cfg["d_ff"], cfg["vocab_size"], cfg["max_seq"]
+    low = dtype != "float32"
+
+    class Attention(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q_proj, self.k_proj, self.v_proj, self.out_proj = linear(E, E), linear(E, E), linear(E, E), linear(E, E)
+
+        def forward(self, x, mask):
+            B, Tn, _ = x.shape
+            flat = x.reshape([B * Tn, E])
+
+            def heads(proj):
+                y = proj(flat).reshape([B, Tn, H, E // H]).transpose(1, 2).contiguous()
+                return y.reshape([B * H, Tn, E // H])
+
+            q, k, v = heads(self.q_proj), heads(self.k_proj), heads(self.v_proj)
+            scores = ortho.matmul(q, k.transpose(-2, -1))
+            if low:
+                scores = ortho.cast(scores, "float32")
+            scores = scores * ((E // H) ** -0.5) + mask
+            weights = ortho.exp(ortho.log_softmax(scores, dim=-1))
+            if low:
+                weights = ortho.cast(weights, dtype)
+            y = ortho.matmul(weights, v).reshape([B, H, Tn, E // H]).transpose(1, 2).contiguous()
+            return self.out_proj(y.reshape([B * Tn, E])).reshape([B, Tn, E])
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.ln1, self.ln2 = layer_norm(), layer_norm()
+            self.attn = Attention()
+            self.fc1, self.fc2 = linear(E, F), linear(F, E)
+
+        def forward(self, x, mask):
+            x = x + self.attn(self.ln1(x), mask)
+            B, Tn, _ = x.shape
+            h = self.ln2(x).reshape([B * Tn, E])
+            h = self.fc2(ortho.gelu(self.fc1(h)))
+            return x + h.reshape([B, Tn, E])
+
+    class LM(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.tok = nn.Parameter(normal((V, E)))
+            self.pos = nn.Parameter(normal((T, E)))
+            for i in range(cfg["n_layers"]):
+                setattr(self, f"block_{i}", Block())
+            self.ln_f = layer_norm()
+            self.head = linear(E, V)
+
+        def forward(self, idx, pos, mask):
+            x = ortho.embedding(idx, self.tok) + ortho.embedding(pos, self.pos)
+            if low:
+                x = ortho.cast(x, dtype)
+            for i in range(cfg["n_layers"]):
+                x = getattr(self, f"block_{i}")(x, mask)
+            x = self.ln_f(x)
+            B, Tn, _ = x.shape
+            logits = self.head(x.reshape([B * Tn, E]))
+            if low:
+                logits = ortho.cast(logits, "float32")
+            return ortho.log_softmax(logits, dim=-1)
+
+    model = LM()
+    if device != "cpu":
+        model.to(device)
+    return model
+
+
+CONFIGS = {
+    "1p3b": (dict(vocab_size=32000, d_model=2048, n_layers=24, n_heads=16, d_ff=8192, max_seq=1024, init_std=0.02), 8, 1024,
+             "causal-transformer-1.3B (vocab 32000, d2048, L24, H16, ffn 8192)"),
+    "tiny": (dict(vocab_size=8192, d_model=512, n_layers=8, n_heads=8, d_ff=2048, max_seq=512, init_std=0.02), 32, 512,
+             "tiny-causal-lm (vocab 8192, d512, L8, H8, ffn 2048)"),
+}
+
+
+def run_reference_lm(args, cfg_override=None, dtype_override=None, device_override=None):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    try:
+        ortho = _import_reference()
+    except Exception as exc:  # noqa: BLE001
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": f"cannot import the reference build: {exc}"}))
+        return
+    cfg, batch, seq, name = CONFIGS[args.model]
+    if cfg_override:
+        cfg, batch, seq = cfg_override
+    dtype = dtype_override or "bfloat16"
+    device = device_override or f"cuda:{local}"
+    if device != "cpu" and not ortho.cuda_enabled():
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "reference build has no CUDA support"}))
+        return
+    import orthon.distributed as ddist
+    from orthon.amp import GradScaler, MixedPrecisionOptimizer
+    from orthon.optim import Adam
+
+    if world > 1:
+        store = f"/tmp/orthon_ref_store_{os.environ.get('MASTER_PORT', '0')}_{os.getppid()}"
+        os.makedirs(store, exist_ok=True)
+        os.environ["ORTHON_NCCL_STORE_DIR"] = store
+        ddist.init_process_group("nccl", rank=rank, world_size=world, device=local)
+
+    model = build_model(ortho, cfg, dtype, device, seed=1234)
+    wrapped = model
+    if world > 1:
+        wrapped = ddist.DistributedDataParallel(model, sync_grads=False)
+    opt = MixedPrecisionOptimizer(wrapped, Adam, lr=3e-4)
+    scaler = GradScaler(enabled=False)
+
+    rng = np.random.default_rng(100 + rank)
+    mask_np = np.triu(np.full((seq, seq), -1e9, dtype=np.float32), k=1).reshape(1, seq, seq)
+    mask = ortho.from_numpy(mask_np)
+    pos = ortho.from_numpy(np.tile(np.arange(seq, dtype=np.int64), (batch, 1)))
+    if device != "cpu":
+        mask, pos = mask.to(device), pos.to(device)
+
+    def make_batch():
+        tok = rng.integers(0, cfg["vocab_size"], size=(batch, seq + 1), dtype=np.int64)
+        x = ortho.from_numpy(np.ascontiguousarray(tok[:, :-1]))
+        y = ortho.from_numpy(np.ascontiguousarray(tok[:, 1:]).reshape(-1))
+        return (x, y) if device == "cpu" else (x.to(device), y.to(device))
+
+    def step(x, y):
+        opt.zero_grad()
+        log_probs = wrapped(x, pos, mask)
+        loss = ortho.nll_loss(log_probs, y, reduction="mean")
+        scaler.scale(loss).backward()
+        scaler.step(opt)
+        scaler.update()
+        return loss
+
+    def sync():
+        if device != "cpu":
+            ortho.cuda_synchronize()
+        if world > 1:
+            ddist.barrier()
+
+    x, y = make_batch()
+    for _ in range(args.warmup):
+        step(x, y)
+    sync()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step(x, y)
+    sync()
+    device_s = time.perf_counter() - t0
+
+    t0 = time.perf_counter()
+    last = None
+    for _ in range(args.steps):
+        x, y = make_batch()            # host -> device copy of this step's inputs
+        last = float(step(x, y).item())  # device -> host read of the loss
+    sync()
+    e2e_s = time.perf_counter() - t0
+
+    if world > 1:
+        t = ortho.from_numpy(np.asarray([device_s, e2e_s], dtype=np.float32)).to(device)
+        # max over ranks via sum of per-rank one-hot rows
+        rows = np.zeros((world, 2), dtype=np.float32)
+        rows[rank] = [device_s, e2e_s]
+        t = ortho.from_numpy(rows).to(device)
+        ddist.all_reduce(t)
+        vals = np.asarray(t.to("cpu").tolist()).reshape(world, 2)
+        device_s, e2e_s = float(vals[:, 0].max()), float(vals[:, 1].max())
+    tokens = batch * seq * world * args.steps
+    if rank == 0:
+        print(json.dumps({
+            "metric": "ddp_train_tokens_per_s", "value": tokens / device_s, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": device_s / args.steps * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if dtype == "bfloat16" else dtype,
+            "data": "synthetic token ids, random-init weights", "impl": "reference",
+            "config": {"model": name, "global_batch": batch * world, "seq_len": seq, "parallelism": f"dp{world}",
+                       "optimizer": "FP32-master Adam (reference MixedPrecisionOptimizer, scaler disabled)",
+                       "timing": "wall clock between cuda_synchronize() calls (no event API in the reference)"},
+            "e2e": {"value": tokens / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 2 * batch * seq * 8,
+                    "d2h_bytes_per_step": 4, "last_loss": last},
+        }), flush=True)
+    if world > 1:
+        ddist.destroy_process_group()
