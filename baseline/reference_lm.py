@@ -163,6 +163,13 @@ def run_reference_lm(args, cfg_override=None, dtype_override=None, device_overri
         os.environ["ORTHON_NCCL_STORE_DIR"] = store
         ddist.init_process_group("nccl", rank=rank, world_size=world, device=local)
 
+    # The reference pool never splits blocks, so cached blocks of one size class cannot serve
+    # another; on the 1.3 B config the cache alone exhausts 180 GB.  Its own runtime toggle caps
+    # the cache so that the configuration fits.
+    cap_gb = os.environ.get("ORTHON_REF_POOL_CAP_GB", "16" if args.model == "1p3b" else "")
+    if cap_gb and device != "cpu":
+        ortho._C._memory_pool_set_max_cached_bytes(int(float(cap_gb) * (1 << 30)))
+
     model = build_model(ortho, cfg, dtype, device, seed=1234)
     wrapped = model
     if world > 1:
@@ -199,8 +206,17 @@ def run_reference_lm(args, cfg_override=None, dtype_override=None, device_overri
             ddist.barrier()
 
     x, y = make_batch()
-    for _ in range(args.warmup):
-        step(x, y)
+    try:
+        for _ in range(args.warmup):
+            step(x, y)
+    except RuntimeError as exc:
+        if "out of memory" not in str(exc):
+            raise
+        stats = ortho._C._memory_pool_stats() if hasattr(ortho._C, "_memory_pool_stats") else None
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "the reference runs out of device memory on this config "
+                              f"(pool cache capped at {cap_gb or 'unlimited'} GB): {exc}", "pool_stats": str(stats)}), flush=True)
+        return
     sync()
     t0 = time.perf_counter()
     for _ in range(args.steps):

@@ -465,6 +465,7 @@ PYBIND11_MODULE(_C, m) {
      py::arg("dropout_p") = 0.0, py::arg("seed") = py::int_(0));
   m.def("_gemm", &ops::gemm, py::arg("a"), py::arg("trans_a"), py::arg("b"), py::arg("trans_b"));
   m.def("isfinite_all", &ops::isfinite_all);
+  m.def("_isfinite_into", [](const Tensor& t, Tensor& flag) { ops::isfinite_into(t, flag); });
   m.def("_amp_unscale_to_float32_and_check", [](const Tensor& g, double inv) {
     auto r = ops::amp_unscale_to_f32_and_check(g, inv);
     return py::make_tuple(r.first, r.second);

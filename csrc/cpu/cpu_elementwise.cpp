@@ -225,6 +225,7 @@ void isfinite_cpu(OpCall& c) {
   walk(t.shape(), t.strides(), {}, {}, [&](int64_t o, int64_t, int64_t) {
     if (!std::isfinite(load_as_double(p + o * esz, t.dtype()))) ok = false;
   });
+  if (c.in[1].defined() && !ok) c.in[1].data_as<int32_t>()[0] = 1;
   c.i[0] = ok ? 1 : 0;
 }
 

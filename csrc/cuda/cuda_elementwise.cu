@@ -549,7 +549,8 @@ void k_isfinite(OpCall& c) {
   const Tensor& t = c.in[0];
   c.i[0] = 1;
   if (!dtype_is_floating(t.dtype())) return;
-  Tensor flag = Tensor::zeros({1}, DType::I32, t.device());
+  const bool shared_flag = c.in[1].defined();  // caller accumulates over many tensors and reads once
+  Tensor flag = shared_flag ? c.in[1] : Tensor::zeros({1}, DType::I32, t.device());
   const int64_t n = t.numel();
   const bool packed = t.is_contiguous();
   const Strided s = make_strided(t.shape(), &t.strides(), nullptr, nullptr);
@@ -563,7 +564,7 @@ void k_isfinite(OpCall& c) {
     default: finite_kernel<__nv_bfloat16><<<grid, kThreads, 0, st>>>(t.data_as<__nv_bfloat16>(), n, s, packed, pf); break;
   }
   check_launch("isfinite_all");
-  c.i[0] = read_flag(flag, st) ? 0 : 1;
+  c.i[0] = shared_flag ? 1 : (read_flag(flag, st) ? 0 : 1);
 }
 
 void k_amp_unscale(OpCall& c) {

@@ -505,11 +505,206 @@ __global__ void layernorm_bwd_finalize(const float* __restrict__ partial, T* __r
   if (db) db[j] = from_f<T>(b);
 }
 
+// ---- register-resident LayerNorm: every thread keeps its 16-byte packs of the row in
+// registers between the statistics and the output pass, so each element is read once.
+__device__ __forceinline__ void block_sum2(float& a, float& b, float* smem /* 64 floats */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  a = warp_sum(a);
+  b = warp_sum(b);
+  __syncthreads();
+  if (lane == 0) { smem[warp] = a; smem[32 + warp] = b; }
+  __syncthreads();
+  float ra = (threadIdx.x < nw) ? smem[threadIdx.x] : 0.f;
+  float rb = (threadIdx.x < nw) ? smem[32 + threadIdx.x] : 0.f;
+  if (warp == 0) {
+    ra = warp_sum(ra);
+    rb = warp_sum(rb);
+    if (lane == 0) { smem[0] = ra; smem[32] = rb; }
+  }
+  __syncthreads();
+  a = smem[0];
+  b = smem[32];
+}
+
+template <class T, int CH>
+__global__ void layernorm_fwd_fast(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ b,
+                                   T* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd, int64_t D,
+                                   float eps) {
+  constexpr int N = Pack<T>::N;
+  __shared__ float smem[64];
+  const int64_t r = blockIdx.x;
+  const T* row = x + r * D;
+  const int64_t npack = D / N;
+  float v[CH][N];
+  float s = 0.f;
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int64_t p = static_cast<int64_t>(c) * blockDim.x + threadIdx.x;
+    if (p < npack) {
+      Pack<T> pk = load_pack(row + p * N);
+#pragma unroll
+      for (int k = 0; k < N; ++k) { v[c][k] = to_f(pk.v[k]); s += v[c][k]; }
+    }
+  }
+  const float m = block_sum(s, smem) / static_cast<float>(D);
+  float q = 0.f;
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int64_t p = static_cast<int64_t>(c) * blockDim.x + threadIdx.x;
+    if (p < npack) {
+#pragma unroll
+      for (int k = 0; k < N; ++k) { const float z = v[c][k] - m; q += z * z; }
+    }
+  }
+  const float rs = rsqrtf(block_sum(q, smem) / static_cast<float>(D) + eps);
+  if (threadIdx.x == 0) { mean[r] = m; rstd[r] = rs; }
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int64_t p = static_cast<int64_t>(c) * blockDim.x + threadIdx.x;
+    if (p < npack) {
+      Pack<T> pw, pb, out;
+      if (w) pw = load_pack(w + p * N);
+      if (b) pb = load_pack(b + p * N);
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        float o = (v[c][k] - m) * rs;
+        if (w) o *= to_f(pw.v[k]);
+        if (b) o += to_f(pb.v[k]);
+        out.v[k] = from_f<T>(o);
+      }
+      store_pack(y + r * D + p * N, out);
+    }
+  }
+}
+
+template <class T, int CH>
+__global__ void layernorm_bwd_fast(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ g,
+                                   const float* __restrict__ mean, const float* __restrict__ rstd, T* __restrict__ dx,
+                                   float* __restrict__ partial, int64_t R, int64_t D) {
+  constexpr int N = Pack<T>::N;
+  __shared__ float smem[64];
+  const int64_t npack = D / N;
+  float wv[CH][N], dw_acc[CH][N], db_acc[CH][N];
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int64_t p = static_cast<int64_t>(c) * blockDim.x + threadIdx.x;
+    Pack<T> pw;
+    if (w && p < npack) pw = load_pack(w + p * N);
+#pragma unroll
+    for (int k = 0; k < N; ++k) {
+      wv[c][k] = (w && p < npack) ? to_f(pw.v[k]) : 1.f;
+      dw_acc[c][k] = db_acc[c][k] = 0.f;
+    }
+  }
+  for (int64_t r = blockIdx.x; r < R; r += gridDim.x) {
+    const float m = mean[r], rs = rstd[r];
+    float xh[CH][N], gy[CH][N];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int64_t p = static_cast<int64_t>(c) * blockDim.x + threadIdx.x;
+      if (p < npack) {
+        Pack<T> px = load_pack(x + r * D + p * N), pg = load_pack(g + r * D + p * N);
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+          const float gv = to_f(pg.v[k]);
+          xh[c][k] = (to_f(px.v[k]) - m) * rs;
+          gy[c][k] = gv * wv[c][k];
+          s1 += gy[c][k];
+          s2 += gy[c][k] * xh[c][k];
+          dw_acc[c][k] += gv * xh[c][k];
+          db_acc[c][k] += gv;
+        }
+      }
+    }
+    block_sum2(s1, s2, smem);
+    const float invD = 1.f / static_cast<float>(D);
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int64_t p = static_cast<int64_t>(c) * blockDim.x + threadIdx.x;
+      if (p < npack) {
+        Pack<T> out;
+#pragma unroll
+        for (int k = 0; k < N; ++k) out.v[k] = from_f<T>(rs * (gy[c][k] - s1 * invD - xh[c][k] * s2 * invD));
+        store_pack(dx + r * D + p * N, out);
+      }
+    }
+  }
+  if (partial) {
+    float* pw_ = partial + static_cast<int64_t>(blockIdx.x) * 2 * D;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int64_t p = static_cast<int64_t>(c) * blockDim.x + threadIdx.x;
+      if (p < npack) {
+#pragma unroll
+        for (int k = 0; k < N; ++k) { pw_[p * N + k] = dw_acc[c][k]; pw_[D + p * N + k] = db_acc[c][k]; }
+      }
+    }
+  }
+}
+
+// Column sums of the per-block partials: block (32, 8), one 32-column strip per block.
+template <class T>
+__global__ void layernorm_bwd_finalize_fast(const float* __restrict__ partial, T* __restrict__ dw, T* __restrict__ db,
+                                            int nblocks, int64_t D) {
+  __shared__ float ta[8][33], tb[8][33];
+  const int64_t j = static_cast<int64_t>(blockIdx.x) * 32 + threadIdx.x;
+  float a = 0.f, b = 0.f;
+  if (j < D) {
+    for (int i = threadIdx.y; i < nblocks; i += 8) {
+      a += partial[static_cast<int64_t>(i) * 2 * D + j];
+      b += partial[static_cast<int64_t>(i) * 2 * D + D + j];
+    }
+  }
+  ta[threadIdx.y][threadIdx.x] = a;
+  tb[threadIdx.y][threadIdx.x] = b;
+  __syncthreads();
+  if (threadIdx.y == 0 && j < D) {
+    float sa = 0.f, sb = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { sa += ta[i][threadIdx.x]; sb += tb[i][threadIdx.x]; }
+    if (dw) dw[j] = from_f<T>(sa);
+    if (db) db[j] = from_f<T>(sb);
+  }
+}
+
+template <class T>
+bool ln_fast_ok(const OpCall& c, int64_t D, int* threads, int* chunks) {
+  constexpr int N = Pack<T>::N;
+  if (D % N != 0) return false;
+  const int64_t npack = D / N;
+  if (npack > 256 * 4) return false;
+  for (int i = 0; i < 5; ++i)
+    if (c.in[i].defined() && !aligned16(c.in[i].data())) return false;
+  if (!aligned16(c.out[0].data())) return false;
+  int ch = static_cast<int>((npack + 255) / 256);
+  if (ch == 3) ch = 4;
+  int th = static_cast<int>((npack + ch - 1) / ch);
+  th = ((th + 31) / 32) * 32;
+  *threads = th;
+  *chunks = ch;
+  return true;
+}
+
 template <class T>
 void k_layernorm(OpCall& c) {
   const Tensor& x = c.in[0];
   const int64_t R = x.shape()[0], D = x.shape()[1];
   if (R > 2147483647LL) throw std::invalid_argument("layer_norm: too many rows");
+  const T* fw = c.in[1].defined() ? c.in[1].data_as<T>() : nullptr;
+  const T* fb = c.in[2].defined() ? c.in[2].data_as<T>() : nullptr;
+  int fth = 0, fch = 0;
+  if (ln_fast_ok<T>(c, D, &fth, &fch)) {
+    cudaStream_t st = stream_of(c);
+    float* pm = c.out[1].data_as<float>();
+    float* pr = c.out[2].data_as<float>();
+    const float eps = static_cast<float>(c.f[0]);
+    if (fch == 1) layernorm_fwd_fast<T, 1><<<static_cast<unsigned>(R), fth, 0, st>>>(x.data_as<T>(), fw, fb, c.out[0].data_as<T>(), pm, pr, D, eps);
+    else if (fch == 2) layernorm_fwd_fast<T, 2><<<static_cast<unsigned>(R), fth, 0, st>>>(x.data_as<T>(), fw, fb, c.out[0].data_as<T>(), pm, pr, D, eps);
+    else layernorm_fwd_fast<T, 4><<<static_cast<unsigned>(R), fth, 0, st>>>(x.data_as<T>(), fw, fb, c.out[0].data_as<T>(), pm, pr, D, eps);
+    check_launch("layer_norm");
+    return;
+  }
   const int per = Pack<T>::N;
   int threads = static_cast<int>(std::min<int64_t>(256, std::max<int64_t>(32, ((D / per + 31) / 32) * 32)));
   layernorm_fwd_kernel<T><<<static_cast<unsigned>(R), threads, 0, stream_of(c)>>>(
@@ -535,6 +730,22 @@ void k_layernorm_bwd(OpCall& c) {
     partial = static_cast<float*>(lease.data());
   }
   const T* pw = c.in[1].defined() ? c.in[1].data_as<T>() : nullptr;
+  int fth = 0, fch = 0;
+  if (ln_fast_ok<T>(c, D, &fth, &fch)) {
+    const T* px = x.data_as<T>();
+    const T* pg = c.in[2].data_as<T>();
+    const float* pmn = c.in[3].data_as<float>();
+    const float* prs = c.in[4].data_as<float>();
+    T* pdx = c.out[0].data_as<T>();
+    if (fch == 1) layernorm_bwd_fast<T, 1><<<nblocks, fth, 0, st>>>(px, pw, pg, pmn, prs, pdx, partial, R, D);
+    else if (fch == 2) layernorm_bwd_fast<T, 2><<<nblocks, fth, 0, st>>>(px, pw, pg, pmn, prs, pdx, partial, R, D);
+    else layernorm_bwd_fast<T, 4><<<nblocks, fth, 0, st>>>(px, pw, pg, pmn, prs, pdx, partial, R, D);
+    if (need_params)
+      layernorm_bwd_finalize_fast<T><<<static_cast<unsigned>((D + 31) / 32), dim3(32, 8), 0, st>>>(
+          partial, c.out[1].defined() ? c.out[1].data_as<T>() : nullptr, c.out[2].defined() ? c.out[2].data_as<T>() : nullptr, nblocks, D);
+    check_launch("layer_norm backward");
+    return;
+  }
   const int cols = static_cast<int>((D + threads - 1) / threads);
 #define LN_BWD(MAXC)                                                                                          \
   layernorm_bwd_kernel<T, MAXC><<<nblocks, threads, 0, st>>>(x.data_as<T>(), pw, c.in[2].data_as<T>(),           \

@@ -69,6 +69,8 @@ Tensor mean(const Tensor& a, std::optional<int> dim, bool keepdim);
 std::pair<Tensor, Tensor> max(const Tensor& a, std::optional<int> dim, bool keepdim);  // values, int64 indices
 Tensor argmax(const Tensor& a, std::optional<int> dim, bool keepdim);
 bool isfinite_all(const Tensor& a);
+// Sets flag[0] = 1 (int32, same device) when `a` holds a non-finite value; no host sync.
+void isfinite_into(const Tensor& a, Tensor& flag);
 
 // ---- linear algebra
 Tensor matmul(const Tensor& a, const Tensor& b);

@@ -724,6 +724,16 @@ Tensor argmax(const Tensor& a, std::optional<int> dim, bool keepdim) {
   return max(a, dim, keepdim).second;
 }
 
+void isfinite_into(const Tensor& a, Tensor& flag) {
+  if (flag.dtype() != DType::I32 || flag.numel() != 1 || flag.device() != a.device())
+    throw std::invalid_argument("isfinite_into: flag must be a one-element int32 tensor on the same device");
+  if (a.numel() == 0) return;
+  OpCall c;
+  c.in[0] = a;
+  c.in[1] = flag;
+  run_kernel(OperatorId::IsFiniteAll, a.device(), a.dtype(), c, layout_of(a));
+}
+
 bool isfinite_all(const Tensor& a) {
   if (a.numel() == 0) return true;
   OpCall c;

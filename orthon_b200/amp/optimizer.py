@@ -81,8 +81,25 @@ class MixedPrecisionOptimizer:
         from ..optim import SGD, Adam
         from ..optim.adam import _Moments
         from ..parallel.peer_reducer import PeerReducer
+        from ..parallel.peer_reducer import LocalFlatReducer
+        if optimizer_cls not in (Adam, SGD) or not params:
+            return False
         reducer = getattr(model, "_reducer", None)
-        if not isinstance(reducer, PeerReducer) or optimizer_cls not in (Adam, SGD):
+        if reducer is None and not hasattr(model, "_reducer"):
+            # Plain module on one GPU: flat local buckets, same fused update schedule.
+            named = [(n, p) for n, p in sorted(model.named_parameters(), key=lambda e: e[0])] if hasattr(model, "named_parameters") \
+                else [(str(i), p) for i, p in enumerate(params)]
+            seen, owners = set(), []
+            for n, p in named:
+                if id(p) not in seen:
+                    seen.add(id(p))
+                    owners.append((n, p))
+            if any(not p.requires_grad for _, p in owners) or not LocalFlatReducer.eligible(owners):
+                return False
+            reducer = LocalFlatReducer(owners)
+            for _, p in owners:
+                p._register_post_accumulate_grad_hook(lambda r=reducer, k=id(p): r.mark(k))
+        if not isinstance(reducer, PeerReducer):
             return False
         if {id(p) for p in params} != {id(p) for _, p in reducer.parameters}:
             return False  # frozen parameters: keep the general path

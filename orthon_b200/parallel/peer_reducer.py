@@ -30,7 +30,7 @@ def _align(n, a):
 
 class _Bucket:
     __slots__ = ("entries", "offsets", "n", "dtype", "grads", "staging", "flags", "grad_flat", "ready", "launched",
-                 "param_flat", "master_flat", "m_flat", "v_flat", "seg")
+                 "param_flat", "master_flat", "m_flat", "v_flat", "seg", "seg_host")
 
 
 class PeerReducer:
@@ -234,3 +234,130 @@ class PeerReducer:
                 else:
                     _C._sgd_step_(b.master_flat, b.grad_flat, model, hyper["lr"], hyper.get("weight_decay", 0.0),
                                   hyper.get("grad_scale", 1.0))
+
+
+class LocalFlatReducer(PeerReducer):
+    """Single-process sibling of PeerReducer: the same flat gradient / parameter / master /
+    moment buckets and the same hook-driven schedule, without peers.  In update mode each
+    bucket's fused optimizer kernel is queued as soon as the bucket's last gradient has been
+    written, so the update of late layers overlaps the backward of early layers."""
+
+    def __init__(self, parameters, bucket_size_mb=None):
+        self.parameters = tuple(parameters)
+        self.group, self.backend = None, None
+        self.overlap = True
+        first = self.parameters[0][1]
+        self.world, self.rank, self.device = 1, 0, first.device.index
+        self.dev = f"cuda:{self.device}"
+        self.mode, self.hyper, self.on_first_launch = "average", None, None
+        self.launch_count, self._step_open, self._bucket_of = 0, False, {}
+        self.buckets = []
+        self._flag = _C._zeros_on([1], "int32", self.dev)
+        for entries in make_buckets(self.parameters, 25 if bucket_size_mb is None else bucket_size_mb):
+            b = _Bucket()
+            b.entries, b.offsets, off = entries, [], 0
+            for _, p in entries:
+                b.offsets.append(off)
+                off = _align(off + int(p.numel), 8)
+            b.n, b.dtype, b.ready, b.launched = off, first.dtype, 0, False
+            b.param_flat = b.master_flat = b.m_flat = b.v_flat = b.seg = None
+            b.grads = b.staging = b.flags = None
+            b.grad_flat = _C._zeros_on([b.n], first.dtype, self.dev)
+            for (name, p), o in zip(b.entries, b.offsets):
+                p._set_grad_slot(_C._view_flat(b.grad_flat, o, list(p.shape)))
+                self._bucket_of[id(p)] = len(self.buckets)
+            self.buckets.append(b)
+
+    @staticmethod
+    def eligible(parameters):
+        if not parameters:
+            return False
+        first = parameters[0][1]
+        return all(p.device.is_cuda() and p.device == first.device and p.dtype == first.dtype and p.is_contiguous
+                   and p.dtype in ("float32", "float16", "bfloat16") for _, p in parameters)
+
+    def _launch(self, i):
+        b = self.buckets[i]
+        if not self._step_open:
+            self._step_open = True
+            if self.on_first_launch is not None:
+                self.on_first_launch()
+        if self.mode != "average":
+            if b.seg is not None:
+                raise RuntimeError("per-parameter weight decay needs fused='reduce' on a single device")
+            self._update_bucket(b, self.mode, self.hyper())
+        b.launched = True
+        self.launch_count += 1
+
+    def _update_bucket(self, b, kind, h):
+        model = b.param_flat if b.master_flat is not b.param_flat else None
+        with _no_grad():
+            if kind == "adam":
+                _C._adam_step_(b.master_flat, b.m_flat, b.v_flat, b.grad_flat, model, h["lr"], h["beta1"], h["beta2"], h["eps"],
+                               h.get("weight_decay", 0.0), h["bias_c1"], h["bias_c2"], h.get("grad_scale", 1.0))
+            else:
+                _C._sgd_step_(b.master_flat, b.grad_flat, model, h["lr"], h.get("weight_decay", 0.0), h.get("grad_scale", 1.0))
+
+    def synchronize(self):
+        with _no_grad():
+            for i, b in enumerate(self.buckets):
+                if b.launched:
+                    continue
+                for (name, p), off in zip(b.entries, b.offsets):
+                    g = p.grad
+                    slot = _C._view_flat(b.grad_flat, off, list(p.shape))
+                    if g is None:
+                        if self.mode != "average":
+                            raise RuntimeError(f"fused optimizer update needs a gradient for every parameter; '{name}' has none")
+                        slot.fill_(0.0)
+                        p.set_grad(slot)
+                    elif g._data_ptr != slot._data_ptr:
+                        slot._copy_data_(g)
+                        p.set_grad(slot)
+                self._launch(i)
+        for b in self.buckets:
+            b.ready, b.launched = 0, False
+        self._step_open = False
+
+    def wait(self):
+        return None
+
+    def found_inf(self, clear=True):
+        for b in self.buckets:
+            _C._isfinite_into(b.grad_flat, self._flag)
+        hit = bool(self._flag.tolist()[0])
+        if hit and clear:
+            self._flag.fill_(0.0)
+        return hit
+
+    def local_update(self, kind, hyper):
+        for b in self.buckets:
+            if b.seg is not None:
+                # Weight decay differs per parameter: update parameter by parameter inside the bucket.
+                self._update_segments(b, kind, hyper)
+            else:
+                self._update_bucket(b, kind, hyper)
+
+    def _update_segments(self, b, kind, h):
+        ends, wds = b.seg_host
+        start = 0
+        with _no_grad():
+            for end, wd in zip(ends, wds):
+                n = end - start
+                sl = lambda t: None if t is None else _C._view_flat(t, start, [n])  # noqa: E731
+                model = sl(b.param_flat) if b.master_flat is not b.param_flat else None
+                if kind == "adam":
+                    _C._adam_step_(sl(b.master_flat), sl(b.m_flat), sl(b.v_flat), sl(b.grad_flat), model, h["lr"], h["beta1"],
+                                   h["beta2"], h["eps"], wd, h["bias_c1"], h["bias_c2"], h.get("grad_scale", 1.0))
+                else:
+                    _C._sgd_step_(sl(b.master_flat), sl(b.grad_flat), model, h["lr"], wd, h.get("grad_scale", 1.0))
+                start = end
+
+    def set_decay_segments(self, decay_of):
+        for b in self.buckets:
+            ends, wds = [], []
+            for i, ((name, p), off) in enumerate(zip(b.entries, b.offsets)):
+                ends.append(b.offsets[i + 1] if i + 1 < len(b.offsets) else b.n)
+                wds.append(float(decay_of(p)))
+            b.seg = (ends, wds) if any(w != 0.0 for w in wds) else None
+            b.seg_host = (ends, wds)
