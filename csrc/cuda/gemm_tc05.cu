@@ -25,7 +25,9 @@
 // routes), :138-400 (16x16 SIMT tiles), src/backends/cuda/fusion_kernels.cu:42-86.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
+#include <string>
 
 #include "ob/cuda_common.cuh"
 #include "ob/ops.h"
@@ -81,6 +83,13 @@ __device__ __forceinline__ void tma_load_4d(void* smem, const CUtensorMap* map, 
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
       ::"r"(smem_u32(smem)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
+}
+
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void* smem, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(map), "r"(smem_u32(smem)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
@@ -145,6 +154,9 @@ struct GemmParams {
   int M, N, K;
   int nb0, nb1;                 // batch extents (outer, inner)
   int a_mn, b_mn;               // operand majors (0 = K-major, 1 = MN-major)
+  int a_bc, b_bc;               // 1 = operand is shared by every batch entry (batch stride 0)
+  int bias_rows;                // 1 = bias is indexed by output row instead of column
+  int tma_store;                // 1 = epilogue stages tiles in shared memory and stores them with TMA
   void* C; long long ldc, c_bs0, c_bs1;
   const void* bias;             // [N] or null
   const void* residual; long long ldr, r_bs0, r_bs1;
@@ -160,7 +172,8 @@ struct SmemLayout {
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // +1024 for manual alignment
+  static constexpr int kEpiBytes = kEpilogueWarps * 2 * 4096;  // two 32x64 staging tiles per epilogue warp
+  static constexpr int kTotal = kStages * kStageBytes + kEpiBytes + kBarrierBytes + 1024;  // +1024 for manual alignment
 };
 
 __device__ __forceinline__ float apply_act(float v, int act) {
@@ -171,11 +184,13 @@ __device__ __forceinline__ float apply_act(float v, int act) {
 
 template <class T, int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_z, GemmParams p) {
   using L = SmemLayout<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kStages * L::kStageBytes);
+  uint8_t* epi_smem = smem + L::kStages * L::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_smem + L::kEpiBytes);
   uint64_t* empty_bar = full_bar + L::kStages;
   uint64_t* tmem_full = empty_bar + L::kStages;
   uint64_t* tmem_empty = tmem_full + 2;
@@ -223,6 +238,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         int bidx, tm, tn;
         decode_tile(t, bidx, tm, tn);
         const int b0 = bidx / p.nb1, b1 = bidx - b0 * p.nb1;
+        const int a0 = p.a_bc ? 0 : b0, a1 = p.a_bc ? 0 : b1, c0 = p.b_bc ? 0 : b0, c1 = p.b_bc ? 0 : b1;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.err, kErrProducer)) { ok = false; break; }
           mbar_expect_tx(&full_bar[stage], L::kStageBytes);
@@ -230,16 +246,16 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           uint8_t* sb = sa + L::kABytes;
           const int k0 = kb * BK;
           if (!p.a_mn) {
-            tma_load_4d(sa, &map_a, &full_bar[stage], k0, tm * BM, b1, b0);
+            tma_load_4d(sa, &map_a, &full_bar[stage], k0, tm * BM, a1, a0);
           } else {
 #pragma unroll
-            for (int c = 0; c < BM / 64; ++c) tma_load_4d(sa + c * (BK * 128), &map_a, &full_bar[stage], tm * BM + c * 64, k0, b1, b0);
+            for (int c = 0; c < BM / 64; ++c) tma_load_4d(sa + c * (BK * 128), &map_a, &full_bar[stage], tm * BM + c * 64, k0, a1, a0);
           }
           if (!p.b_mn) {
-            tma_load_4d(sb, &map_b, &full_bar[stage], k0, tn * BN, b1, b0);
+            tma_load_4d(sb, &map_b, &full_bar[stage], k0, tn * BN, c1, c0);
           } else {
 #pragma unroll
-            for (int c = 0; c < BN / 64; ++c) tma_load_4d(sb + c * (BK * 128), &map_b, &full_bar[stage], tn * BN + c * 64, k0, b1, b0);
+            for (int c = 0; c < BN / 64; ++c) tma_load_4d(sb + c * (BK * 128), &map_b, &full_bar[stage], tn * BN + c * 64, k0, c1, c0);
           }
           if (++stage == L::kStages) { stage = 0; phase ^= 1; }
         }
@@ -293,6 +309,16 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         (!Rb || ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(Rb) & 15u) == 0) && (p.r_bs0 % 8 == 0) && (p.r_bs1 % 8 == 0))) &&
                         (!Zb || ((reinterpret_cast<uintptr_t>(Zb) & 15u) == 0)) &&
                         (!bias || ((reinterpret_cast<uintptr_t>(bias) & 15u) == 0));
+    // One loop body for every output mode keeps the epilogue code small enough to stay resident
+    // in the instruction cache next to the producer and MMA loops.  Per 32-column slice: load the
+    // accumulators, add bias, optionally write the pre-activation, activate, add the residual,
+    // write the result.  Writing is either (a) staged: each lane puts its row into a swizzled
+    // 32x64 shared-memory tile that one TMA store moves out as full 128-byte lines (edges clipped
+    // by the tensor map), or (b) direct 16-byte / scalar stores when the output is not TMA-friendly.
+    const bool staged = p.tma_store != 0;
+    const bool vec = staged || (vec_ok && (p.N % 8 == 0));
+    uint8_t* ebuf = epi_smem + (warp - 2) * 8192;
+    int buf = 0;
     for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
       int bidx, tm, tn;
       decode_tile(t, bidx, tm, tn);
@@ -300,60 +326,117 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int acc = it & 1;
       if (!mbar_wait(&tmem_full[acc], (it >> 1) & 1, p.err, kErrEpilogue)) { ok = false; break; }
       tc_fence_after();
-      const int row = tm * BM + quarter * 32 + lane;
+      const int row0 = tm * BM + quarter * 32;
+      const int row = row0 + lane;
+      const bool row_ok = row < p.M;
       const long long c_off = b0 * p.c_bs0 + b1 * p.c_bs1 + static_cast<long long>(row) * p.ldc;
       const long long r_off = b0 * p.r_bs0 + b1 * p.r_bs1 + static_cast<long long>(row) * p.ldr;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      const float bias_row = (bias && p.bias_rows && row_ok) ? to_f(bias[row]) : 0.f;
 #pragma unroll 1
-      for (int ch = 0; ch < BN / 32; ++ch) {
-        const int col0 = tn * BN + ch * 32;
+      for (int sub = 0; sub < BN / 32; ++sub) {
+        const int col0 = tn * BN + sub * 32;
         if (col0 >= p.N) break;  // uniform across the warp
         float v[32];
-        tmem_ld32(taddr + ch * 32, v);
-        if (row < p.M) {
-          const bool full = vec_ok && (col0 + 32 <= p.N);
-          if (full) {
+        tmem_ld32(taddr + sub * 32, v);
+        if (row0 >= p.M) continue;  // uniform: none of this warp's rows exist
+        const int half = sub & 1;
+        if (staged && half == 0) {
+          // The tile about to be overwritten must have been read by its previous store.
+          if (lane == 0) {
+            if (Zb) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          }
+          __syncwarp();
+        }
+        auto emit = [&](T* base, uint8_t* tile, bool is_z) {
+          if (staged) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              if (bias) {
+              Pack<T> pk;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) pk.v[j] = from_f<T>(v[q * 8 + j]);
+              *reinterpret_cast<uint4*>(tile + lane * 128 + (((half * 4 + q) ^ (lane & 7)) << 4)) = *reinterpret_cast<uint4*>(&pk);
+            }
+            if (half == 1 || col0 + 32 >= p.N) {
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+              __syncwarp();
+              if (lane == 0) {
+                if (is_z) tma_store_4d(&map_z, tile, col0 - half * 32, row0, b1, b0);
+                else tma_store_4d(&map_c, tile, col0 - half * 32, row0, b1, b0);
+              }
+            }
+          } else if (row_ok) {
+            if (vec) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                if (col0 + q * 8 < p.N) {
+                  Pack<T> pk;
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) pk.v[j] = from_f<T>(v[q * 8 + j]);
+                  store_pack(base + c_off + col0 + q * 8, pk);
+                }
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) base[c_off + col0 + j] = from_f<T>(v[j]);
+            }
+          }
+        };
+        if (bias) {
+          if (p.bias_rows) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += bias_row;
+          } else if (vec) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (col0 + q * 8 < p.N) {
                 Pack<T> pb = load_pack(bias + col0 + q * 8);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) v[q * 8 + j] += to_f(pb.v[j]);
               }
-              if (Zb) {
-                Pack<T> pz;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) pz.v[j] = from_f<T>(v[q * 8 + j]);
-                store_pack(Zb + c_off + col0 + q * 8, pz);
-              }
-              Pack<T> po;
-              if (Rb) {
-                Pack<T> pr = load_pack(Rb + r_off + col0 + q * 8);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) po.v[j] = from_f<T>(apply_act(v[q * 8 + j], p.act) + to_f(pr.v[j]));
-              } else {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) po.v[j] = from_f<T>(apply_act(v[q * 8 + j], p.act));
-              }
-              store_pack(Cb + c_off + col0 + q * 8, po);
             }
           } else {
-            for (int j = 0; j < 32; ++j) {
-              const int col = col0 + j;
-              if (col >= p.N) break;
-              float x = v[j];
-              if (bias) x += to_f(bias[col]);
-              if (Zb) Zb[c_off + col] = from_f<T>(x);
-              x = apply_act(x, p.act);
-              if (Rb) x += to_f(Rb[r_off + col]);
-              Cb[c_off + col] = from_f<T>(x);
-            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) v[j] += to_f(bias[col0 + j]);
           }
         }
+        if (Zb) emit(Zb, ebuf, true);
+        if (p.act == 1) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
+        } else if (p.act == 2) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.5f * v[j] * (1.f + erff(v[j] * 0.70710678118654752f));
+        }
+        if (Rb && row_ok) {
+          if (vec) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (col0 + q * 8 < p.N) {
+                Pack<T> pr = load_pack(Rb + r_off + col0 + q * 8);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[q * 8 + j] += to_f(pr.v[j]);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) v[j] += to_f(Rb[r_off + col0 + j]);
+          }
+        }
+        emit(Cb, Zb ? ebuf + 4096 : ebuf + buf * 4096, false);
+        if (staged && !Zb && (half == 1 || col0 + 32 >= p.N)) buf ^= 1;
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+    }
+    if (staged) {
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      __syncwarp();
     }
   }
 
@@ -369,7 +452,7 @@ __global__ void gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ 
                                  long long a_sm, long long a_sk, long long b_sk, long long b_sn, long long ldc,
                                  int nb1, long long a_bs0, long long a_bs1, long long b_bs0, long long b_bs1,
                                  long long c_bs0, long long c_bs1, const T* __restrict__ bias, const T* __restrict__ residual,
-                                 long long ldr, long long r_bs0, long long r_bs1, T* __restrict__ preact, int act) {
+                                 long long ldr, long long r_bs0, long long r_bs1, T* __restrict__ preact, int act, int bias_rows) {
   __shared__ float As[16][64 + 1];
   __shared__ float Bs[16][64 + 1];
   const int b0 = blockIdx.z / nb1, b1 = blockIdx.z % nb1;
@@ -409,7 +492,7 @@ __global__ void gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ 
       const int gm = m0 + ty * 4 + i, gn = n0 + tx * 4 + j;
       if (gm < M && gn < N) {
         float x = acc[i][j];
-        if (bias) x += to_f(bias[gn]);
+        if (bias) x += to_f(bias[bias_rows ? gm : gn]);
         if (preact) preact[c_base + gm * ldc + gn] = from_f<T>(x);
         x = apply_act(x, act);
         if (residual) x += to_f(residual[r_base + gm * ldr + gn]);
@@ -439,6 +522,7 @@ EncodeFn encode_fn() {
 struct OperandView {
   const void* ptr;
   long long mn, k, s_mn, s_k, bs0, bs1;
+  bool bcast;  // every batch entry reads the same matrix
 };
 
 bool tma_compatible(const OperandView& o, int nb0, int nb1) {
@@ -448,6 +532,7 @@ bool tma_compatible(const OperandView& o, int nb0, int nb1) {
   if (!k_major && !mn_major) return false;
   const long long other = (o.s_k == 1 || (o.k == 1 && o.s_mn != 1)) ? o.s_mn : o.s_k;
   if (other % 8 != 0 || other <= 0) return false;
+  if (o.bcast) return true;
   if (nb1 > 1 && (o.bs1 % 8 != 0 || o.bs1 <= 0)) return false;
   if (nb0 > 1 && (o.bs0 % 8 != 0 || o.bs0 <= 0)) return false;
   return true;
@@ -460,6 +545,7 @@ CUtensorMap make_map(const OperandView& o, bool mn_major, int box_rows, int nb0,
   const cuuint64_t inner = mn_major ? o.mn : o.k;
   const cuuint64_t rows = mn_major ? o.k : o.mn;
   const long long row_stride = mn_major ? o.s_k : o.s_mn;
+  if (o.bcast) { nb0 = 1; nb1 = 1; }
   cuuint64_t dims[4] = {inner, rows, static_cast<cuuint64_t>(nb1), static_cast<cuuint64_t>(nb0)};
   // Strides of unit dims still have to be valid multiples of 16 bytes.
   const long long rs = rows > 1 ? row_stride : static_cast<long long>((inner + 7) / 8 * 8);
@@ -491,6 +577,7 @@ int* error_flag(int device) {
 struct Epilogue {
   Tensor bias, residual, preact;
   int act = 0;
+  bool bias_rows = false;
 };
 
 template <class T>
@@ -502,7 +589,7 @@ void launch_simt(const OperandView& a, const OperandView& b, Tensor& C, int M, i
       static_cast<const T*>(a.ptr), static_cast<const T*>(b.ptr), C.data_as<T>(), M, N, K, a.s_mn, a.s_k, b.s_k, b.s_mn, ldc,
       nb1, a.bs0, a.bs1, b.bs0, b.bs1, c_bs0, c_bs1, ep.bias.defined() ? ep.bias.data_as<T>() : nullptr,
       ep.residual.defined() ? ep.residual.data_as<T>() : nullptr, ldr, c_bs0, c_bs1,
-      ep.preact.defined() ? ep.preact.data_as<T>() : nullptr, ep.act);
+      ep.preact.defined() ? ep.preact.data_as<T>() : nullptr, ep.act, ep.bias_rows ? 1 : 0);
   check_launch("gemm (SIMT)");
 }
 
@@ -515,6 +602,7 @@ void launch_tc05(const OperandView& a, const OperandView& b, bool a_mn, bool b_m
   const CUtensorMap mb = make_map(b, b_mn, BN, nb0, nb1, dt);
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.nb0 = nb0; p.nb1 = nb1; p.a_mn = a_mn; p.b_mn = b_mn;
+  p.a_bc = a.bcast ? 1 : 0; p.b_bc = b.bcast ? 1 : 0; p.bias_rows = ep.bias_rows ? 1 : 0;
   p.C = C.data(); p.ldc = ldc; p.c_bs0 = c_bs0; p.c_bs1 = c_bs1;
   p.bias = ep.bias.defined() ? ep.bias.data() : nullptr;
   p.residual = ep.residual.defined() ? ep.residual.data() : nullptr;
@@ -522,13 +610,36 @@ void launch_tc05(const OperandView& a, const OperandView& b, bool a_mn, bool b_m
   p.preact = ep.preact.defined() ? ep.preact.data() : nullptr;
   p.act = ep.act;
   p.err = error_flag(C.device().index);
+  // Output tensor maps for the TMA-store epilogue (row-major [M, N] tiles of 64 x 32).
+  auto out_map = [&](void* ptr, CUtensorMap* out) {
+    if (ptr == nullptr || (reinterpret_cast<uintptr_t>(ptr) & 15u) || ldc % 8 != 0 || ldc < N || N % 8 != 0) return false;
+    if (nb1 > 1 && (c_bs1 % 8 != 0 || c_bs1 <= 0)) return false;
+    if (nb0 > 1 && (c_bs0 % 8 != 0 || c_bs0 <= 0)) return false;
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M), static_cast<cuuint64_t>(nb1), static_cast<cuuint64_t>(nb0)};
+    const long long s1 = nb1 > 1 ? c_bs1 : ldc * static_cast<long long>(M);
+    const long long s0 = nb0 > 1 ? c_bs0 : s1 * nb1;
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(ldc) * 2, static_cast<cuuint64_t>(s1) * 2, static_cast<cuuint64_t>(s0) * 2};
+    cuuint32_t box[4] = {64, 32, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    return encode_fn()(out, dt == DType::BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, ptr, dims,
+                       strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                       CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  };
+  CUtensorMap mc = ma, mz = ma;
+  static const bool direct_store = [] { const char* e = std::getenv("ORTHON_GEMM_STORE"); return e != nullptr && std::string(e) == "direct"; }();
+  bool tma_store = !direct_store && out_map(p.C, &mc);
+  if (tma_store && p.preact != nullptr) tma_store = out_map(p.preact, &mz);
+  if (tma_store && p.residual != nullptr &&
+      ((reinterpret_cast<uintptr_t>(p.residual) & 15u) || p.ldr % 8 != 0 || p.r_bs0 % 8 != 0 || p.r_bs1 % 8 != 0)) tma_store = false;
+  if (tma_store && p.bias != nullptr && (reinterpret_cast<uintptr_t>(p.bias) & 15u)) tma_store = false;
+  p.tma_store = tma_store ? 1 : 0;
   static std::once_flag once;
   std::call_once(once, [] {
     OB_CUDA(cudaFuncSetAttribute(gemm_tc05_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
   });
   const long long tiles = static_cast<long long>((M + BM - 1) / BM) * ((N + BN - 1) / BN) * nb0 * nb1;
   const int grid = static_cast<int>(std::min<long long>(tiles, sm_count_for(C)));
-  gemm_tc05_kernel<T, BN><<<grid, kGemmThreads, L::kTotal, st>>>(ma, mb, p);
+  gemm_tc05_kernel<T, BN><<<grid, kGemmThreads, L::kTotal, st>>>(ma, mb, mc, mz, p);
   check_launch("gemm_tc05");
 }
 
@@ -550,6 +661,7 @@ void gemm_dispatch(const Tensor& A_in, bool ta, const Tensor& B_in, bool tb, Ten
     else { o.k = lr; o.mn = lc; o.s_k = lrs; o.s_mn = lcs; }
     o.bs0 = nbd == 2 ? t.strides()[0] : 0;
     o.bs1 = nbd >= 1 ? t.strides()[nbd - 1] : 0;
+    o.bcast = nbd >= 1 && o.bs1 == 0 && (nbd < 2 || o.bs0 == 0) && (nb0 * nb1 > 1);
     return o;
   };
   OperandView a = view_of(A, ta, true), b = view_of(B, tb, false);
@@ -610,6 +722,15 @@ void k_linear(OpCall& c) {
 }
 
 }  // namespace
+
+// GEMM entry for other kernels of the backend (convolution lowers to it).
+void gemm_launch(const Tensor& A, bool ta, const Tensor& B, bool tb, Tensor& C, const Tensor& bias, bool bias_rows,
+                 cudaStream_t st) {
+  Epilogue ep;
+  ep.bias = bias;
+  ep.bias_rows = bias_rows;
+  gemm_dispatch(A, ta, B, tb, C, ep, st);
+}
 
 // Reads and clears the GEMM error word of a device (0 = no error).  Synchronizes the device.
 int take_gemm_error(int device) {
