@@ -34,7 +34,6 @@ def worker(rank, dtypes, max_mb, iters):
     dev = f"cuda:{dev_i}"
     max_bytes = max_mb << 20
     rows = []
-    nccl = _C._NcclGroup if False else None  # placeholder to keep linters quiet
     from orthon_b200.distributed.nccl_backend import NcclBackend
     nccl_be = NcclBackend(rank, ws, dev_i, be._store)
     for dtype in dtypes:

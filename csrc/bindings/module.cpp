@@ -463,6 +463,7 @@ PYBIND11_MODULE(_C, m) {
                                  seed.attr("__and__")(py::int_(0xFFFFFFFFFFFFFFFFull)).cast<uint64_t>());
   }, py::arg("qkv"), py::arg("heads"), py::arg("mask") = py::none(), py::arg("causal") = false, py::arg("scale") = 1.0,
      py::arg("dropout_p") = 0.0, py::arg("seed") = py::int_(0));
+  m.def("_attention_qkv_fused", [](const Tensor& qkv, int64_t heads) { return cu::flash_attention_supported(qkv, heads); });
   m.def("_gemm", &ops::gemm, py::arg("a"), py::arg("trans_a"), py::arg("b"), py::arg("trans_b"));
   m.def("isfinite_all", &ops::isfinite_all);
   m.def("_isfinite_into", [](const Tensor& t, Tensor& flag) { ops::isfinite_into(t, flag); });

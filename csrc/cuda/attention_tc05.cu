@@ -1,0 +1,884 @@
+// attention_tc05: fused multi-head self-attention on the 5th-generation tensor cores (sm_100a).
+//
+// Input is the packed projection qkv[B, T, 3E] (E = H*D, head h of q/k/v at columns
+// {0,E,2E} + h*D); heads are read in place through one rank-3 tensor map, nothing is split,
+// transposed or packed, and the [T, T] score matrix never exists in global memory.
+//
+//   forward : O = softmax(scale * Q K^T + causal mask) V, LSE[b,h,t] = log sum exp (natural log)
+//   backward: dQ, dK, dV from (qkv, O, LSE, dO) with the probabilities recomputed tile by tile
+//
+// Forward design (one CTA = one (batch, head) and 256 query rows, 320 threads):
+//   warp 0      TMA producer: Q (two 128-row tiles, once), then K_j / V_j tiles of 128 keys
+//   warp 1      one thread issues tcgen05.mma: S_w = Q_w K_j^T (TMEM, 128 fp32 columns per query
+//               tile) and O_w += P_w V_j (TMEM, D columns per query tile)
+//   warps 2-5   softmax group 0, warps 6-9 softmax group 1: one thread per query row reads its
+//               S row from TMEM, keeps the running max / sum (online softmax, base-2 exponent),
+//               rescales the O accumulator in TMEM when the max moved, writes P as bf16/f16 into
+//               128-byte-swizzled shared memory (the A operand of the second MMA)
+//   The two groups work on alternating MMAs (S_1 and P_0 V run while group 0 is in softmax and
+//   vice versa), so the tensor pipe and the exponent unit overlap.
+// Backward is two kernels so that every output element has exactly one writer (deterministic,
+// no atomics): one CTA per key tile accumulates dK and dV over query tiles; one CTA per query
+// tile accumulates dQ over key tiles.  Both recompute S and dP = dO V^T on the tensor cores.
+//
+// Every mbarrier wait is bounded (clock budget -> error word, unwind, TMEM released).
+//
+// Replaces (reference project paths): python/orthon/functional/math.py:39-72 (composed
+// matmul / log_softmax / exp / matmul attention) and python/orthon/nn/attention.py:84-103
+// (head split by reshape + transpose + contiguous).
+#include <cuda.h>
+
+#include <mutex>
+
+#include "ob/cuda_common.cuh"
+#include "ob/ops.h"
+#include "ob/tc05.cuh"
+
+namespace ob {
+namespace cu {
+
+int* tc05_error_flag(int device);
+bool tc05_encode_map(CUtensorMap* out, DType dt, int rank, void* base, const uint64_t* dims, const uint64_t* strides_bytes,
+                     const uint32_t* box);
+
+namespace {
+
+using namespace tc05;
+
+enum : int { kErrAttnProducer = 11, kErrAttnMma = 12, kErrAttnSoftmax = 13 };
+
+constexpr int kTile = 128;  // query rows per softmax group and keys per K/V tile
+
+struct FlashParams {
+  int B, H, T, E;
+  int causal;
+  float scale_log2;  // softmax scale * log2(e)
+  float scale;       // softmax scale
+  float* lse;        // [B, H, T]
+  const float* delta;  // [B, H, T] (backward): sum_d dO * O
+  int* err;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Packs 8 floats into 8 16-bit values (one 16-byte chunk).
+template <class T>
+__device__ __forceinline__ uint4 pack8(const float* v) {
+  Pack<T> p;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) p.v[j] = from_f<T>(v[j]);
+  return *reinterpret_cast<uint4*>(&p);
+}
+
+// ------------------------------------------------------------------ forward
+template <int D>
+struct FwdSmem {
+  static constexpr int kQBytes = kTile * D * 2;        // one query tile
+  static constexpr int kKVBytes = kTile * D * 2;       // one K or V tile
+  static constexpr int kPBytes = kTile * kTile * 2;    // one probability tile
+  static constexpr int kKStages = 2;
+  static constexpr int kVStages = (D == 128) ? 1 : 2;
+  static constexpr int kQOff = 0;
+  static constexpr int kKOff = kQOff + 2 * kQBytes;
+  static constexpr int kVOff = kKOff + kKStages * kKVBytes;
+  static constexpr int kPOff = kVOff + kVStages * kKVBytes;
+  static constexpr int kBarOff = kPOff + 2 * kPBytes;
+  static constexpr int kTotal = kBarOff + 256 + 1024;  // +1024 for manual alignment
+};
+
+constexpr int kFwdThreads = 320;
+
+template <class T, int D>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_o, FlashParams p) {
+  using L = FwdSmem<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* q_full = bars;                      // 1
+  uint64_t* k_full = q_full + 1;                // kKStages
+  uint64_t* k_empty = k_full + L::kKStages;
+  uint64_t* v_full = k_empty + L::kKStages;     // kVStages
+  uint64_t* v_empty = v_full + L::kVStages;
+  uint64_t* s_full = v_empty + L::kVStages;     // 2
+  uint64_t* p_full = s_full + 2;                // 2
+  uint64_t* o_done = p_full + 2;                // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.x, b = bh / p.H, h = bh - b * p.H;
+  const int n_pairs = gridDim.y;
+  const int pair = n_pairs - 1 - static_cast<int>(blockIdx.y);  // heaviest (latest rows) first
+  const int n_tiles = (p.T + kTile - 1) / kTile;
+  // Number of key tiles each query tile needs.
+  auto tiles_for = [&](int w) {
+    const int qt = 2 * pair + w;
+    return (qt >= n_tiles) ? 0 : (p.causal ? min(n_tiles, qt + 1) : n_tiles);
+  };
+  const int n_w0 = tiles_for(0), n_w1 = tiles_for(1);
+  const int n_kv = max(n_w0, n_w1);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < L::kKStages; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+    for (int s = 0; s < L::kVStages; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+    for (int w = 0; w < 2; ++w) { mbar_init(&s_full[w], 1); mbar_init(&p_full[w], 4); mbar_init(&o_done[w], 1); }
+    mbar_init_fence();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  auto tmem_s = [&](int w) { return tmem_base + static_cast<uint32_t>(w) * 128u; };
+  auto tmem_o = [&](int w) { return tmem_base + 256u + static_cast<uint32_t>(w) * D; };
+
+  const int col_q = h * D, col_k = p.E + h * D, col_v = 2 * p.E + h * D;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- TMA producer
+    if (lane == 0 && n_kv > 0) {
+      mbar_expect_tx(q_full, 2 * L::kQBytes);
+#pragma unroll
+      for (int w = 0; w < 2; ++w)
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_3d(smem + L::kQOff + w * L::kQBytes + c * (kTile * 128), &map_qkv, q_full, col_q + c * 64,
+                      (2 * pair + w) * kTile, b);
+      bool ok = true;
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int ks = j % L::kKStages, vs = j % L::kVStages;
+        if (!mbar_wait(&k_empty[ks], ((j / L::kKStages) & 1) ^ 1, p.err, kErrAttnProducer)) { ok = false; break; }
+        mbar_expect_tx(&k_full[ks], L::kKVBytes);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_3d(smem + L::kKOff + ks * L::kKVBytes + c * (kTile * 128), &map_qkv, &k_full[ks], col_k + c * 64, j * kTile, b);
+        if (!mbar_wait(&v_empty[vs], ((j / L::kVStages) & 1) ^ 1, p.err, kErrAttnProducer)) { ok = false; break; }
+        mbar_expect_tx(&v_full[vs], L::kKVBytes);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_3d(smem + L::kVOff + vs * L::kKVBytes + c * (kTile * 128), &map_qkv, &v_full[vs], col_v + c * 64, j * kTile, b);
+      }
+    }
+  } else if (warp == 1) {
+    // --------------------------------------------------------------- MMA issuer
+    if (lane == 0 && n_kv > 0) {
+      const bool bf = std::is_same<T, __nv_bfloat16>::value;
+      const uint32_t idesc_s = make_idesc(bf, 0, 0, kTile, kTile);  // S = Q K^T  (both K-major)
+      const uint32_t idesc_o = make_idesc(bf, 0, 1, kTile, D);      // O = P V    (V is MN-major)
+      auto issue_s = [&](int w, int ks) {
+        const uint32_t sq = smem_u32(smem + L::kQOff + w * L::kQBytes);
+        const uint32_t sk = smem_u32(smem + L::kKOff + ks * L::kKVBytes);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * (kTile * 128) + (kk % 4) * 32;
+          umma_f16(tmem_s(w), make_desc(sq + off, 16, 1024), make_desc(sk + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[w]);
+      };
+      auto issue_o = [&](int w, int vs, bool accumulate) {
+        const uint32_t sp = smem_u32(smem + L::kPOff + w * L::kPBytes);
+        const uint32_t sv = smem_u32(smem + L::kVOff + vs * L::kKVBytes);
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk) {
+          const uint32_t a_off = (kk / 4) * (kTile * 128) + (kk % 4) * 32;
+          umma_f16(tmem_o(w), make_desc(sp + a_off, 16, 1024), make_desc(sv + kk * 2048, kTile * 128, 1024), idesc_o,
+                   (accumulate || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&o_done[w]);
+      };
+      bool ok = mbar_wait(q_full, 0, p.err, kErrAttnMma);
+      if (ok) ok = mbar_wait(&k_full[0], 0, p.err, kErrAttnMma);
+      if (ok) {
+        tc_fence_after();
+        if (n_w0 > 0) issue_s(0, 0);
+        if (n_w1 > 0) issue_s(1, 0);
+        umma_commit(&k_empty[0]);
+      }
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int vs = j % L::kVStages, ks_next = (j + 1) % L::kKStages;
+        if (!mbar_wait(&v_full[vs], (j / L::kVStages) & 1, p.err, kErrAttnMma)) { ok = false; break; }
+        bool k_ready = false;
+        for (int w = 0; w < 2 && ok; ++w) {
+          const int n_w = w ? n_w1 : n_w0;
+          if (j < n_w) {
+            if (!mbar_wait(&p_full[w], j & 1, p.err, kErrAttnMma)) { ok = false; break; }
+            tc_fence_after();
+            issue_o(w, vs, j > 0);
+          }
+          if (j + 1 < n_w) {
+            if (!k_ready) {
+              if (!mbar_wait(&k_full[ks_next], ((j + 1) / L::kKStages) & 1, p.err, kErrAttnMma)) { ok = false; break; }
+              tc_fence_after();
+              k_ready = true;
+            }
+            issue_s(w, ks_next);  // P_w ready implies S_w has been read out
+          }
+        }
+        if (!ok) break;
+        umma_commit(&v_empty[vs]);
+        if (j + 1 < n_kv) umma_commit(&k_empty[ks_next]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax groups
+    const int w = (warp - 2) >> 2;        // query tile within the pair
+    const int quarter = warp & 3;         // TMEM lane quarter of this warp
+    const int r = quarter * 32 + lane;    // row within the query tile
+    const int q_row = (2 * pair + w) * kTile + r;
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    uint8_t* sp = smem + L::kPOff + w * L::kPBytes;
+    const int n_it = w ? n_w1 : n_w0;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_it && ok; ++j) {
+      if (!mbar_wait(&s_full[w], j & 1, p.err, kErrAttnSoftmax)) { ok = false; break; }
+      tc_fence_after();
+      float s[kTile];
+#pragma unroll
+      for (int c = 0; c < kTile / 32; ++c) tmem_ld32_nowait(tmem_s(w) + lane_off + c * 32, s + c * 32);
+      tmem_ld_wait();
+      // Mask: keys past the sequence end, and keys after the query on the diagonal tile.
+      const int key0 = j * kTile;
+      const bool diag = p.causal && (j == 2 * pair + w);
+      if (diag || key0 + kTile > p.T) {
+        const int limit = diag ? min(q_row, p.T - 1) : p.T - 1;  // last visible key
+#pragma unroll
+        for (int c = 0; c < kTile; ++c)
+          if (key0 + c > limit) s[c] = -INFINITY;
+      }
+      float mx = s[0];
+#pragma unroll
+      for (int c = 1; c < kTile; ++c) mx = fmaxf(mx, s[c]);
+      float m_new = fmaxf(m, mx * p.scale_log2);
+      if (m_new == -INFINITY) m_new = 0.f;  // fully masked row (only rows past the sequence end)
+      const float alpha = fast_exp2(m - m_new);
+      if (j > 0) {
+        // P_{j-1} V has finished: the O accumulator is consistent and the P tile is free.
+        if (!mbar_wait(&o_done[w], (j - 1) & 1, p.err, kErrAttnSoftmax)) { ok = false; break; }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, m_new > m)) {
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            float o[32];
+            tmem_ld32(tmem_o(w) + lane_off + c * 32, o);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] *= alpha;
+            tmem_st32(tmem_o(w) + lane_off + c * 32, o);
+          }
+          tmem_st_wait();
+        }
+      }
+      float sum = 0.f;
+#pragma unroll
+      for (int c8 = 0; c8 < kTile / 8; ++c8) {
+        float pv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          pv[i] = fast_exp2(fmaf(s[c8 * 8 + i], p.scale_log2, -m_new));
+          sum += pv[i];
+        }
+        *reinterpret_cast<uint4*>(sp + (c8 / 8) * (kTile * 128) + sw128_offset(r, c8 % 8)) = pack8<T>(pv);
+      }
+      l = l * alpha + sum;
+      m = m_new;
+      fence_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[w]);
+    }
+    if (ok && n_it > 0 && mbar_wait(&o_done[w], (n_it - 1) & 1, p.err, kErrAttnSoftmax)) {
+      tc_fence_after();
+      const float inv_l = 1.f / l;
+      // Stage this warp's 32 rows (the P tile is free now) and store them with TMA.
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        float o[32];
+        tmem_ld32(tmem_o(w) + lane_off + c * 32, o);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] *= inv_l;
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          *reinterpret_cast<uint4*>(sp + (c / 2) * (kTile * 128) + sw128_offset(r, (c % 2) * 4 + q)) = pack8<T>(o + q * 8);
+      }
+      fence_async_smem();
+      __syncwarp();
+      const int store_row = (2 * pair + w) * kTile + quarter * 32;
+      if (lane == 0 && store_row < p.T) {  // rows past the end of a partly covered box are clipped by TMA
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_store_3d(&map_o, sp + c * (kTile * 128) + quarter * 32 * 128, h * D + c * 64, store_row, b);
+        tma_store_wait_all();
+      }
+      if (q_row < p.T) p.lse[(static_cast<long long>(b) * p.H + h) * p.T + q_row] = (m + log2f(l)) * 0.6931471805599453f;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// ----------------------------------------------------------------- backward
+// delta[b, h, t] = sum_d dO[b, t, h*D + d] * O[b, t, h*D + d]; one warp per (b, t, h).
+template <class T>
+__global__ void attn_delta_kernel(const T* __restrict__ dout, const T* __restrict__ out, float* __restrict__ delta, int B, int Tn,
+                                  int H, int D) {
+  const long long warp_id = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(B) * Tn * H;
+  if (warp_id >= total) return;
+  const int h = static_cast<int>(warp_id % H);
+  const long long bt = warp_id / H;
+  const long long base = bt * static_cast<long long>(H) * D + static_cast<long long>(h) * D;
+  float acc = 0.f;
+  for (int d = lane * 2; d < D; d += 64) {
+    acc += to_f(dout[base + d]) * to_f(out[base + d]) + to_f(dout[base + d + 1]) * to_f(out[base + d + 1]);
+  }
+  acc = warp_sum(acc);
+  const long long b = bt / Tn, t = bt - b * Tn;
+  if (lane == 0) delta[(b * H + h) * Tn + t] = acc;
+}
+
+constexpr int kBwdThreads = 192;
+constexpr int kSub = 64;  // rows of the streamed operand per step (N of the score MMAs)
+
+// Shared-memory plan of both backward kernels: two resident [128 x D] tiles, a ring of streamed
+// [64 x D] tile pairs, two double-buffered [128 x 64] operand tiles written by the softmax warps.
+template <int D>
+struct BwdSmem {
+  static constexpr int kBigBytes = kTile * D * 2;   // resident tile
+  static constexpr int kSubBytes = kSub * D * 2;    // streamed tile
+  static constexpr int kOpBytes = kTile * kSub * 2; // operand tile written by the softmax warps
+  static constexpr int kStages = (D == 128) ? 2 : 3;
+  static constexpr int kBigOff = 0;                                   // two resident tiles
+  static constexpr int kRingOff = kBigOff + 2 * kBigBytes;            // kStages x (two streamed tiles)
+  static constexpr int kOpOff = kRingOff + kStages * 2 * kSubBytes;   // [2 buffers][2 tiles]
+  static constexpr int kVecOff = kOpOff + 4 * kOpBytes;               // per-warp lse/delta staging
+  static constexpr int kBarOff = kVecOff + 4 * 2 * 128 * 4;
+  static constexpr int kTotal = kBarOff + 256 + 1024;
+};
+
+// dK, dV: one CTA per (batch, head, 128-key tile); streams 64-row query tiles.
+//   S^T = K Q^T, dP^T = V dO^T (TMEM, 64 columns each, double buffered); one thread per key row
+//   turns them into P^T and dS^T (shared memory); dV += P^T dO, dK += dS^T Q (TMEM).
+template <class T, int D>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_constant__ CUtensorMap map_qkv64,
+                     const __grid_constant__ CUtensorMap map_do64, const __grid_constant__ CUtensorMap map_dqkv, FlashParams p) {
+  using L = BwdSmem<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* kv_full = bars;
+  uint64_t* ring_full = kv_full + 1;
+  uint64_t* ring_empty = ring_full + L::kStages;
+  uint64_t* sdp_full = ring_empty + L::kStages;  // 2
+  uint64_t* pds_full = sdp_full + 2;             // 2
+  uint64_t* pds_free = pds_full + 2;             // 2
+  uint64_t* acc_done = pds_free + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.x, b = bh / p.H, h = bh - b * p.H;
+  const int jt = blockIdx.y;                 // key tile (128 keys); tile 0 is the heaviest under the causal mask
+  const int key0 = jt * kTile;
+  const int n_sub = (p.T + kSub - 1) / kSub;  // query sub-tiles in the sequence
+  const int i0 = p.causal ? (key0 / kSub) : 0;
+  const int n_it = max(0, n_sub - i0);
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < L::kStages; ++s) { mbar_init(&ring_full[s], 1); mbar_init(&ring_empty[s], 1); }
+    for (int w = 0; w < 2; ++w) { mbar_init(&sdp_full[w], 1); mbar_init(&pds_full[w], 4); mbar_init(&pds_free[w], 1); }
+    mbar_init(acc_done, 1);
+    mbar_init_fence();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_dv = tmem_base + 256, tmem_dk = tmem_base + 256 + D;
+  const int col_q = h * D, col_k = p.E + h * D, col_v = 2 * p.E + h * D;
+  uint8_t* sk = smem + L::kBigOff;
+  uint8_t* sv = sk + L::kBigBytes;
+
+  if (warp == 0) {
+    if (lane == 0 && n_it > 0) {
+      mbar_expect_tx(kv_full, 2 * L::kBigBytes);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        tma_load_3d(sk + c * (kTile * 128), &map_qkv128, kv_full, col_k + c * 64, key0, b);
+        tma_load_3d(sv + c * (kTile * 128), &map_qkv128, kv_full, col_v + c * 64, key0, b);
+      }
+      for (int it = 0; it < n_it; ++it) {
+        const int st = it % L::kStages;
+        if (!mbar_wait(&ring_empty[st], ((it / L::kStages) & 1) ^ 1, p.err, kErrAttnProducer)) break;
+        mbar_expect_tx(&ring_full[st], 2 * L::kSubBytes);
+        uint8_t* sq = smem + L::kRingOff + st * 2 * L::kSubBytes;
+        uint8_t* sdo = sq + L::kSubBytes;
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          tma_load_3d(sq + c * (kSub * 128), &map_qkv64, &ring_full[st], col_q + c * 64, (i0 + it) * kSub, b);
+          tma_load_3d(sdo + c * (kSub * 128), &map_do64, &ring_full[st], col_q + c * 64, (i0 + it) * kSub, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_it > 0) {
+      const bool bf = std::is_same<T, __nv_bfloat16>::value;
+      const uint32_t idesc_s = make_idesc(bf, 0, 0, kTile, kSub);  // [128 keys x 64 queries], both K-major
+      const uint32_t idesc_a = make_idesc(bf, 0, 1, kTile, D);     // [128 keys x D], B operand MN-major
+      auto issue_scores = [&](int buf, int st) {
+        const uint32_t a_k = smem_u32(sk), a_v = smem_u32(sv);
+        const uint32_t b_q = smem_u32(smem + L::kRingOff + st * 2 * L::kSubBytes), b_do = b_q + L::kSubBytes;
+        const uint32_t d_s = tmem_base + buf * 128, d_dp = d_s + 64;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t a_off = (kk / 4) * (kTile * 128) + (kk % 4) * 32, b_off = (kk / 4) * (kSub * 128) + (kk % 4) * 32;
+          umma_f16(d_s, make_desc(a_k + a_off, 16, 1024), make_desc(b_q + b_off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t a_off = (kk / 4) * (kTile * 128) + (kk % 4) * 32, b_off = (kk / 4) * (kSub * 128) + (kk % 4) * 32;
+          umma_f16(d_dp, make_desc(a_v + a_off, 16, 1024), make_desc(b_do + b_off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&sdp_full[buf]);
+      };
+      bool ok = mbar_wait(kv_full, 0, p.err, kErrAttnMma) && mbar_wait(&ring_full[0], 0, p.err, kErrAttnMma);
+      if (ok) {
+        tc_fence_after();
+        issue_scores(0, 0);
+      }
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int st = it % L::kStages, buf = it & 1;
+        if (it + 1 < n_it) {
+          const int st1 = (it + 1) % L::kStages;
+          if (!mbar_wait(&ring_full[st1], ((it + 1) / L::kStages) & 1, p.err, kErrAttnMma)) { ok = false; break; }
+          tc_fence_after();
+          issue_scores((it + 1) & 1, st1);
+        }
+        if (!mbar_wait(&pds_full[buf], (it >> 1) & 1, p.err, kErrAttnMma)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t a_p = smem_u32(smem + L::kOpOff + buf * 2 * L::kOpBytes), a_ds = a_p + L::kOpBytes;
+        const uint32_t b_q = smem_u32(smem + L::kRingOff + st * 2 * L::kSubBytes), b_do = b_q + L::kSubBytes;
+#pragma unroll
+        for (int kk = 0; kk < kSub / 16; ++kk)
+          umma_f16(tmem_dv, make_desc(a_p + kk * 32, 16, 1024), make_desc(b_do + kk * 2048, kSub * 128, 1024), idesc_a,
+                   (it > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < kSub / 16; ++kk)
+          umma_f16(tmem_dk, make_desc(a_ds + kk * 32, 16, 1024), make_desc(b_q + kk * 2048, kSub * 128, 1024), idesc_a,
+                   (it > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&ring_empty[st]);
+        umma_commit(&pds_free[buf]);
+      }
+      if (ok) umma_commit(acc_done);
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;  // key row within the tile
+    const int key = key0 + r;
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    float* vec = reinterpret_cast<float*>(smem + L::kVecOff) + (warp - 2) * 256;  // [2 buffers][lse2 64 | delta 64]
+    const float* lse_row = p.lse + (static_cast<long long>(b) * p.H + h) * p.T;
+    const float* delta_row = p.delta + (static_cast<long long>(b) * p.H + h) * p.T;
+    bool ok = true;
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int buf = it & 1;
+      const int q0 = (i0 + it) * kSub;
+      float* vb = vec + buf * 128;
+      // Stage log2-scaled LSE and delta of the 64 queries; queries past the end get +inf (P = 0).
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int q = q0 + half * 32 + lane;
+        vb[half * 32 + lane] = q < p.T ? lse_row[q] * 1.4426950408889634f : INFINITY;
+        vb[64 + half * 32 + lane] = q < p.T ? delta_row[q] : 0.f;
+      }
+      __syncwarp();
+      if (!mbar_wait(&sdp_full[buf], (it >> 1) & 1, p.err, kErrAttnSoftmax)) { ok = false; break; }
+      tc_fence_after();
+      float s[kSub], dp[kSub];
+      tmem_ld32_nowait(tmem_base + buf * 128 + lane_off, s);
+      tmem_ld32_nowait(tmem_base + buf * 128 + lane_off + 32, s + 32);
+      tmem_ld32_nowait(tmem_base + buf * 128 + lane_off + 64, dp);
+      tmem_ld32_nowait(tmem_base + buf * 128 + lane_off + 96, dp + 32);
+      tmem_ld_wait();
+      if (!mbar_wait(&pds_free[buf], ((it >> 1) & 1) ^ 1, p.err, kErrAttnSoftmax)) { ok = false; break; }
+      uint8_t* sp = smem + L::kOpOff + buf * 2 * L::kOpBytes;
+      uint8_t* sds = sp + L::kOpBytes;
+      const bool key_ok = key < p.T;
+      const bool need_mask = p.causal && (q0 < key0 + kTile);
+#pragma unroll
+      for (int c8 = 0; c8 < kSub / 8; ++c8) {
+        const float4 l0 = *reinterpret_cast<const float4*>(vb + c8 * 8), l1 = *reinterpret_cast<const float4*>(vb + c8 * 8 + 4);
+        const float4 d0 = *reinterpret_cast<const float4*>(vb + 64 + c8 * 8), d1 = *reinterpret_cast<const float4*>(vb + 64 + c8 * 8 + 4);
+        const float l8[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+        const float d8[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+        float pv[8], dsv[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int c = c8 * 8 + e;
+          float pe = fast_exp2(fmaf(s[c], p.scale_log2, -l8[e]));
+          if (!key_ok || (need_mask && key > q0 + c)) pe = 0.f;
+          pv[e] = pe;
+          dsv[e] = pe * (dp[c] - d8[e]) * p.scale;
+        }
+        *reinterpret_cast<uint4*>(sp + sw128_offset(r, c8)) = pack8<T>(pv);
+        *reinterpret_cast<uint4*>(sds + sw128_offset(r, c8)) = pack8<T>(dsv);
+      }
+      fence_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&pds_full[buf]);
+    }
+    if (ok && n_it > 0 && mbar_wait(acc_done, 0, p.err, kErrAttnSoftmax)) {
+      tc_fence_after();
+      // dV then dK: stage this warp's 32 rows in the (now idle) V / K tiles and store them.
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        uint8_t* dst = which ? sk : sv;
+        const uint32_t src = which ? tmem_dk : tmem_dv;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          float o[32];
+          tmem_ld32(src + lane_off + c * 32, o);
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            *reinterpret_cast<uint4*>(dst + (c / 2) * (kTile * 128) + sw128_offset(r, (c % 2) * 4 + q)) = pack8<T>(o + q * 8);
+        }
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0 && key0 + quarter * 32 < p.T) {
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          tma_store_3d(&map_dqkv, sv + c * (kTile * 128) + quarter * 32 * 128, col_v + c * 64, key0 + quarter * 32, b);
+          tma_store_3d(&map_dqkv, sk + c * (kTile * 128) + quarter * 32 * 128, col_k + c * 64, key0 + quarter * 32, b);
+        }
+        tma_store_wait_all();
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// dQ: one CTA per (batch, head, 128-query tile); streams 64-key sub-tiles of K and V.
+//   S = Q K^T, dP = dO V^T (TMEM, 64 columns each, double buffered); one thread per query row
+//   writes dS = P (dP - delta) * scale to shared memory; dQ += dS K (TMEM).
+template <class T, int D>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_constant__ CUtensorMap map_qkv64,
+                    const __grid_constant__ CUtensorMap map_do64, const __grid_constant__ CUtensorMap map_dqkv, FlashParams p) {
+  using L = BwdSmem<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* q_full = bars;
+  uint64_t* ring_full = q_full + 1;
+  uint64_t* ring_empty = ring_full + L::kStages;
+  uint64_t* sdp_full = ring_empty + L::kStages;  // 2
+  uint64_t* ds_full = sdp_full + 2;              // 2
+  uint64_t* ds_free = ds_full + 2;               // 2
+  uint64_t* acc_done = ds_free + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.x, b = bh / p.H, h = bh - b * p.H;
+  const int n_tiles = gridDim.y;
+  const int qt = n_tiles - 1 - static_cast<int>(blockIdx.y);  // latest rows (most keys under the causal mask) first
+  const int row0 = qt * kTile;
+  const int last_q = min(p.T - 1, row0 + kTile - 1);
+  const int n_it = p.causal ? (last_q / kSub + 1) : (p.T + kSub - 1) / kSub;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < L::kStages; ++s) { mbar_init(&ring_full[s], 1); mbar_init(&ring_empty[s], 1); }
+    for (int w = 0; w < 2; ++w) { mbar_init(&sdp_full[w], 1); mbar_init(&ds_full[w], 4); mbar_init(&ds_free[w], 1); }
+    mbar_init(acc_done, 1);
+    mbar_init_fence();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_dq = tmem_base + 256;
+  const int col_q = h * D, col_k = p.E + h * D, col_v = 2 * p.E + h * D;
+  uint8_t* sq = smem + L::kBigOff;
+  uint8_t* sdo = sq + L::kBigBytes;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 2 * L::kBigBytes);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        tma_load_3d(sq + c * (kTile * 128), &map_qkv128, q_full, col_q + c * 64, row0, b);
+        tma_load_3d(sdo + c * (kTile * 128), &map_do64, q_full, col_q + c * 64, row0, b);
+        tma_load_3d(sdo + c * (kTile * 128) + kSub * 128, &map_do64, q_full, col_q + c * 64, row0 + kSub, b);
+      }
+      for (int it = 0; it < n_it; ++it) {
+        const int st = it % L::kStages;
+        if (!mbar_wait(&ring_empty[st], ((it / L::kStages) & 1) ^ 1, p.err, kErrAttnProducer)) break;
+        mbar_expect_tx(&ring_full[st], 2 * L::kSubBytes);
+        uint8_t* sk = smem + L::kRingOff + st * 2 * L::kSubBytes;
+        uint8_t* sv = sk + L::kSubBytes;
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          tma_load_3d(sk + c * (kSub * 128), &map_qkv64, &ring_full[st], col_k + c * 64, it * kSub, b);
+          tma_load_3d(sv + c * (kSub * 128), &map_qkv64, &ring_full[st], col_v + c * 64, it * kSub, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const bool bf = std::is_same<T, __nv_bfloat16>::value;
+      const uint32_t idesc_s = make_idesc(bf, 0, 0, kTile, kSub);  // [128 queries x 64 keys], both K-major
+      const uint32_t idesc_a = make_idesc(bf, 0, 1, kTile, D);     // [128 queries x D], K tile read MN-major
+      auto issue_scores = [&](int buf, int st) {
+        const uint32_t a_q = smem_u32(sq), a_do = smem_u32(sdo);
+        const uint32_t b_k = smem_u32(smem + L::kRingOff + st * 2 * L::kSubBytes), b_v = b_k + L::kSubBytes;
+        const uint32_t d_s = tmem_base + buf * 128, d_dp = d_s + 64;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t a_off = (kk / 4) * (kTile * 128) + (kk % 4) * 32, b_off = (kk / 4) * (kSub * 128) + (kk % 4) * 32;
+          umma_f16(d_s, make_desc(a_q + a_off, 16, 1024), make_desc(b_k + b_off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t a_off = (kk / 4) * (kTile * 128) + (kk % 4) * 32, b_off = (kk / 4) * (kSub * 128) + (kk % 4) * 32;
+          umma_f16(d_dp, make_desc(a_do + a_off, 16, 1024), make_desc(b_v + b_off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&sdp_full[buf]);
+      };
+      bool ok = mbar_wait(q_full, 0, p.err, kErrAttnMma) && mbar_wait(&ring_full[0], 0, p.err, kErrAttnMma);
+      if (ok) {
+        tc_fence_after();
+        issue_scores(0, 0);
+      }
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int st = it % L::kStages, buf = it & 1;
+        if (it + 1 < n_it) {
+          const int st1 = (it + 1) % L::kStages;
+          if (!mbar_wait(&ring_full[st1], ((it + 1) / L::kStages) & 1, p.err, kErrAttnMma)) { ok = false; break; }
+          tc_fence_after();
+          issue_scores((it + 1) & 1, st1);
+        }
+        if (!mbar_wait(&ds_full[buf], (it >> 1) & 1, p.err, kErrAttnMma)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t a_ds = smem_u32(smem + L::kOpOff + buf * 2 * L::kOpBytes);
+        const uint32_t b_k = smem_u32(smem + L::kRingOff + st * 2 * L::kSubBytes);
+#pragma unroll
+        for (int kk = 0; kk < kSub / 16; ++kk)
+          umma_f16(tmem_dq, make_desc(a_ds + kk * 32, 16, 1024), make_desc(b_k + kk * 2048, kSub * 128, 1024), idesc_a,
+                   (it > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&ring_empty[st]);
+        umma_commit(&ds_free[buf]);
+      }
+      if (ok) umma_commit(acc_done);
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int q = row0 + r;
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const long long vec_off = (static_cast<long long>(b) * p.H + h) * p.T + q;
+    const float lse2 = q < p.T ? p.lse[vec_off] * 1.4426950408889634f : INFINITY;
+    const float delta = q < p.T ? p.delta[vec_off] : 0.f;
+    bool ok = true;
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int buf = it & 1;
+      const int k0 = it * kSub;
+      if (!mbar_wait(&sdp_full[buf], (it >> 1) & 1, p.err, kErrAttnSoftmax)) { ok = false; break; }
+      tc_fence_after();
+      float s[kSub], dp[kSub];
+      tmem_ld32_nowait(tmem_base + buf * 128 + lane_off, s);
+      tmem_ld32_nowait(tmem_base + buf * 128 + lane_off + 32, s + 32);
+      tmem_ld32_nowait(tmem_base + buf * 128 + lane_off + 64, dp);
+      tmem_ld32_nowait(tmem_base + buf * 128 + lane_off + 96, dp + 32);
+      tmem_ld_wait();
+      if (!mbar_wait(&ds_free[buf], ((it >> 1) & 1) ^ 1, p.err, kErrAttnSoftmax)) { ok = false; break; }
+      uint8_t* sds = smem + L::kOpOff + buf * 2 * L::kOpBytes;
+      const bool need_mask = (p.causal && (k0 + kSub - 1 > row0)) || (k0 + kSub > p.T);
+      const int limit = p.causal ? min(q, p.T - 1) : p.T - 1;  // last visible key
+#pragma unroll
+      for (int c8 = 0; c8 < kSub / 8; ++c8) {
+        float dsv[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int c = c8 * 8 + e;
+          float pe = fast_exp2(fmaf(s[c], p.scale_log2, -lse2));
+          if (need_mask && k0 + c > limit) pe = 0.f;
+          dsv[e] = pe * (dp[c] - delta) * p.scale;
+        }
+        *reinterpret_cast<uint4*>(sds + sw128_offset(r, c8)) = pack8<T>(dsv);
+      }
+      fence_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ds_full[buf]);
+    }
+    if (ok && mbar_wait(acc_done, 0, p.err, kErrAttnSoftmax)) {
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        float o[32];
+        tmem_ld32(tmem_dq + lane_off + c * 32, o);
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          *reinterpret_cast<uint4*>(sq + (c / 2) * (kTile * 128) + sw128_offset(r, (c % 2) * 4 + e)) = pack8<T>(o + e * 8);
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0 && row0 + quarter * 32 < p.T) {
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_store_3d(&map_dqkv, sq + c * (kTile * 128) + quarter * 32 * 128, col_q + c * 64, row0 + quarter * 32, b);
+        tma_store_wait_all();
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// ---------------------------------------------------------------- host side
+struct AttnMaps {
+  CUtensorMap qkv128;  // [B, T, 3E], box {64, 128, 1}
+  CUtensorMap out32;   // [B, T, E],  box {64, 32, 1}
+};
+
+CUtensorMap make_map3(const Tensor& t, int cols, int T, int B, int box_rows, const char* what) {
+  CUtensorMap m;
+  const uint64_t dims[3] = {static_cast<uint64_t>(cols), static_cast<uint64_t>(T), static_cast<uint64_t>(B)};
+  const uint64_t strides[2] = {static_cast<uint64_t>(cols) * 2, static_cast<uint64_t>(cols) * 2 * static_cast<uint64_t>(T)};
+  const uint32_t box[3] = {64, static_cast<uint32_t>(box_rows), 1};
+  if (!tc05_encode_map(&m, t.dtype(), 3, t.data(), dims, strides, box))
+    throw std::runtime_error(std::string("attention: cannot encode the tensor map of ") + what);
+  return m;
+}
+
+template <class T, int D>
+void launch_fwd(const Tensor& qkv, Tensor& out, Tensor& lse, int B, int Tn, int H, bool causal, float scale, cudaStream_t st) {
+  using L = FwdSmem<D>;
+  const int E = H * D;
+  const CUtensorMap mq = make_map3(qkv, 3 * E, Tn, B, kTile, "qkv");
+  const CUtensorMap mo = make_map3(out, E, Tn, B, 32, "the output");
+  FlashParams p{};
+  p.B = B; p.H = H; p.T = Tn; p.E = E; p.causal = causal ? 1 : 0;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.lse = lse.data_as<float>();
+  p.err = tc05_error_flag(qkv.device().index);
+  static std::once_flag once;
+  std::call_once(once, [] {
+    OB_CUDA(cudaFuncSetAttribute(flash_fwd_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+  });
+  const int n_tiles = (Tn + kTile - 1) / kTile;
+  dim3 grid(B * H, (n_tiles + 1) / 2);
+  flash_fwd_kernel<T, D><<<grid, kFwdThreads, L::kTotal, st>>>(mq, mo, p);
+  check_launch("flash_attention_forward");
+}
+
+template <class T, int D>
+void launch_bwd(const Tensor& qkv, const Tensor& out, const Tensor& lse, const Tensor& dout, Tensor& dqkv, Tensor& delta, int B,
+                int Tn, int H, bool causal, float scale, cudaStream_t st) {
+  using L = BwdSmem<D>;
+  const int E = H * D;
+  const CUtensorMap m128 = make_map3(qkv, 3 * E, Tn, B, kTile, "qkv");
+  const CUtensorMap m64 = make_map3(qkv, 3 * E, Tn, B, kSub, "qkv");
+  const CUtensorMap mdo = make_map3(dout, E, Tn, B, kSub, "the output gradient");
+  const CUtensorMap mdq = make_map3(dqkv, 3 * E, Tn, B, 32, "the qkv gradient");
+  FlashParams p{};
+  p.B = B; p.H = H; p.T = Tn; p.E = E; p.causal = causal ? 1 : 0;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.lse = const_cast<float*>(lse.data_as<float>());
+  p.delta = delta.data_as<float>();
+  p.err = tc05_error_flag(qkv.device().index);
+  static std::once_flag once;
+  std::call_once(once, [] {
+    OB_CUDA(cudaFuncSetAttribute(flash_bwd_dkv_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    OB_CUDA(cudaFuncSetAttribute(flash_bwd_dq_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+  });
+  const long long rows = static_cast<long long>(B) * Tn * H;
+  attn_delta_kernel<T><<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, st>>>(dout.data_as<T>(), out.data_as<T>(),
+                                                                                         delta.data_as<float>(), B, Tn, H, D);
+  check_launch("attention_delta");
+  const int n_tiles = (Tn + kTile - 1) / kTile;
+  dim3 grid(B * H, n_tiles);
+  flash_bwd_dkv_kernel<T, D><<<grid, kBwdThreads, L::kTotal, st>>>(m128, m64, mdo, mdq, p);
+  check_launch("flash_attention_backward_dkv");
+  flash_bwd_dq_kernel<T, D><<<grid, kBwdThreads, L::kTotal, st>>>(m128, m64, mdo, mdq, p);
+  check_launch("flash_attention_backward_dq");
+}
+
+}  // namespace
+
+// True when the fused kernels cover this problem (otherwise callers compose the op).
+bool flash_attention_supported(const Tensor& qkv, int64_t heads) {
+  if (!qkv.device().is_cuda() || qkv.ndim() != 3 || !qkv.is_contiguous()) return false;
+  if (qkv.dtype() != DType::BF16 && qkv.dtype() != DType::F16) return false;
+  const int64_t E = qkv.shape()[2] / 3;
+  if (heads < 1 || E % heads != 0) return false;
+  const int64_t D = E / heads;
+  if (D != 64 && D != 128) return false;
+  if ((reinterpret_cast<uintptr_t>(qkv.data()) & 15u) != 0) return false;
+  if (qkv.shape()[0] * heads > 65535 * 32 || qkv.shape()[1] < 1) return false;
+  static const bool off = [] { const char* e = std::getenv("ORTHON_ATTENTION"); return e != nullptr && std::string(e) == "composed"; }();
+  return !off;
+}
+
+// out[B, T, E] and lse[B, H, T] (float32) must be allocated by the caller.
+void flash_attention_forward(const Tensor& qkv, int64_t heads, bool causal, double scale, Tensor& out, Tensor& lse, cudaStream_t st) {
+  const int B = static_cast<int>(qkv.shape()[0]), Tn = static_cast<int>(qkv.shape()[1]);
+  const int E = static_cast<int>(qkv.shape()[2] / 3), H = static_cast<int>(heads), D = E / H;
+  DeviceGuard g(qkv.device().index);
+  const float sc = static_cast<float>(scale);
+  if (qkv.dtype() == DType::BF16) {
+    if (D == 128) launch_fwd<__nv_bfloat16, 128>(qkv, out, lse, B, Tn, H, causal, sc, st);
+    else launch_fwd<__nv_bfloat16, 64>(qkv, out, lse, B, Tn, H, causal, sc, st);
+  } else {
+    if (D == 128) launch_fwd<__half, 128>(qkv, out, lse, B, Tn, H, causal, sc, st);
+    else launch_fwd<__half, 64>(qkv, out, lse, B, Tn, H, causal, sc, st);
+  }
+}
+
+// dqkv[B, T, 3E] (fully overwritten) from qkv, the forward output and LSE, and dout[B, T, E];
+// `delta` is float32 scratch of shape [B, H, T].
+void flash_attention_backward(const Tensor& qkv, const Tensor& out, const Tensor& lse, const Tensor& dout, int64_t heads, bool causal,
+                              double scale, Tensor& dqkv, Tensor& delta, cudaStream_t st) {
+  const int B = static_cast<int>(qkv.shape()[0]), Tn = static_cast<int>(qkv.shape()[1]);
+  const int E = static_cast<int>(qkv.shape()[2] / 3), H = static_cast<int>(heads), D = E / H;
+  DeviceGuard g(qkv.device().index);
+  const float sc = static_cast<float>(scale);
+  if (qkv.dtype() == DType::BF16) {
+    if (D == 128) launch_bwd<__nv_bfloat16, 128>(qkv, out, lse, dout, dqkv, delta, B, Tn, H, causal, sc, st);
+    else launch_bwd<__nv_bfloat16, 64>(qkv, out, lse, dout, dqkv, delta, B, Tn, H, causal, sc, st);
+  } else {
+    if (D == 128) launch_bwd<__half, 128>(qkv, out, lse, dout, dqkv, delta, B, Tn, H, causal, sc, st);
+    else launch_bwd<__half, 64>(qkv, out, lse, dout, dqkv, delta, B, Tn, H, causal, sc, st);
+  }
+}
+
+// Entry points for the semantic-op layer: run on the device's current stream.
+void flash_attention_forward_current(const Tensor& qkv, int64_t heads, bool causal, double scale, Tensor& out, Tensor& lse) {
+  cudaStream_t st = static_cast<cudaStream_t>(Runtime::instance().cuda(qkv.device().index).current_stream());
+  flash_attention_forward(qkv, heads, causal, scale, out, lse, st);
+}
+void flash_attention_backward_current(const Tensor& qkv, const Tensor& out, const Tensor& lse, const Tensor& dout, int64_t heads,
+                                      bool causal, double scale, Tensor& dqkv, Tensor& delta) {
+  cudaStream_t st = static_cast<cudaStream_t>(Runtime::instance().cuda(qkv.device().index).current_stream());
+  flash_attention_backward(qkv, out, lse, dout, heads, causal, scale, dqkv, delta, st);
+}
+
+}  // namespace cu
+}  // namespace ob

@@ -41,7 +41,7 @@ namespace cu {
 namespace {
 
 constexpr int kMaxRanks = 8;
-constexpr int kMaxCtas = 128;
+constexpr int kMaxCtas = 160;
 constexpr int kPeerThreads = 512;
 constexpr long long kPeerWaitBudget = 4000000000LL;  // about two seconds
 
@@ -433,7 +433,9 @@ void bind_peer(py::module_& m) {
     a.found_inf = found_inf.data_as<int>();
     DeviceGuard g(device);
     const int sms = Runtime::instance().cuda(device).sm_count();
-    int grid = ctas > 0 ? ctas : std::max(8, std::min(kMaxCtas, sms / 2));
+    // Large buckets are bandwidth-bound in the update phase and want every SM; small ones want
+    // few CTAs so the flag exchange stays cheap.
+    int grid = ctas > 0 ? ctas : std::max(8, std::min(kMaxCtas, (n >= (8ll << 20)) ? sms : sms / 2));
     const long long vecs = n / (gd == DType::F32 ? 4 : 8);
     grid = static_cast<int>(std::max<long long>(1, std::min<long long>(grid, (vecs / world + kPeerThreads - 1) / kPeerThreads)));
     if (grid > kMaxCtas) grid = kMaxCtas;

@@ -123,4 +123,12 @@ void check_same_device(const Tensor& a, const Tensor& b, const char* op);
 void check_same_dtype(const Tensor& a, const Tensor& b, const char* op);
 
 }  // namespace ops
+namespace cu {
+// Fused tcgen05 attention over a packed [B, T, 3E] projection (bf16 / f16, head size 64 or 128).
+bool flash_attention_supported(const Tensor& qkv, int64_t heads);
+void flash_attention_forward_current(const Tensor& qkv, int64_t heads, bool causal, double scale, Tensor& out, Tensor& lse);
+void flash_attention_backward_current(const Tensor& qkv, const Tensor& out, const Tensor& lse, const Tensor& dout, int64_t heads,
+                                      bool causal, double scale, Tensor& dqkv, Tensor& delta);
+}  // namespace cu
+
 }  // namespace ob

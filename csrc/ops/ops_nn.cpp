@@ -812,6 +812,24 @@ struct PackedAttentionNode : Node {
   void release_saved() override { qkv = Tensor(); probs = Tensor(); keep = Tensor(); }
 };
 
+// Fused path: the forward keeps only the output and the per-row log-sum-exp; the backward
+// recomputes the probabilities tile by tile on the tensor cores.
+struct FlashAttentionNode : Node {
+  Tensor qkv, out, lse;
+  int64_t heads;
+  double scale;
+  bool causal;
+  const char* name() const override { return "FlashAttentionNode"; }
+  std::vector<Tensor> backward(const Tensor& g_in) override {
+    Tensor g = contiguous(g_in);
+    Tensor dqkv = Tensor::empty(qkv.shape(), qkv.dtype(), qkv.device());
+    Tensor delta = Tensor::empty(lse.shape(), DType::F32, qkv.device());
+    cu::flash_attention_backward_current(qkv, out, lse, g, heads, causal, scale, dqkv, delta);
+    return {dqkv};
+  }
+  void release_saved() override { qkv = Tensor(); out = Tensor(); lse = Tensor(); }
+};
+
 }  // namespace
 
 Tensor attention_packed(const Tensor& qkv_in, int64_t heads, const Tensor& mask, bool causal, double scale,
@@ -823,6 +841,24 @@ Tensor attention_packed(const Tensor& qkv_in, int64_t heads, const Tensor& mask,
   if (mask.defined() && (mask.ndim() != 2 || mask.shape()[0] != T || mask.shape()[1] != T))
     throw std::invalid_argument("attention_packed: mask must have shape [T, T]");
   Tensor qkv = contiguous(qkv_in.detach());
+  if (!mask.defined() && dropout_p == 0.0 && cu::flash_attention_supported(qkv, heads)) {
+    Tensor out = Tensor::empty({B, T, E}, qkv.dtype(), qkv.device());
+    Tensor lse = Tensor::empty({B, heads, T}, DType::F32, qkv.device());
+    cu::flash_attention_forward_current(qkv, heads, causal, scale, out, lse);
+    if (needs_graph({qkv_in})) {
+      auto n = std::make_shared<FlashAttentionNode>();
+      n->qkv = qkv;
+      n->out = out.detach();
+      n->lse = lse;
+      n->heads = heads;
+      n->scale = scale;
+      n->causal = causal;
+      n->watch_version(qkv_in, "qkv");
+      n->set_inputs({qkv_in});
+      attach(out, n);
+    }
+    return out;
+  }
   Tensor q = head_view(qkv, 3, 0, heads), k = head_view(qkv, 3, 1, heads), v = head_view(qkv, 3, 2, heads);
   Tensor scores, probs, keep;
   {
