@@ -34,13 +34,21 @@ def build_model(ortho, cfg, dtype, device, seed):
     nn = ortho.nn
     rng = np.random.default_rng(seed)
 
+    def lower(t, dt):
+        # float16 tensors can only be produced by the reference's CUDA cast kernel.
+        if dt == "float16" and device != "cpu":
+            return ortho.cast(t.to(device), dt)
+        return ortho.cast(t, dt)
+
     def normal(shape, dt="float32"):
         arr = (rng.standard_normal(shape, dtype=np.float32) * cfg["init_std"]).astype(np.float32)
-        return ortho.from_numpy(arr) if dt == "float32" else ortho.from_numpy(arr, dtype=dt)
+        if dt == "float32":
+            return ortho.from_numpy(arr)
+        return ortho.from_numpy(arr, dtype=dt) if dt == "bfloat16" else lower(ortho.from_numpy(arr), dt)
 
     def const(shape, value):
         t = ortho.full(shape, value)
-        return t if dtype == "float32" else ortho.cast(t, dtype)
+        return t if dtype == "float32" else lower(t, dtype)
 
     def linear(i, o):
         lin = nn.Linear.__new__(nn.Linear)  # stock forward; weights filled in bulk
@@ -147,7 +155,8 @@ def run_reference_lm(args, cfg_override=None, dtype_override=None, device_overri
     cfg, batch, seq, name = CONFIGS[args.model]
     if cfg_override:
         cfg, batch, seq = cfg_override
-    dtype = dtype_override or "bfloat16"
+    fp16 = getattr(args, "amp", "bf16") == "fp16"
+    dtype = dtype_override or ("float16" if fp16 else "bfloat16")
     device = device_override or f"cuda:{local}"
     if device != "cpu" and not ortho.cuda_enabled():
         if rank == 0:
@@ -175,7 +184,7 @@ def run_reference_lm(args, cfg_override=None, dtype_override=None, device_overri
     if world > 1:
         wrapped = ddist.DistributedDataParallel(model, sync_grads=False)
     opt = MixedPrecisionOptimizer(wrapped, Adam, lr=3e-4)
-    scaler = GradScaler(enabled=False)
+    scaler = GradScaler(init_scale=128.0, enabled=fp16)
 
     rng = np.random.default_rng(100 + rank)
     mask_np = np.triu(np.full((seq, seq), -1e9, dtype=np.float32), k=1).reshape(1, seq, seq)
@@ -246,10 +255,11 @@ def run_reference_lm(args, cfg_override=None, dtype_override=None, device_overri
         print(json.dumps({
             "metric": "ddp_train_tokens_per_s", "value": tokens / device_s, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": device_s / args.steps * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if dtype == "bfloat16" else dtype,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": {"bfloat16": "bf16", "float16": "fp16"}.get(dtype, dtype),
             "data": "synthetic token ids, random-init weights", "impl": "reference",
             "config": {"model": name, "global_batch": batch * world, "seq_len": seq, "parallelism": f"dp{world}",
-                       "optimizer": "FP32-master Adam (reference MixedPrecisionOptimizer, scaler disabled)",
+                       "optimizer": "FP32-master Adam (reference MixedPrecisionOptimizer, " + ("GradScaler init 128)" if fp16 else "scaler disabled)"),
                        "timing": "wall clock between cuda_synchronize() calls (no event API in the reference)"},
             "e2e": {"value": tokens / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 2 * batch * seq * 8,
                     "d2h_bytes_per_step": 4, "last_loss": last},

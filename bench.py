@@ -35,6 +35,8 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="1p3b", choices=["1p3b", "tiny"])
     ap.add_argument("--backend", default=None, help="distributed transport for --gpus > 1 (default: p2p)")
+    ap.add_argument("--amp", default="bf16", choices=["bf16", "fp16"],
+                    help="bf16: bf16 compute, scaler disabled; fp16: fp16 compute with GradScaler(init_scale=128)")
     return ap.parse_args()
 
 
@@ -60,6 +62,9 @@ def run_ours(args):
         raise SystemExit(f"--gpus {args.gpus} does not match WORLD_SIZE {world}")
     device = f"cuda:{local}"
     cfg, batch, seq, dtype, model_name = model_config(args.model)
+    fp16 = args.amp == "fp16"
+    if fp16:
+        dtype = "float16"
 
     if world > 1:
         dist.init_process_group(args.backend or "p2p", rank=rank, world_size=world, device=local)
@@ -69,7 +74,10 @@ def run_ours(args):
     wrapped = model
     if world > 1:
         wrapped = dist.DDP(model, sync_grads=False, bucket_size_mb=25)
-    opt = ob.amp.MixedPrecisionOptimizer(wrapped, ob.optim.Adam, fused="update", lr=3e-4)
+    # With a live GradScaler the update must wait for the found-inf verdict, so buckets are only
+    # reduced during backward ("reduce"); otherwise the optimizer update is fused into them.
+    opt = ob.amp.MixedPrecisionOptimizer(wrapped, ob.optim.Adam, fused="reduce" if fp16 else "update", lr=3e-4)
+    scaler = ob.amp.GradScaler(init_scale=128.0, enabled=fp16)
 
     rng = np.random.default_rng(100 + rank)
     host_ids = _C._pinned_empty([batch, seq], "int64")
@@ -90,8 +98,13 @@ def run_ours(args):
     def train_step():
         opt.zero_grad()
         loss = model.loss(dev_ids, dev_tgt) if world == 1 else _ddp_loss(wrapped, model, dev_ids, dev_tgt)
-        loss.backward()
-        opt.step()
+        if fp16:
+            scaler.scale(loss).backward()
+            scaler.step(opt)
+            scaler.update()
+        else:
+            loss.backward()
+            opt.step()
         return loss
 
     fill_host()
@@ -134,9 +147,10 @@ def run_ours(args):
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": device_ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None if BASELINE_PUBLISHED is None else value / BASELINE_PUBLISHED,
-            "dtype": "bf16", "data": "synthetic token ids, random-init weights", "impl": "ours",
+            "dtype": "fp16" if fp16 else "bf16", "data": "synthetic token ids, random-init weights", "impl": "ours",
             "config": {"model": model_name, "global_batch": batch * world, "seq_len": seq,
-                       "parallelism": f"dp{world}", "optimizer": "FP32-master Adam (AMP, scaler disabled)",
+                       "parallelism": f"dp{world}",
+                       "optimizer": "FP32-master Adam (AMP, GradScaler init 128)" if fp16 else "FP32-master Adam (AMP, scaler disabled)",
                        "l2": "per-step working set (>= 2.7 GB of weights) exceeds the 126 MB L2; no flush needed",
                        "params": model.parameter_count()},
             "clocks": {"sm_mhz": clocks.result["sm_mhz"], "sm_max_mhz": clocks.result["sm_max_mhz"],

@@ -60,7 +60,9 @@ def _compile_one(src: Path, flags_cxx, flags_cu, hdr: str, verbose: bool, ptxas:
         if ptxas:
             cmd += ["-Xptxas", "-v"]
     else:
-        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall",
+        # The CPU backend's loops are written for the vectoriser; everything else is glue.
+        opt = "-O3" if src.parent.name == "cpu" else "-O2"
+        cmd = ["g++", opt, "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall",
                "-Wno-unused-function", *flags_cxx]
     key = hashlib.sha256()
     key.update(src.read_bytes())

@@ -8,6 +8,7 @@
 #include <cstring>
 #include <limits>
 
+#include "ob/cpu_parallel.h"
 #include "ob/kernels.h"
 
 namespace ob {
@@ -15,6 +16,68 @@ namespace {
 
 inline int64_t target_at(const Tensor& t, int64_t i) {
   return t.dtype() == DType::I64 ? t.data_as<int64_t>()[i] : static_cast<int64_t>(t.data_as<int32_t>()[i]);
+}
+
+// Vector kernels of the matmul family.  Written as plain loops over contiguous arrays so the
+// compiler vectorises them; clones for wider vector ISAs are selected at load time.
+#if defined(__x86_64__) && defined(__GNUC__) && !defined(__clang__)
+#define OB_VEC_CLONES __attribute__((target_clones("arch=x86-64-v4", "arch=x86-64-v3", "default")))
+#else
+#define OB_VEC_CLONES
+#endif
+
+#define OB_DEFINE_VEC_KERNELS(T, SUFFIX)                                                             \
+  OB_VEC_CLONES void axpy_##SUFFIX(T* __restrict__ c, const T* __restrict__ b, T a, int64_t n) {     \
+    for (int64_t j = 0; j < n; ++j) c[j] += a * b[j];                                                \
+  }                                                                                                  \
+  OB_VEC_CLONES T dot_##SUFFIX(const T* __restrict__ a, const T* __restrict__ b, int64_t n) {        \
+    T acc[16] = {};                                                                                  \
+    int64_t k = 0;                                                                                   \
+    for (; k + 16 <= n; k += 16)                                                                     \
+      for (int l = 0; l < 16; ++l) acc[l] += a[k + l] * b[k + l];                                    \
+    T s = T(0);                                                                                      \
+    for (; k < n; ++k) s += a[k] * b[k];                                                             \
+    for (int l = 0; l < 16; ++l) s += acc[l];                                                        \
+    return s;                                                                                        \
+  }
+OB_DEFINE_VEC_KERNELS(float, f32)
+OB_DEFINE_VEC_KERNELS(double, f64)
+#undef OB_DEFINE_VEC_KERNELS
+
+inline void axpy(float* c, const float* b, float a, int64_t n) { axpy_f32(c, b, a, n); }
+inline void axpy(double* c, const double* b, double a, int64_t n) { axpy_f64(c, b, a, n); }
+inline float dot(const float* a, const float* b, int64_t n) { return dot_f32(a, b, n); }
+inline double dot(const double* a, const double* b, int64_t n) { return dot_f64(a, b, n); }
+
+// One batch entry: C[M, N] = A'[M, K] @ B'[K, N] through element strides.  Rows of C are split
+// over the worker pool; every element is produced by one worker in a fixed order.
+template <class T>
+void gemm_rows(const T* pa, int64_t a_rs, int64_t a_cs, const T* pb, int64_t b_rs, int64_t b_cs, T* pc, int64_t c_rs,
+               int64_t c_cs, int64_t M, int64_t N, int64_t K) {
+  const int64_t work_per_row = std::max<int64_t>(1, N * K);
+  const int64_t grain = std::max<int64_t>(1, (1 << 16) / work_per_row);
+  cpu::parallel_for(M, grain, [&](int64_t lo, int64_t hi) {
+    if (b_cs == 1 && c_cs == 1) {
+      // B rows contiguous: accumulate row i of C as a sum of scaled rows of B.
+      for (int64_t i = lo; i < hi; ++i) {
+        T* crow = pc + i * c_rs;
+        for (int64_t j = 0; j < N; ++j) crow[j] = T(0);
+        for (int64_t k = 0; k < K; ++k) axpy(crow, pb + k * b_rs, pa[i * a_rs + k * a_cs], N);
+      }
+    } else if (b_rs == 1 && a_cs == 1) {
+      // Both operands contiguous along K (B given transposed): dot products.
+      for (int64_t i = lo; i < hi; ++i)
+        for (int64_t j = 0; j < N; ++j) pc[i * c_rs + j * c_cs] = dot(pa + i * a_rs, pb + j * b_cs, K);
+    } else {
+      for (int64_t i = lo; i < hi; ++i) {
+        for (int64_t j = 0; j < N; ++j) pc[i * c_rs + j * c_cs] = T(0);
+        for (int64_t k = 0; k < K; ++k) {
+          const T av = pa[i * a_rs + k * a_cs];
+          for (int64_t j = 0; j < N; ++j) pc[i * c_rs + j * c_cs] += av * pb[k * b_rs + j * b_cs];
+        }
+      }
+    }
+  });
 }
 
 // C[b] = op(A[b]) @ op(B[b]); operands addressed through element strides, so transposed
@@ -42,19 +105,7 @@ void matmul_cpu(OpCall& c) {
     const T* pa = A.data_as<T>() + b0 * bstride(A, 0) + b1 * bstride(A, 1);
     const T* pb = B.data_as<T>() + b0 * bstride(B, 0) + b1 * bstride(B, 1);
     T* pc = C.data_as<T>() + b0 * bstride(C, 0) + b1 * bstride(C, 1);
-    for (int64_t i = 0; i < M; ++i) {
-      for (int64_t j = 0; j < N; ++j) pc[i * c_rs + j * c_cs] = T(0);
-      for (int64_t k = 0; k < K; ++k) {
-        const T av = pa[i * a_rs + k * a_cs];
-        const T* brow = pb + k * b_rs;
-        T* crow = pc + i * c_rs;
-        if (b_cs == 1 && c_cs == 1) {
-          for (int64_t j = 0; j < N; ++j) crow[j] += av * brow[j];
-        } else {
-          for (int64_t j = 0; j < N; ++j) crow[j * c_cs] += av * brow[j * b_cs];
-        }
-      }
-    }
+    gemm_rows<T>(pa, a_rs, a_cs, pb, b_rs, b_cs, pc, c_rs, c_cs, M, N, K);
   }
 }
 
@@ -68,24 +119,30 @@ void linear_cpu(OpCall& c) {
   const T* pw = w.data_as<T>();
   T* py = y.data_as<T>();
   T* pz = c.out[1].defined() ? c.out[1].data_as<T>() : nullptr;
-  std::vector<T> row(static_cast<size_t>(N));
-  for (int64_t i = 0; i < M; ++i) {
-    for (int64_t j = 0; j < N; ++j) row[j] = bias.defined() ? bias.data_as<T>()[j] : T(0);
-    for (int64_t k = 0; k < K; ++k) {
-      const T xv = px[i * x.strides()[0] + k * x.strides()[1]];
-      const T* wr = pw + k * w.strides()[0];
-      const int64_t wcs = w.strides()[1];
-      for (int64_t j = 0; j < N; ++j) row[j] += xv * wr[j * wcs];
+  const int64_t x_rs = x.strides()[0], x_cs = x.strides()[1], w_rs = w.strides()[0], w_cs = w.strides()[1];
+  const int64_t grain = std::max<int64_t>(1, (1 << 16) / std::max<int64_t>(1, N * K));
+  cpu::parallel_for(M, grain, [&](int64_t lo, int64_t hi) {
+    std::vector<T> row(static_cast<size_t>(N));
+    for (int64_t i = lo; i < hi; ++i) {
+      for (int64_t j = 0; j < N; ++j) row[j] = bias.defined() ? bias.data_as<T>()[j] : T(0);
+      if (w_cs == 1) {
+        for (int64_t k = 0; k < K; ++k) axpy(row.data(), pw + k * w_rs, px[i * x_rs + k * x_cs], N);
+      } else {
+        for (int64_t k = 0; k < K; ++k) {
+          const T xv = px[i * x_rs + k * x_cs];
+          for (int64_t j = 0; j < N; ++j) row[j] += xv * pw[k * w_rs + j * w_cs];
+        }
+      }
+      for (int64_t j = 0; j < N; ++j) {
+        T v = row[j];
+        if (pz) pz[i * N + j] = v;
+        if (act == 1) v = v > T(0) ? v : T(0);
+        else if (act == 2) v = T(0.5) * v * (T(1) + std::erf(v * T(0.70710678118654752440)));
+        if (res.defined()) v += res.data_as<T>()[i * N + j];
+        py[i * N + j] = v;
+      }
     }
-    for (int64_t j = 0; j < N; ++j) {
-      T v = row[j];
-      if (pz) pz[i * N + j] = v;
-      if (act == 1) v = v > T(0) ? v : T(0);
-      else if (act == 2) v = T(0.5) * v * (T(1) + std::erf(v * T(0.70710678118654752440)));
-      if (res.defined()) v += res.data_as<T>()[i * N + j];
-      py[i * N + j] = v;
-    }
-  }
+  });
 }
 
 template <class T>

@@ -65,6 +65,12 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Bounded wait whose verdict is uniform across the warp (lanes may otherwise disagree right at
+// the timeout, and the softmax warps use warp-collective instructions afterwards).
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, int* err, int code) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, err, code));
+}
+
 // Packs 8 floats into 8 16-bit values (one 16-byte chunk).
 template <class T>
 __device__ __forceinline__ uint4 pack8(const float* v) {
@@ -236,7 +242,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_const
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_it && ok; ++j) {
-      if (!mbar_wait(&s_full[w], j & 1, p.err, kErrAttnSoftmax)) { ok = false; break; }
+      if (!warp_wait(&s_full[w], j & 1, p.err, kErrAttnSoftmax)) { ok = false; break; }
       tc_fence_after();
       float s[kTile];
 #pragma unroll
@@ -251,15 +257,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_const
         for (int c = 0; c < kTile; ++c)
           if (key0 + c > limit) s[c] = -INFINITY;
       }
-      float mx = s[0];
+      float mx4[4] = {s[0], s[1], s[2], s[3]};  // four independent chains instead of one of 128
 #pragma unroll
-      for (int c = 1; c < kTile; ++c) mx = fmaxf(mx, s[c]);
+      for (int c = 4; c < kTile; c += 4) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mx4[i] = fmaxf(mx4[i], s[c + i]);
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       float m_new = fmaxf(m, mx * p.scale_log2);
       if (m_new == -INFINITY) m_new = 0.f;  // fully masked row (only rows past the sequence end)
       const float alpha = fast_exp2(m - m_new);
       if (j > 0) {
         // P_{j-1} V has finished: the O accumulator is consistent and the P tile is free.
-        if (!mbar_wait(&o_done[w], (j - 1) & 1, p.err, kErrAttnSoftmax)) { ok = false; break; }
+        if (!warp_wait(&o_done[w], (j - 1) & 1, p.err, kErrAttnSoftmax)) { ok = false; break; }
         tc_fence_after();
         if (__any_sync(0xffffffffu, m_new > m)) {
 #pragma unroll 1
@@ -273,25 +283,25 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_const
           tmem_st_wait();
         }
       }
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c8 = 0; c8 < kTile / 8; ++c8) {
         float pv[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           pv[i] = fast_exp2(fmaf(s[c8 * 8 + i], p.scale_log2, -m_new));
-          sum += pv[i];
+          sum4[i & 3] += pv[i];
         }
         *reinterpret_cast<uint4*>(sp + (c8 / 8) * (kTile * 128) + sw128_offset(r, c8 % 8)) = pack8<T>(pv);
       }
-      l = l * alpha + sum;
+      l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
       m = m_new;
       fence_async_smem();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[w]);
     }
-    if (ok && n_it > 0 && mbar_wait(&o_done[w], (n_it - 1) & 1, p.err, kErrAttnSoftmax)) {
+    if (ok && n_it > 0 && warp_wait(&o_done[w], (n_it - 1) & 1, p.err, kErrAttnSoftmax)) {
       tc_fence_after();
       const float inv_l = 1.f / l;
       // Stage this warp's 32 rows (the P tile is free now) and store them with TMA.
@@ -324,44 +334,51 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_const
 }
 
 // ----------------------------------------------------------------- backward
-// delta[b, h, t] = sum_d dO[b, t, h*D + d] * O[b, t, h*D + d]; one warp per (b, t, h).
+// delta[b, h, t] = sum_d dO[b, t, h*D + d] * O[b, t, h*D + d]; D/8 lanes per (b, t, h) row, 16-byte loads.
 template <class T>
 __global__ void attn_delta_kernel(const T* __restrict__ dout, const T* __restrict__ out, float* __restrict__ delta, int B, int Tn,
                                   int H, int D) {
-  const long long warp_id = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
+  const int lanes = D / 8;  // 8 or 16
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long row = tid / lanes;  // (b*T + t)*H + h, which is also the row of the [B*T*H, D] view
+  const int sub = static_cast<int>(tid - row * lanes);
   const long long total = static_cast<long long>(B) * Tn * H;
-  if (warp_id >= total) return;
-  const int h = static_cast<int>(warp_id % H);
-  const long long bt = warp_id / H;
-  const long long base = bt * static_cast<long long>(H) * D + static_cast<long long>(h) * D;
   float acc = 0.f;
-  for (int d = lane * 2; d < D; d += 64) {
-    acc += to_f(dout[base + d]) * to_f(out[base + d]) + to_f(dout[base + d + 1]) * to_f(out[base + d + 1]);
+  if (row < total) {
+    const Pack<T> a = load_pack(dout + row * D + sub * 8), o = load_pack(out + row * D + sub * 8);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc += to_f(a.v[k]) * to_f(o.v[k]);
   }
-  acc = warp_sum(acc);
-  const long long b = bt / Tn, t = bt - b * Tn;
-  if (lane == 0) delta[(b * H + h) * Tn + t] = acc;
+  for (int off = lanes / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (row < total && sub == 0) {
+    const int h = static_cast<int>(row % H);
+    const long long bt = row / H;
+    const long long b = bt / Tn, t = bt - b * Tn;
+    delta[(b * H + h) * Tn + t] = acc;
+  }
 }
 
-constexpr int kBwdThreads = 192;
+constexpr int kBwdThreads = 320;  // TMA warp, MMA warp, two softmax groups of four warps
 constexpr int kSub = 64;  // rows of the streamed operand per step (N of the score MMAs)
 
-// Shared-memory plan of both backward kernels: two resident [128 x D] tiles, a ring of streamed
-// [64 x D] tile pairs, two double-buffered [128 x 64] operand tiles written by the softmax warps.
-template <int D>
+// Shared-memory plan of the backward kernels: two resident [128 x D] tiles, a ring of streamed
+// [64 x D] tile pairs (deep enough to hide the TMA latency behind the MMAs of the other ring
+// slots), and OPS double-buffered [128 x 64] operand tiles written by the softmax warps.
+template <int D, int OPS, int STAGES>
 struct BwdSmem {
   static constexpr int kBigBytes = kTile * D * 2;   // resident tile
   static constexpr int kSubBytes = kSub * D * 2;    // streamed tile
   static constexpr int kOpBytes = kTile * kSub * 2; // operand tile written by the softmax warps
-  static constexpr int kStages = (D == 128) ? 2 : 3;
+  static constexpr int kStages = STAGES;
   static constexpr int kBigOff = 0;                                   // two resident tiles
   static constexpr int kRingOff = kBigOff + 2 * kBigBytes;            // kStages x (two streamed tiles)
-  static constexpr int kOpOff = kRingOff + kStages * 2 * kSubBytes;   // [2 buffers][2 tiles]
-  static constexpr int kVecOff = kOpOff + 4 * kOpBytes;               // per-warp lse/delta staging
-  static constexpr int kBarOff = kVecOff + 4 * 2 * 128 * 4;
+  static constexpr int kOpOff = kRingOff + kStages * 2 * kSubBytes;   // [2 buffers][OPS tiles]
+  static constexpr int kBarOff = kOpOff + 2 * OPS * kOpBytes;
   static constexpr int kTotal = kBarOff + 256 + 1024;
+  static_assert(kTotal <= 232448, "exceeds the shared memory of one CTA");
 };
+template <int D> using DkvSmem = BwdSmem<D, 2, (D == 128) ? 3 : 4>;
+template <int D> using DqSmem = BwdSmem<D, 1, 4>;
 
 // dK, dV: one CTA per (batch, head, 128-key tile); streams 64-row query tiles.
 //   S^T = K Q^T, dP^T = V dO^T (TMEM, 64 columns each, double buffered); one thread per key row
@@ -370,7 +387,7 @@ template <class T, int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_constant__ CUtensorMap map_qkv64,
                      const __grid_constant__ CUtensorMap map_do64, const __grid_constant__ CUtensorMap map_dqkv, FlashParams p) {
-  using L = BwdSmem<D>;
+  using L = DkvSmem<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
@@ -394,7 +411,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gri
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int s = 0; s < L::kStages; ++s) { mbar_init(&ring_full[s], 1); mbar_init(&ring_empty[s], 1); }
-    for (int w = 0; w < 2; ++w) { mbar_init(&sdp_full[w], 1); mbar_init(&pds_full[w], 4); mbar_init(&pds_free[w], 1); }
+    for (int w = 0; w < 2; ++w) { mbar_init(&sdp_full[w], 1); mbar_init(&pds_full[w], 8); mbar_init(&pds_free[w], 1); }
     mbar_init(acc_done, 1);
     mbar_init_fence();
   }
@@ -482,85 +499,81 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gri
     }
   } else {
     const int quarter = warp & 3;
+    const int grp = (warp - 2) >> 2;    // column half of the 64-query sub-tile this group converts
     const int r = quarter * 32 + lane;  // key row within the tile
     const int key = key0 + r;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
-    float* vec = reinterpret_cast<float*>(smem + L::kVecOff) + (warp - 2) * 256;  // [2 buffers][lse2 64 | delta 64]
     const float* lse_row = p.lse + (static_cast<long long>(b) * p.H + h) * p.T;
     const float* delta_row = p.delta + (static_cast<long long>(b) * p.H + h) * p.T;
     bool ok = true;
     for (int it = 0; it < n_it && ok; ++it) {
       const int buf = it & 1;
-      const int q0 = (i0 + it) * kSub;
-      float* vb = vec + buf * 128;
-      // Stage log2-scaled LSE and delta of the 64 queries; queries past the end get +inf (P = 0).
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int q = q0 + half * 32 + lane;
-        vb[half * 32 + lane] = q < p.T ? lse_row[q] * 1.4426950408889634f : INFINITY;
-        vb[64 + half * 32 + lane] = q < p.T ? delta_row[q] : 0.f;
-      }
-      __syncwarp();
-      if (!mbar_wait(&sdp_full[buf], (it >> 1) & 1, p.err, kErrAttnSoftmax)) { ok = false; break; }
+      const int q0 = (i0 + it) * kSub + grp * 32;  // first query of this group's columns
+      // Lane l holds the log2-scaled LSE and delta of query q0 + l; queries past the end get +inf
+      // (P = 0).  Column values are fetched with shuffles below.
+      const int q_lane = q0 + lane;
+      const float lse_lane = q_lane < p.T ? lse_row[q_lane] * 1.4426950408889634f : INFINITY;
+      const float delta_lane = q_lane < p.T ? delta_row[q_lane] : 0.f;
+      if (!warp_wait(&sdp_full[buf], (it >> 1) & 1, p.err, kErrAttnSoftmax)) { ok = false; break; }
       tc_fence_after();
-      float s[kSub], dp[kSub];
-      tmem_ld32_nowait(tmem_base + buf * 128 + lane_off, s);
-      tmem_ld32_nowait(tmem_base + buf * 128 + lane_off + 32, s + 32);
-      tmem_ld32_nowait(tmem_base + buf * 128 + lane_off + 64, dp);
-      tmem_ld32_nowait(tmem_base + buf * 128 + lane_off + 96, dp + 32);
+      float s[32], dp[32];
+      tmem_ld32_nowait(tmem_base + buf * 128 + lane_off + grp * 32, s);
+      tmem_ld32_nowait(tmem_base + buf * 128 + lane_off + 64 + grp * 32, dp);
       tmem_ld_wait();
-      if (!mbar_wait(&pds_free[buf], ((it >> 1) & 1) ^ 1, p.err, kErrAttnSoftmax)) { ok = false; break; }
+      if (!warp_wait(&pds_free[buf], ((it >> 1) & 1) ^ 1, p.err, kErrAttnSoftmax)) { ok = false; break; }
       uint8_t* sp = smem + L::kOpOff + buf * 2 * L::kOpBytes;
       uint8_t* sds = sp + L::kOpBytes;
-      const bool key_ok = key < p.T;
-      const bool need_mask = p.causal && (q0 < key0 + kTile);
+      // Masking is needed only on tiles that touch the diagonal or the end of the sequence.
+      const bool need_mask = (p.causal && (q0 < key0 + kTile)) || (key0 + kTile > p.T);
 #pragma unroll
-      for (int c8 = 0; c8 < kSub / 8; ++c8) {
-        const float4 l0 = *reinterpret_cast<const float4*>(vb + c8 * 8), l1 = *reinterpret_cast<const float4*>(vb + c8 * 8 + 4);
-        const float4 d0 = *reinterpret_cast<const float4*>(vb + 64 + c8 * 8), d1 = *reinterpret_cast<const float4*>(vb + 64 + c8 * 8 + 4);
-        const float l8[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
-        const float d8[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+      for (int c8 = 0; c8 < 4; ++c8) {
+        float l8[8], d8[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          l8[e] = __shfl_sync(0xffffffffu, lse_lane, c8 * 8 + e);
+          d8[e] = __shfl_sync(0xffffffffu, delta_lane, c8 * 8 + e);
+        }
         float pv[8], dsv[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const int c = c8 * 8 + e;
-          float pe = fast_exp2(fmaf(s[c], p.scale_log2, -l8[e]));
-          if (!key_ok || (need_mask && key > q0 + c)) pe = 0.f;
-          pv[e] = pe;
-          dsv[e] = pe * (dp[c] - d8[e]) * p.scale;
+          pv[e] = fast_exp2(fmaf(s[c], p.scale_log2, -l8[e]));
         }
-        *reinterpret_cast<uint4*>(sp + sw128_offset(r, c8)) = pack8<T>(pv);
-        *reinterpret_cast<uint4*>(sds + sw128_offset(r, c8)) = pack8<T>(dsv);
+        if (need_mask) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            if (key >= p.T || (p.causal && key > q0 + c8 * 8 + e)) pv[e] = 0.f;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dsv[e] = (pv[e] * p.scale) * (dp[c8 * 8 + e] - d8[e]);
+        *reinterpret_cast<uint4*>(sp + sw128_offset(r, grp * 4 + c8)) = pack8<T>(pv);
+        *reinterpret_cast<uint4*>(sds + sw128_offset(r, grp * 4 + c8)) = pack8<T>(dsv);
       }
       fence_async_smem();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&pds_full[buf]);
     }
-    if (ok && n_it > 0 && mbar_wait(acc_done, 0, p.err, kErrAttnSoftmax)) {
+    if (ok && n_it > 0 && warp_wait(acc_done, 0, p.err, kErrAttnSoftmax)) {
       tc_fence_after();
-      // dV then dK: stage this warp's 32 rows in the (now idle) V / K tiles and store them.
+      // Group 0 writes dV, group 1 dK: stage this warp's 32 rows in the (now idle) V / K tile and
+      // store them.
+      uint8_t* dst = grp ? sk : sv;
+      const uint32_t src = grp ? tmem_dk : tmem_dv;
 #pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
-        uint8_t* dst = which ? sk : sv;
-        const uint32_t src = which ? tmem_dk : tmem_dv;
-#pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-          float o[32];
-          tmem_ld32(src + lane_off + c * 32, o);
+      for (int c = 0; c < D / 32; ++c) {
+        float o[32];
+        tmem_ld32(src + lane_off + c * 32, o);
 #pragma unroll
-          for (int q = 0; q < 4; ++q)
-            *reinterpret_cast<uint4*>(dst + (c / 2) * (kTile * 128) + sw128_offset(r, (c % 2) * 4 + q)) = pack8<T>(o + q * 8);
-        }
+        for (int q = 0; q < 4; ++q)
+          *reinterpret_cast<uint4*>(dst + (c / 2) * (kTile * 128) + sw128_offset(r, (c % 2) * 4 + q)) = pack8<T>(o + q * 8);
       }
       fence_async_smem();
       __syncwarp();
       if (lane == 0 && key0 + quarter * 32 < p.T) {
 #pragma unroll
-        for (int c = 0; c < D / 64; ++c) {
-          tma_store_3d(&map_dqkv, sv + c * (kTile * 128) + quarter * 32 * 128, col_v + c * 64, key0 + quarter * 32, b);
-          tma_store_3d(&map_dqkv, sk + c * (kTile * 128) + quarter * 32 * 128, col_k + c * 64, key0 + quarter * 32, b);
-        }
+        for (int c = 0; c < D / 64; ++c)
+          tma_store_3d(&map_dqkv, dst + c * (kTile * 128) + quarter * 32 * 128, (grp ? col_k : col_v) + c * 64, key0 + quarter * 32, b);
         tma_store_wait_all();
       }
     }
@@ -578,7 +591,7 @@ template <class T, int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_constant__ CUtensorMap map_qkv64,
                     const __grid_constant__ CUtensorMap map_do64, const __grid_constant__ CUtensorMap map_dqkv, FlashParams p) {
-  using L = BwdSmem<D>;
+  using L = DqSmem<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
@@ -602,7 +615,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < L::kStages; ++s) { mbar_init(&ring_full[s], 1); mbar_init(&ring_empty[s], 1); }
-    for (int w = 0; w < 2; ++w) { mbar_init(&sdp_full[w], 1); mbar_init(&ds_full[w], 4); mbar_init(&ds_free[w], 1); }
+    for (int w = 0; w < 2; ++w) { mbar_init(&sdp_full[w], 1); mbar_init(&ds_full[w], 8); mbar_init(&ds_free[w], 1); }
     mbar_init(acc_done, 1);
     mbar_init_fence();
   }
@@ -674,7 +687,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid
         }
         if (!mbar_wait(&ds_full[buf], (it >> 1) & 1, p.err, kErrAttnMma)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t a_ds = smem_u32(smem + L::kOpOff + buf * 2 * L::kOpBytes);
+        const uint32_t a_ds = smem_u32(smem + L::kOpOff + buf * L::kOpBytes);
         const uint32_t b_k = smem_u32(smem + L::kRingOff + st * 2 * L::kSubBytes);
 #pragma unroll
         for (int kk = 0; kk < kSub / 16; ++kk)
@@ -687,62 +700,64 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid
     }
   } else {
     const int quarter = warp & 3;
+    const int grp = (warp - 2) >> 2;  // column half of the 64-key sub-tile this group converts
     const int r = quarter * 32 + lane;
     const int q = row0 + r;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     const long long vec_off = (static_cast<long long>(b) * p.H + h) * p.T + q;
     const float lse2 = q < p.T ? p.lse[vec_off] * 1.4426950408889634f : INFINITY;
     const float delta = q < p.T ? p.delta[vec_off] : 0.f;
+    const int limit = p.causal ? min(q, p.T - 1) : p.T - 1;  // last visible key
     bool ok = true;
     for (int it = 0; it < n_it && ok; ++it) {
       const int buf = it & 1;
-      const int k0 = it * kSub;
-      if (!mbar_wait(&sdp_full[buf], (it >> 1) & 1, p.err, kErrAttnSoftmax)) { ok = false; break; }
+      const int k0 = it * kSub + grp * 32;
+      if (!warp_wait(&sdp_full[buf], (it >> 1) & 1, p.err, kErrAttnSoftmax)) { ok = false; break; }
       tc_fence_after();
-      float s[kSub], dp[kSub];
-      tmem_ld32_nowait(tmem_base + buf * 128 + lane_off, s);
-      tmem_ld32_nowait(tmem_base + buf * 128 + lane_off + 32, s + 32);
-      tmem_ld32_nowait(tmem_base + buf * 128 + lane_off + 64, dp);
-      tmem_ld32_nowait(tmem_base + buf * 128 + lane_off + 96, dp + 32);
+      float s[32], dp[32];
+      tmem_ld32_nowait(tmem_base + buf * 128 + lane_off + grp * 32, s);
+      tmem_ld32_nowait(tmem_base + buf * 128 + lane_off + 64 + grp * 32, dp);
       tmem_ld_wait();
-      if (!mbar_wait(&ds_free[buf], ((it >> 1) & 1) ^ 1, p.err, kErrAttnSoftmax)) { ok = false; break; }
-      uint8_t* sds = smem + L::kOpOff + buf * 2 * L::kOpBytes;
-      const bool need_mask = (p.causal && (k0 + kSub - 1 > row0)) || (k0 + kSub > p.T);
-      const int limit = p.causal ? min(q, p.T - 1) : p.T - 1;  // last visible key
+      if (!warp_wait(&ds_free[buf], ((it >> 1) & 1) ^ 1, p.err, kErrAttnSoftmax)) { ok = false; break; }
+      uint8_t* sds = smem + L::kOpOff + buf * L::kOpBytes;
+      const bool need_mask = (p.causal && (k0 + 31 > row0)) || (k0 + 32 > p.T);
 #pragma unroll
-      for (int c8 = 0; c8 < kSub / 8; ++c8) {
-        float dsv[8];
+      for (int c8 = 0; c8 < 4; ++c8) {
+        float pv[8], dsv[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int c = c8 * 8 + e;
-          float pe = fast_exp2(fmaf(s[c], p.scale_log2, -lse2));
-          if (need_mask && k0 + c > limit) pe = 0.f;
-          dsv[e] = pe * (dp[c] - delta) * p.scale;
+        for (int e = 0; e < 8; ++e) pv[e] = fast_exp2(fmaf(s[c8 * 8 + e], p.scale_log2, -lse2));
+        if (need_mask) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            if (k0 + c8 * 8 + e > limit) pv[e] = 0.f;
         }
-        *reinterpret_cast<uint4*>(sds + sw128_offset(r, c8)) = pack8<T>(dsv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dsv[e] = (pv[e] * p.scale) * (dp[c8 * 8 + e] - delta);
+        *reinterpret_cast<uint4*>(sds + sw128_offset(r, grp * 4 + c8)) = pack8<T>(dsv);
       }
       fence_async_smem();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ds_full[buf]);
     }
-    if (ok && mbar_wait(acc_done, 0, p.err, kErrAttnSoftmax)) {
+    if (ok && warp_wait(acc_done, 0, p.err, kErrAttnSoftmax)) {
       tc_fence_after();
+      // Each group drains and stores one 64-column block of dQ (group 0 alone when D = 64).
+      if (grp < D / 64) {
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        float o[32];
-        tmem_ld32(tmem_dq + lane_off + c * 32, o);
+        for (int c = grp * 2; c < grp * 2 + 2; ++c) {
+          float o[32];
+          tmem_ld32(tmem_dq + lane_off + c * 32, o);
 #pragma unroll
-        for (int e = 0; e < 4; ++e)
-          *reinterpret_cast<uint4*>(sq + (c / 2) * (kTile * 128) + sw128_offset(r, (c % 2) * 4 + e)) = pack8<T>(o + e * 8);
-      }
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0 && row0 + quarter * 32 < p.T) {
-#pragma unroll
-        for (int c = 0; c < D / 64; ++c)
-          tma_store_3d(&map_dqkv, sq + c * (kTile * 128) + quarter * 32 * 128, col_q + c * 64, row0 + quarter * 32, b);
-        tma_store_wait_all();
+          for (int e = 0; e < 4; ++e)
+            *reinterpret_cast<uint4*>(sq + grp * (kTile * 128) + sw128_offset(r, (c % 2) * 4 + e)) = pack8<T>(o + e * 8);
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0 && row0 + quarter * 32 < p.T) {
+          tma_store_3d(&map_dqkv, sq + grp * (kTile * 128) + quarter * 32 * 128, col_q + grp * 64, row0 + quarter * 32, b);
+          tma_store_wait_all();
+        }
       }
     }
   }
@@ -792,7 +807,8 @@ void launch_fwd(const Tensor& qkv, Tensor& out, Tensor& lse, int B, int Tn, int 
 template <class T, int D>
 void launch_bwd(const Tensor& qkv, const Tensor& out, const Tensor& lse, const Tensor& dout, Tensor& dqkv, Tensor& delta, int B,
                 int Tn, int H, bool causal, float scale, cudaStream_t st) {
-  using L = BwdSmem<D>;
+  using LA = DkvSmem<D>;
+  using LB = DqSmem<D>;
   const int E = H * D;
   const CUtensorMap m128 = make_map3(qkv, 3 * E, Tn, B, kTile, "qkv");
   const CUtensorMap m64 = make_map3(qkv, 3 * E, Tn, B, kSub, "qkv");
@@ -806,18 +822,18 @@ void launch_bwd(const Tensor& qkv, const Tensor& out, const Tensor& lse, const T
   p.err = tc05_error_flag(qkv.device().index);
   static std::once_flag once;
   std::call_once(once, [] {
-    OB_CUDA(cudaFuncSetAttribute(flash_bwd_dkv_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-    OB_CUDA(cudaFuncSetAttribute(flash_bwd_dq_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    OB_CUDA(cudaFuncSetAttribute(flash_bwd_dkv_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, LA::kTotal));
+    OB_CUDA(cudaFuncSetAttribute(flash_bwd_dq_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, LB::kTotal));
   });
   const long long rows = static_cast<long long>(B) * Tn * H;
-  attn_delta_kernel<T><<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, st>>>(dout.data_as<T>(), out.data_as<T>(),
+  attn_delta_kernel<T><<<static_cast<unsigned>((rows * (D / 8) + 255) / 256), 256, 0, st>>>(dout.data_as<T>(), out.data_as<T>(),
                                                                                          delta.data_as<float>(), B, Tn, H, D);
   check_launch("attention_delta");
   const int n_tiles = (Tn + kTile - 1) / kTile;
   dim3 grid(B * H, n_tiles);
-  flash_bwd_dkv_kernel<T, D><<<grid, kBwdThreads, L::kTotal, st>>>(m128, m64, mdo, mdq, p);
+  flash_bwd_dkv_kernel<T, D><<<grid, kBwdThreads, LA::kTotal, st>>>(m128, m64, mdo, mdq, p);
   check_launch("flash_attention_backward_dkv");
-  flash_bwd_dq_kernel<T, D><<<grid, kBwdThreads, L::kTotal, st>>>(m128, m64, mdo, mdq, p);
+  flash_bwd_dq_kernel<T, D><<<grid, kBwdThreads, LB::kTotal, st>>>(m128, m64, mdo, mdq, p);
   check_launch("flash_attention_backward_dq");
 }
 

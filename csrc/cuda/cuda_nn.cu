@@ -643,15 +643,17 @@ __global__ void layernorm_bwd_fast(const T* __restrict__ x, const T* __restrict_
   }
 }
 
-// Column sums of the per-block partials: block (32, 8), one 32-column strip per block.
+// Column sums of the per-block partials: block (32, 32), one 32-column strip per block; the 32
+// row groups keep enough loads in flight to hide DRAM latency, then a fixed-order sum.
 template <class T>
 __global__ void layernorm_bwd_finalize_fast(const float* __restrict__ partial, T* __restrict__ dw, T* __restrict__ db,
                                             int nblocks, int64_t D) {
-  __shared__ float ta[8][33], tb[8][33];
+  __shared__ float ta[32][33], tb[32][33];
   const int64_t j = static_cast<int64_t>(blockIdx.x) * 32 + threadIdx.x;
   float a = 0.f, b = 0.f;
   if (j < D) {
-    for (int i = threadIdx.y; i < nblocks; i += 8) {
+#pragma unroll 4
+    for (int i = threadIdx.y; i < nblocks; i += 32) {
       a += partial[static_cast<int64_t>(i) * 2 * D + j];
       b += partial[static_cast<int64_t>(i) * 2 * D + D + j];
     }
@@ -662,7 +664,7 @@ __global__ void layernorm_bwd_finalize_fast(const float* __restrict__ partial, T
   if (threadIdx.y == 0 && j < D) {
     float sa = 0.f, sb = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { sa += ta[i][threadIdx.x]; sb += tb[i][threadIdx.x]; }
+    for (int i = 0; i < 32; ++i) { sa += ta[i][threadIdx.x]; sb += tb[i][threadIdx.x]; }
     if (dw) dw[j] = from_f<T>(sa);
     if (db) db[j] = from_f<T>(sb);
   }
@@ -741,7 +743,7 @@ void k_layernorm_bwd(OpCall& c) {
     else if (fch == 2) layernorm_bwd_fast<T, 2><<<nblocks, fth, 0, st>>>(px, pw, pg, pmn, prs, pdx, partial, R, D);
     else layernorm_bwd_fast<T, 4><<<nblocks, fth, 0, st>>>(px, pw, pg, pmn, prs, pdx, partial, R, D);
     if (need_params)
-      layernorm_bwd_finalize_fast<T><<<static_cast<unsigned>((D + 31) / 32), dim3(32, 8), 0, st>>>(
+      layernorm_bwd_finalize_fast<T><<<static_cast<unsigned>((D + 31) / 32), dim3(32, 32), 0, st>>>(
           partial, c.out[1].defined() ? c.out[1].data_as<T>() : nullptr, c.out[2].defined() ? c.out[2].data_as<T>() : nullptr, nblocks, D);
     check_launch("layer_norm backward");
     return;

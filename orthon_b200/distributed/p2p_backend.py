@@ -107,24 +107,34 @@ class PeerBackend(Backend):
 
     # ------------------------------------------------------------- collectives
     def _peer_sum(self, tensor):
-        """In-place sum over ranks through the symmetric staging region (compute stream)."""
+        """In-place sum over ranks through the symmetric staging region (compute stream).
+
+        Tensors larger than the staging region go through it chunk by chunk, so no size falls
+        back to another transport."""
         n = int(tensor.numel)
         esz = _ESIZE[tensor.dtype]
+        flat = tensor.reshape([-1])
+        cap = (STAGING_BYTES // esz) & ~7
+        off = 0
+        while off < n:
+            m = min(cap, n - off)
+            self._peer_sum_chunk(flat, off, m, tensor.dtype, esz)
+            off += m
+        return True
+
+    def _peer_sum_chunk(self, flat, off, n, dtype, esz):
         padded = (n + 7) & ~7
-        if padded * esz > STAGING_BYTES:
-            return False
-        stage = _C._tensor_from_ptr(self._stage.local, [padded], tensor.dtype, self._device)
+        stage = _C._tensor_from_ptr(self._stage.local, [padded], dtype, self._device)
         if padded != n:
             stage.fill_(0.0)
-        stage._copy_flat_range_from(0, tensor.reshape([-1]), 0, n)
+        stage._copy_flat_range_from(0, flat, off, n)
         grads = list(self._stage.ptrs)
         staging = [p + STAGING_BYTES for p in self._stage.ptrs]
         flags = [p + 2 * STAGING_BYTES for p in self._stage.ptrs]
-        _C._peer_reduce(self._rank, self._world, self._device, grads, staging, flags, padded, tensor.dtype, self.next_epoch(),
+        _C._peer_reduce(self._rank, self._world, self._device, grads, staging, flags, padded, dtype, self.next_epoch(),
                         1.0, "average", padded * esz <= (1 << 20), status=self._status, found_inf=self._found_inf,
                         stream_kind=0)
-        tensor.reshape([-1])._copy_flat_range_from(0, stage, 0, n)
-        return True
+        flat._copy_flat_range_from(off, stage, 0, n)
 
     def _fallback(self):
         if self._nccl is None:
