@@ -1,5 +1,5 @@
-"""Reducer sweep: fused peer-memory all-reduce (+ unscale, inf check, 1/world scaling, FP32-master
-Adam) against NCCL all-reduce followed by a local fused Adam kernel, for gradient buckets of
+"""Reducer sweep: fused peer-memory all-reduce (peer-load and, where available, in-switch multimem
+variants; + unscale, inf check, 1/world scaling, FP32-master Adam) against NCCL all-reduce followed by a local fused Adam kernel, for gradient buckets of
 4 KB .. 1 GB in float32 and bfloat16.
 
     python benchmarks/bench_reducer.py --gpus 2 [--max-mb 1024] [--dtypes float32 bfloat16]
@@ -39,7 +39,8 @@ def worker(rank, dtypes, max_mb, iters):
     for dtype in dtypes:
         esz = ESZ[dtype]
         n_max = max_bytes // esz
-        region = be.allocate_symmetric(n_max * esz + n_max * 4 + _C._PEER_FLAG_BYTES)
+        region = be.allocate_symmetric(n_max * esz + n_max * 4 + _C._PEER_FLAG_BYTES, multicast=True)
+        mc = getattr(region, "mc", None) or 0
         grads = list(region.ptrs)
         staging = [p + n_max * esz for p in region.ptrs]
         flags = [p + n_max * esz + n_max * 4 for p in region.ptrs]
@@ -73,13 +74,13 @@ def worker(rank, dtypes, max_mb, iters):
                     samples.append(b.elapsed_ms_since(a))
                 return statistics.median(samples)
 
-            def fused(mode):
+            def fused(mode, mc_ptr=0):
                 return lambda: _C._peer_reduce(rank, ws, dev_i, grads, staging, flags, n, dtype, be.next_epoch(),
-                                               1.0 / (128.0 * ws), mode, oneshot,
+                                               1.0 / (128.0 * ws), mode, oneshot and not mc_ptr,
                                                master=_C._view_flat(master, 0, [n]), m=_C._view_flat(m, 0, [n]),
                                                v=_C._view_flat(v, 0, [n]),
                                                model=None if model is None else _C._view_flat(model, 0, [n]),
-                                               hyper=dict(hyper), status=status, found_inf=found, stream_kind=0)
+                                               hyper=dict(hyper), status=status, found_inf=found, stream_kind=0, mc_grads=mc_ptr)
 
             view = _C._view_flat(grad_t, 0, [n])
 
@@ -93,19 +94,24 @@ def worker(rank, dtypes, max_mb, iters):
                                1.0 / (128.0 * ws))
 
             t = {"fused_average": timed(fused("average")), "fused_adam": timed(fused("adam")),
-                 "nccl_allreduce": timed(nccl_only), "nccl_then_adam": timed(nccl_adam)}
+                 "nccl_allreduce": timed(nccl_only), "nccl_then_adam": timed(nccl_adam),
+                 "nvls_average": timed(fused("average", mc)) if mc else 0.0,
+                 "nvls_adam": timed(fused("adam", mc)) if mc else 0.0}
             # max over ranks
-            vec = np.zeros([ws, 4], dtype=np.float32)
-            vec[rank] = [t["fused_average"], t["fused_adam"], t["nccl_allreduce"], t["nccl_then_adam"]]
+            vec = np.zeros([ws, 6], dtype=np.float32)
+            vec[rank] = [t["fused_average"], t["fused_adam"], t["nccl_allreduce"], t["nccl_then_adam"], t["nvls_average"],
+                         t["nvls_adam"]]
             tt = _C.from_numpy(vec).to(dev)
             dist.all_reduce(tt)
-            worst = np.asarray(tt.tolist()).reshape(ws, 4).max(axis=0)
+            worst = np.asarray(tt.tolist()).reshape(ws, 6).max(axis=0)
             bus = lambda ms: 2.0 * size * (ws - 1) / ws / (ms * 1e-3) / 1e9  # noqa: E731
             rows.append({"dtype": dtype, "bytes": size, "world": ws, "oneshot": oneshot,
                          "fused_average_ms": float(worst[0]), "fused_adam_ms": float(worst[1]),
                          "nccl_allreduce_ms": float(worst[2]), "nccl_then_adam_ms": float(worst[3]),
                          "fused_average_bus_gbs": bus(worst[0]), "fused_adam_bus_gbs": bus(worst[1]),
                          "nccl_bus_gbs": bus(worst[2]),
+                         "nvls_average_ms": float(worst[4]), "nvls_adam_ms": float(worst[5]),
+                         "nvls_average_bus_gbs": bus(worst[4]) if worst[4] > 0 else None,
                          "fused_average_frac_of_nvlink_roofline": bus(worst[0]) / NVLINK_PEER_GBS})
             size *= 2
         be.check_status()

@@ -21,6 +21,10 @@ void copy_h2d_async(Tensor& dst, const Tensor& src, int stream_kind);
 void copy_d2h_async(Tensor& dst, const Tensor& src);
 unsigned int take_index_errors();
 int take_gemm_error(int device);
+void set_gemm_route(int route);
+int last_gemm_route();
+void set_conv_route(int route);
+int last_conv_route();
 uint64_t kernel_launch_count();
 }  // namespace cu
 void bind_distributed(py::module_& m);
@@ -463,6 +467,26 @@ PYBIND11_MODULE(_C, m) {
                                  seed.attr("__and__")(py::int_(0xFFFFFFFFFFFFFFFFull)).cast<uint64_t>());
   }, py::arg("qkv"), py::arg("heads"), py::arg("mask") = py::none(), py::arg("causal") = false, py::arg("scale") = 1.0,
      py::arg("dropout_p") = 0.0, py::arg("seed") = py::int_(0));
+  // Diagnostics (reference project: bindings/ops_bindings.cpp:300-363, src/diagnostics/matmul.cpp).
+  m.def("_matmul_force_route", [](const std::string& route) {
+    if (route == "auto") cu::set_gemm_route(0);
+    else if (route == "simt") cu::set_gemm_route(1);
+    else if (route == "tcgen05") cu::set_gemm_route(2);
+    else throw std::invalid_argument("matmul route must be 'auto', 'simt' or 'tcgen05'");
+  });
+  m.def("_matmul_last_route", [] {
+    static const char* names[] = {"none", "simt", "tcgen05_128x128", "tcgen05_128x256"};
+    return std::string(names[cu::last_gemm_route() & 3]);
+  });
+  m.def("_conv2d_force_route", [](const std::string& route) {
+    if (route == "auto") cu::set_conv_route(0);
+    else if (route == "direct") cu::set_conv_route(1);
+    else throw std::invalid_argument("conv2d route must be 'auto' or 'direct'");
+  });
+  m.def("_conv2d_last_route", [] {
+    static const char* names[] = {"none", "direct", "tcgen05_lowering", "none"};
+    return std::string(names[cu::last_conv_route() & 3]);
+  });
   m.def("_attention_qkv_fused", [](const Tensor& qkv, int64_t heads) { return cu::flash_attention_supported(qkv, heads); });
   m.def("_gemm", &ops::gemm, py::arg("a"), py::arg("trans_a"), py::arg("b"), py::arg("trans_b"));
   m.def("isfinite_all", &ops::isfinite_all);

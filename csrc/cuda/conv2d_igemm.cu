@@ -15,6 +15,8 @@
 #include <cstdlib>
 #include <cstring>
 
+#include <atomic>
+
 #include "ob/cuda_common.cuh"
 #include "ob/ops.h"
 
@@ -123,8 +125,15 @@ Tensor broadcast_batch(const Tensor& m2d, int64_t n) {  // [rows, cols] -> [n, r
 
 }  // namespace
 
+std::atomic<int> g_conv_force{0};  // 0 = planner, 1 = direct kernels, 2 = tcgen05 lowering required
+std::atomic<int> g_conv_last{0};   // 1 = direct, 2 = tcgen05 lowering
+void set_conv_route(int route) { g_conv_force.store(route, std::memory_order_relaxed); }
+int last_conv_route() { return g_conv_last.load(std::memory_order_relaxed); }
+void note_conv_route(int route) { g_conv_last.store(route, std::memory_order_relaxed); }
+
 bool conv_igemm_enabled(const Tensor& x, const Geom* unused = nullptr) {
   (void)unused;
+  if (g_conv_force.load(std::memory_order_relaxed) == 1) return false;
   const char* env = std::getenv("ORTHON_CUDA_CONV2D");
   if (env && std::strcmp(env, "direct") == 0) return false;
   if (x.dtype() != DType::BF16 && x.dtype() != DType::F16) return false;

@@ -16,6 +16,7 @@ template <class T> bool conv_wgrad_igemm(OpCall& c);
 template <> inline bool conv_fprop_igemm<float>(OpCall&) { return false; }
 template <> inline bool conv_dgrad_igemm<float>(OpCall&) { return false; }
 template <> inline bool conv_wgrad_igemm<float>(OpCall&) { return false; }
+void note_conv_route(int route);  // diagnostics: 1 = direct kernels, 2 = tcgen05 lowering
 
 namespace {
 
@@ -128,7 +129,8 @@ __global__ void conv_bgrad_kernel(const T* __restrict__ gy, T* __restrict__ db, 
 
 template <class T>
 void k_conv(OpCall& c) {
-  if (conv_fprop_igemm<T>(c)) return;
+  if (conv_fprop_igemm<T>(c)) { note_conv_route(2); return; }
+  note_conv_route(1);
   const ConvGeom g = geom_of(c.in[0].shape(), c.in[1].shape(), c.i);
   conv_fwd_kernel<T><<<ew_grid(c.out[0].numel(), kThreads, sm_count_for(c.in[0])), kThreads, 0, stream_of(c)>>>(
       c.in[0].data_as<T>(), c.in[1].data_as<T>(), c.in[2].defined() ? c.in[2].data_as<T>() : nullptr, c.out[0].data_as<T>(), g);
@@ -137,7 +139,8 @@ void k_conv(OpCall& c) {
 
 template <class T>
 void k_conv_dgrad(OpCall& c) {
-  if (conv_dgrad_igemm<T>(c)) return;
+  if (conv_dgrad_igemm<T>(c)) { note_conv_route(2); return; }
+  note_conv_route(1);
   const ConvGeom g = geom_of(c.out[0].shape(), c.in[1].shape(), c.i);
   conv_dgrad_kernel<T><<<ew_grid(c.out[0].numel(), kThreads, sm_count_for(c.in[0])), kThreads, 0, stream_of(c)>>>(
       c.in[0].data_as<T>(), c.in[1].data_as<T>(), c.out[0].data_as<T>(), g);
@@ -146,7 +149,8 @@ void k_conv_dgrad(OpCall& c) {
 
 template <class T>
 void k_conv_wgrad(OpCall& c) {
-  if (conv_wgrad_igemm<T>(c)) return;
+  if (conv_wgrad_igemm<T>(c)) { note_conv_route(2); return; }
+  note_conv_route(1);
   const ConvGeom g = geom_of(c.in[1].shape(), c.out[0].shape(), c.i);
   conv_wgrad_kernel<T><<<static_cast<unsigned>(c.out[0].numel()), kThreads, 0, stream_of(c)>>>(
       c.in[0].data_as<T>(), c.in[1].data_as<T>(), c.out[0].data_as<T>(), g);

@@ -27,6 +27,7 @@
 // routes), :138-400 (16x16 SIMT tiles), src/backends/cuda/fusion_kernels.cu:42-86.
 #include <cuda.h>
 
+#include <atomic>
 #include <cstdlib>
 #include <mutex>
 #include <string>
@@ -43,6 +44,10 @@ void strided_copy_cuda(const Tensor& src, Tensor& dst, cudaStream_t st);
 namespace {
 
 using namespace tc05;
+
+// Diagnostic route control: 0 = planner decides, 1 = force the SIMT kernel, 2 = require tcgen05.
+std::atomic<int> g_force_route{0};
+std::atomic<int> g_last_route{0};  // 1 = simt, 2 = tcgen05 128x128, 3 = tcgen05 128x256
 
 constexpr int BM = 128;
 constexpr int BK = 64;
@@ -570,13 +575,16 @@ void gemm_dispatch(const Tensor& A_in, bool ta, const Tensor& B_in, bool tb, Ten
   const long long c_bs0 = nbd == 2 ? C.strides()[0] : 0, c_bs1 = nbd >= 1 ? C.strides()[nbd - 1] : 0;
   const DType dt = C.dtype();
 
+  const int force = g_force_route.load(std::memory_order_relaxed);
   if (dt == DType::F32) {
+    if (force == 2) throw std::runtime_error("matmul diagnostics: the tcgen05 route needs float16 or bfloat16 operands");
+    g_last_route.store(1, std::memory_order_relaxed);
     launch_simt<float>(a, b, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);
     return;
   }
   // Operands that TMA cannot describe are packed once (the packed copy is K-major).
-  const bool tiny = static_cast<long long>(M) * N * K < (1LL << 18);
-  bool use_tc = !tiny && Runtime::instance().cuda(C.device().index).supports_tcgen05();
+  const bool tiny = static_cast<long long>(M) * N * K < (1LL << 18) && force != 2;
+  bool use_tc = !tiny && force != 1 && Runtime::instance().cuda(C.device().index).supports_tcgen05();
   if (use_tc) {
     if (!tma_compatible(a, nb0, nb1)) {
       A = Tensor::empty(A.shape(), A.dtype(), A.device());
@@ -591,6 +599,8 @@ void gemm_dispatch(const Tensor& A_in, bool ta, const Tensor& B_in, bool tb, Ten
     use_tc = tma_compatible(a, nb0, nb1) && tma_compatible(b, nb0, nb1);
   }
   if (!use_tc) {
+    if (force == 2) throw std::runtime_error("matmul diagnostics: this problem cannot take the tcgen05 route");
+    g_last_route.store(1, std::memory_order_relaxed);
     if (dt == DType::BF16) launch_simt<__nv_bfloat16>(a, b, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);
     else launch_simt<__half>(a, b, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);
     return;
@@ -598,6 +608,7 @@ void gemm_dispatch(const Tensor& A_in, bool ta, const Tensor& B_in, bool tb, Ten
   const bool a_mn = !(a.s_k == 1 || (a.k == 1 && a.s_mn != 1));
   const bool b_mn = !(b.s_k == 1 || (b.k == 1 && b.s_mn != 1));
   const bool wide = N > 128;
+  g_last_route.store(wide ? 3 : 2, std::memory_order_relaxed);
   if (dt == DType::BF16) {
     if (wide) launch_tc05<__nv_bfloat16, 256>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);
     else launch_tc05<__nv_bfloat16, 128>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);
@@ -647,6 +658,11 @@ bool tc05_encode_map(CUtensorMap* out, DType dt, int rank, void* base, const uin
                      static_cast<cuuint32_t>(rank), base, d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
+
+// Diagnostics (reference project: src/diagnostics/matmul.cpp:14-87): force a route, read the
+// route the last matmul took.
+void set_gemm_route(int route) { g_force_route.store(route, std::memory_order_relaxed); }
+int last_gemm_route() { return g_last_route.load(std::memory_order_relaxed); }
 
 // Reads and clears the GEMM error word of a device (0 = no error).  Synchronizes the device.
 int take_gemm_error(int device) {

@@ -64,6 +64,7 @@ struct PeerArgs {
   const long long* seg_end;  // optional per-parameter weight-decay segments
   const float* seg_wd;
   int nseg;
+  void* mc_grads;  // multicast mapping of every rank's bucket (NVLS path), or null
   int* status;     // local: first error code
   int* found_inf;  // local: set to 1 when any rank saw a non-finite reduced gradient
 };
@@ -163,21 +164,18 @@ __device__ __forceinline__ void apply_update(const PeerArgs& a, long long e, con
   }
 }
 
-// Sums VEC elements at offset `e` over all ranks (fixed order), scales, reports non-finite.
-template <class GT, int VEC>
-__device__ __forceinline__ bool reduce_pack(const PeerArgs& a, long long e, float* acc) {
-  Pack<GT> in[kMaxRanks];
-#pragma unroll
-  for (int s = 0; s < kMaxRanks; ++s)
-    if (s < a.world) in[s] = load_pack(static_cast<const GT*>(a.grads[s]) + e);
-#pragma unroll
-  for (int k = 0; k < VEC; ++k) acc[k] = 0.f;
-#pragma unroll
-  for (int s = 0; s < kMaxRanks; ++s)
-    if (s < a.world) {
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) acc[k] += to_f(in[s].v[k]);
-    }
+// Number of ranks known at compile time (W = 2, 4, 8) lets one thread keep U = 8 / W vectors
+// of every rank in flight, so the NVLink round trip is covered at any world size; W = 0 is the
+// generic fallback (runtime world, one vector at a time).
+template <int W>
+struct Unroll {
+  static constexpr int kRanks = W ? W : kMaxRanks;
+  static constexpr int kVectors = W ? 8 / W : 1;
+};
+
+// Scales VEC summed elements, reports non-finite values.
+template <int VEC>
+__device__ __forceinline__ bool finish_sum(const PeerArgs& a, float* acc) {
   bool bad = false;
 #pragma unroll
   for (int k = 0; k < VEC; ++k) {
@@ -187,9 +185,52 @@ __device__ __forceinline__ bool reduce_pack(const PeerArgs& a, long long e, floa
   return bad;
 }
 
-template <class GT>
+// Reduces the vectors [0, nvec) of the slice starting at element `lo` over all ranks (fixed
+// rank order, fp32 accumulation) and hands every reduced vector to `emit(element, acc)`.
+template <class GT, int W, class Emit>
+__device__ __forceinline__ bool reduce_range(const PeerArgs& a, long long lo, long long nvec, Emit emit) {
+  constexpr int VEC = Pack<GT>::N;
+  constexpr int R = Unroll<W>::kRanks, U = Unroll<W>::kVectors;
+  const int world = W ? W : a.world;
+  const long long stride = static_cast<long long>(gridDim.x) * kPeerThreads;
+  bool bad = false;
+  for (long long v0 = static_cast<long long>(blockIdx.x) * kPeerThreads + threadIdx.x; v0 < nvec; v0 += stride * U) {
+    Pack<GT> in[U][R];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long vi = v0 + u * stride;
+      if (vi < nvec) {
+#pragma unroll
+        for (int s = 0; s < R; ++s)
+          if (s < world) in[u][s] = load_pack(static_cast<const GT*>(a.grads[s]) + lo + vi * VEC);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long vi = v0 + u * stride;
+      if (vi < nvec) {
+        float acc[VEC];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) acc[k] = 0.f;
+#pragma unroll
+        for (int s = 0; s < R; ++s)
+          if (s < world) {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) acc[k] += to_f(in[u][s].v[k]);
+          }
+        bad |= finish_sum<VEC>(a, acc);
+        emit(lo + vi * VEC, acc);
+      }
+    }
+  }
+  return bad;
+}
+
+template <class GT, int W>
 __global__ void __launch_bounds__(kPeerThreads) peer_reduce_kernel(PeerArgs a) {
   constexpr int VEC = Pack<GT>::N;  // 16 bytes of gradients per access
+  constexpr int R = Unroll<W>::kRanks;
+  const int world = W ? W : a.world;
   __shared__ int s_bad;
   if (threadIdx.x == 0) s_bad = 0;
   const int G = gridDim.x;
@@ -198,39 +239,34 @@ __global__ void __launch_bounds__(kPeerThreads) peer_reduce_kernel(PeerArgs a) {
   bool bad = false;
   if (a.oneshot) {
     // Every rank reduces everything; the update (or write-back) follows immediately.
-    const long long nvec = a.n / VEC;
-    for (long long vi = static_cast<long long>(blockIdx.x) * kPeerThreads + threadIdx.x; vi < nvec;
-         vi += static_cast<long long>(G) * kPeerThreads) {
-      float acc[VEC];
-      bad |= reduce_pack<GT, VEC>(a, vi * VEC, acc);
+    bad = reduce_range<GT, W>(a, 0, a.n / VEC, [&](long long e, const float* acc) {
 #pragma unroll
       for (int k = 0; k < VEC; k += 4)
-        *reinterpret_cast<float4*>(a.staging[a.rank] + vi * VEC + k) = *reinterpret_cast<float4*>(acc + k);
-    }
+        *reinterpret_cast<float4*>(a.staging[a.rank] + e + k) = *reinterpret_cast<const float4*>(acc + k);
+    });
   } else {
     const long long lo = min(a.n, static_cast<long long>(a.rank) * a.per), hi = min(a.n, lo + a.per);
-    const long long nvec = (hi - lo) / VEC;
-    for (long long vi = static_cast<long long>(blockIdx.x) * kPeerThreads + threadIdx.x; vi < nvec;
-         vi += static_cast<long long>(G) * kPeerThreads) {
-      const long long e = lo + vi * VEC;
-      float acc[VEC];
-      bad |= reduce_pack<GT, VEC>(a, e, acc);
-      if (a.mode == kModeAverage) {
+    if (a.mode == kModeAverage) {
+      // The reduced slice goes straight back into every rank's bucket in the gradient dtype.
+      bad = reduce_range<GT, W>(a, lo, (hi - lo) / VEC, [&](long long e, const float* acc) {
         Pack<GT> out;
 #pragma unroll
         for (int k = 0; k < VEC; ++k) out.v[k] = from_f<GT>(acc[k]);
 #pragma unroll
-        for (int s = 0; s < kMaxRanks; ++s)
-          if (s < a.world) store_pack(const_cast<GT*>(static_cast<const GT*>(a.grads[s])) + e, out);
-      } else {
+        for (int s = 0; s < R; ++s)
+          if (s < world) store_pack(const_cast<GT*>(static_cast<const GT*>(a.grads[s])) + e, out);
+      });
+    } else {
+      // The optimizer wants fp32: push the reduced slice into every rank's fp32 staging.
+      bad = reduce_range<GT, W>(a, lo, (hi - lo) / VEC, [&](long long e, const float* acc) {
 #pragma unroll
-        for (int s = 0; s < kMaxRanks; ++s)
-          if (s < a.world) {
+        for (int s = 0; s < R; ++s)
+          if (s < world) {
 #pragma unroll
             for (int k = 0; k < VEC; k += 4)
-              *reinterpret_cast<float4*>(a.staging[s] + e + k) = *reinterpret_cast<float4*>(acc + k);
+              *reinterpret_cast<float4*>(a.staging[s] + e + k) = *reinterpret_cast<const float4*>(acc + k);
           }
-      }
+      });
     }
   }
   if (bad) atomicExch(&s_bad, 1);
@@ -281,6 +317,93 @@ __global__ void __launch_bounds__(kPeerThreads) peer_reduce_kernel(PeerArgs a) {
           apply_update<GT, VEC>(a, e, g);
         }
       }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ NVLS path
+// multimem.ld_reduce sums one 16-byte vector over every rank's bucket inside the NVSwitch
+// (fp32 accumulation for 16-bit gradients) and multimem.st writes the result to every rank at
+// once, so each GPU moves S bytes per direction instead of 2 S (w-1)/w.
+template <class GT>
+__device__ __forceinline__ void multimem_ld_reduce(const void* mc, uint32_t (&r)[4]);
+template <>
+__device__ __forceinline__ void multimem_ld_reduce<float>(const void* mc, uint32_t (&r)[4]) {
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "l"(mc) : "memory");
+}
+template <>
+__device__ __forceinline__ void multimem_ld_reduce<__nv_bfloat16>(const void* mc, uint32_t (&r)[4]) {
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "l"(mc) : "memory");
+}
+template <>
+__device__ __forceinline__ void multimem_ld_reduce<__half>(const void* mc, uint32_t (&r)[4]) {
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "l"(mc) : "memory");
+}
+__device__ __forceinline__ void multimem_st(void* mc, const uint32_t (&r)[4]) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+               ::"l"(mc), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]) : "memory");
+}
+
+// Same protocol as peer_reduce_kernel (entry barrier, reduce own slice, found-inf word, middle
+// barrier, optimizer update on the local copy), with the slice reduced and re-broadcast in the
+// switch.  The reduced gradients land in every rank's bucket in the gradient dtype; the update
+// reads them from the local bucket.
+template <class GT>
+__global__ void __launch_bounds__(kPeerThreads) nvls_reduce_kernel(PeerArgs a) {
+  constexpr int VEC = Pack<GT>::N;
+  constexpr int U = 4;  // vectors in flight per thread
+  __shared__ int s_bad;
+  if (threadIdx.x == 0) s_bad = 0;
+  if (!peer_barrier(a, 0, kErrEntryBarrier)) return;
+
+  const long long lo = min(a.n, static_cast<long long>(a.rank) * a.per), hi = min(a.n, lo + a.per);
+  const long long nvec = (hi - lo) / VEC;
+  const long long stride = static_cast<long long>(gridDim.x) * kPeerThreads;
+  GT* mc = static_cast<GT*>(a.mc_grads);
+  bool bad = false;
+  for (long long v0 = static_cast<long long>(blockIdx.x) * kPeerThreads + threadIdx.x; v0 < nvec; v0 += stride * U) {
+    uint32_t raw[U][4];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long vi = v0 + u * stride;
+      if (vi < nvec) multimem_ld_reduce<GT>(mc + lo + vi * VEC, raw[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long vi = v0 + u * stride;
+      if (vi < nvec) {
+        Pack<GT> in = *reinterpret_cast<Pack<GT>*>(raw[u]);
+        float acc[VEC];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) acc[k] = to_f(in.v[k]);
+        bad |= finish_sum<VEC>(a, acc);
+        Pack<GT> out;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) out.v[k] = from_f<GT>(acc[k]);
+        multimem_st(mc + lo + vi * VEC, *reinterpret_cast<uint32_t(*)[4]>(&out));
+      }
+    }
+  }
+  if (bad) atomicExch(&s_bad, 1);
+  __syncthreads();
+  if (s_bad && threadIdx.x < a.world) *inf_word(a.flags[threadIdx.x]) = a.epoch;  // tell every rank
+
+  if (!peer_barrier(a, 1, kErrMidBarrier)) return;
+  const bool any_inf = ld_acquire_sys(inf_word(a.flags[a.rank])) == a.epoch;
+  if (any_inf && threadIdx.x == 0 && blockIdx.x == 0) atomicExch(a.found_inf, 1);
+
+  if (a.mode != kModeAverage && !any_inf) {
+    const GT* red = static_cast<const GT*>(a.grads[a.rank]);
+    const long long all = a.n / VEC;
+    for (long long vi = static_cast<long long>(blockIdx.x) * kPeerThreads + threadIdx.x; vi < all; vi += stride) {
+      const Pack<GT> in = load_pack(red + vi * VEC);
+      float g[VEC];
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) g[k] = to_f(in.v[k]);
+      apply_update<GT, VEC>(a, vi * VEC, g);
     }
   }
 }
@@ -386,7 +509,8 @@ void bind_peer(py::module_& m) {
   m.def("_peer_reduce", [](int rank, int world, int device, const std::vector<uintptr_t>& grads, const std::vector<uintptr_t>& staging,
                            const std::vector<uintptr_t>& flags, long long n, const std::string& dtype, uint32_t epoch, double scale,
                            const std::string& mode, bool oneshot, const py::object& master, const py::object& mom, const py::object& var,
-                           const py::object& model, const py::dict& hyper, Tensor& status, Tensor& found_inf, int ctas, int stream_kind) {
+                           const py::object& model, const py::dict& hyper, Tensor& status, Tensor& found_inf, int ctas, int stream_kind,
+                           uintptr_t mc_grads) {
     if (world < 1 || world > kMaxRanks) throw std::invalid_argument("peer reduce supports 1..8 ranks");
     if (static_cast<int>(grads.size()) != world || static_cast<int>(staging.size()) != world || static_cast<int>(flags.size()) != world)
       throw std::invalid_argument("peer reduce: one gradient, staging and flag pointer per rank is required");
@@ -400,6 +524,7 @@ void bind_peer(py::module_& m) {
       a.staging[s] = reinterpret_cast<float*>(staging[s]);
       a.flags[s] = reinterpret_cast<uint32_t*>(flags[s]);
     }
+    a.mc_grads = reinterpret_cast<void*>(mc_grads);
     a.n = n;
     a.per = (((n + world - 1) / world) + 7) & ~7LL;
     a.epoch = epoch;
@@ -440,16 +565,30 @@ void bind_peer(py::module_& m) {
     grid = static_cast<int>(std::max<long long>(1, std::min<long long>(grid, (vecs / world + kPeerThreads - 1) / kPeerThreads)));
     if (grid > kMaxCtas) grid = kMaxCtas;
     cudaStream_t st = pick_stream(device, stream_kind);
-    if (gd == DType::F32) peer_reduce_kernel<float><<<grid, kPeerThreads, 0, st>>>(a);
-    else if (gd == DType::BF16) peer_reduce_kernel<__nv_bfloat16><<<grid, kPeerThreads, 0, st>>>(a);
-    else if (gd == DType::F16) peer_reduce_kernel<__half><<<grid, kPeerThreads, 0, st>>>(a);
+#define OB_PEER_LAUNCH(GT)                                                                    \
+  do {                                                                                        \
+    if (world == 2) peer_reduce_kernel<GT, 2><<<grid, kPeerThreads, 0, st>>>(a);              \
+    else if (world == 4) peer_reduce_kernel<GT, 4><<<grid, kPeerThreads, 0, st>>>(a);         \
+    else if (world == 8) peer_reduce_kernel<GT, 8><<<grid, kPeerThreads, 0, st>>>(a);         \
+    else peer_reduce_kernel<GT, 0><<<grid, kPeerThreads, 0, st>>>(a);                         \
+  } while (0)
+    if (mc_grads != 0) {
+      // In-switch reduction and broadcast through the multicast mapping of the bucket.
+      if (gd == DType::F32) nvls_reduce_kernel<float><<<grid, kPeerThreads, 0, st>>>(a);
+      else if (gd == DType::BF16) nvls_reduce_kernel<__nv_bfloat16><<<grid, kPeerThreads, 0, st>>>(a);
+      else if (gd == DType::F16) nvls_reduce_kernel<__half><<<grid, kPeerThreads, 0, st>>>(a);
+      else throw std::invalid_argument("peer reduce: gradients must be float32, float16 or bfloat16");
+    } else if (gd == DType::F32) OB_PEER_LAUNCH(float);
+    else if (gd == DType::BF16) OB_PEER_LAUNCH(__nv_bfloat16);
+    else if (gd == DType::F16) OB_PEER_LAUNCH(__half);
     else throw std::invalid_argument("peer reduce: gradients must be float32, float16 or bfloat16");
+#undef OB_PEER_LAUNCH
     check_launch("peer reduce");
     return grid;
   }, py::arg("rank"), py::arg("world"), py::arg("device"), py::arg("grads"), py::arg("staging"), py::arg("flags"), py::arg("n"),
      py::arg("dtype"), py::arg("epoch"), py::arg("scale"), py::arg("mode"), py::arg("oneshot"), py::arg("master") = py::none(),
      py::arg("m") = py::none(), py::arg("v") = py::none(), py::arg("model") = py::none(), py::arg("hyper") = py::dict(),
-     py::arg("status"), py::arg("found_inf"), py::arg("ctas") = 0, py::arg("stream_kind") = 1);
+     py::arg("status"), py::arg("found_inf"), py::arg("ctas") = 0, py::arg("stream_kind") = 1, py::arg("mc_grads") = 0);
 }
 
 }  // namespace ob

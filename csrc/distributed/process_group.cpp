@@ -405,6 +405,7 @@ class NcclProcessGroup final : public ProcessGroup {
 }  // namespace dist
 
 void bind_peer(py::module_& m);
+void bind_vmm(py::module_& m);
 
 void bind_process_group(py::module_& m) {
   using namespace dist;
@@ -452,6 +453,7 @@ void bind_process_group(py::module_& m) {
     g_fake_log.fail_check = check ? 1 : 0;
   });
   bind_peer(m);
+  bind_vmm(m);
 }
 
 }  // namespace ob

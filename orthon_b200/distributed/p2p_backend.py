@@ -2,10 +2,16 @@
 
 Collectives on tensors run as the peer-memory reduction kernel over a symmetric staging region
 that every rank maps from every other rank (CUDA IPC): no NCCL call is made for all_reduce,
-broadcast or barrier.  NCCL is only created lazily for tensors larger than the staging region.
+broadcast or barrier; tensors larger than the staging region go through it in chunks.
 The DDP gradient path does not go through these generic collectives at all: PeerReducer keeps
-the gradients inside symmetric buckets and launches the fused kernel on them directly.
+the gradients inside symmetric buckets and launches the fused kernel on them directly.  Those
+buckets are cuMemCreate allocations shared through file descriptors and, where the devices
+support NVLink multicast, bound to one multicast object (`region.mc`) so the kernel can reduce
+and broadcast inside the NVSwitch (`multimem`); ORTHON_NVLS=0 keeps to plain peer mappings.
 """
+import json
+import os
+import socket
 import struct
 
 from .. import _C
@@ -26,8 +32,9 @@ def _no_grad():
 class SymmetricRegion:
     """`ptrs[r]` is rank r's copy of the region as mapped into this process."""
 
-    def __init__(self, nbytes, ptrs, rank):
+    def __init__(self, nbytes, ptrs, rank, mc=None):
         self.nbytes, self.ptrs, self.rank = nbytes, ptrs, rank
+        self.mc = mc  # multicast (NVLS) mapping of all copies, or None
 
     @property
     def local(self):
@@ -58,6 +65,8 @@ class PeerBackend(Backend):
         # One symmetric region: [staging grads | float32 staging | flags].
         self._stage = self.allocate_symmetric(STAGING_BYTES * 2 + _C._PEER_FLAG_BYTES)
         self._nccl = None
+        self._vmm = None  # decided collectively on first use
+        self._vmm = None  # decided collectively on first use
 
     rank = property(lambda self: self._rank)
     world_size = property(lambda self: self._world)
@@ -82,14 +91,135 @@ class PeerBackend(Backend):
                 self._store.delete(k)
         return out
 
-    def allocate_symmetric(self, nbytes):
-        """Collective: every rank allocates `nbytes` (zeroed) and maps everybody else's copy."""
+    def allocate_symmetric(self, nbytes, multicast=False):
+        """Collective: every rank allocates `nbytes` (zeroed) and maps everybody else's copy.
+
+        With `multicast=True` the copies are additionally bound to one NVLink multicast object
+        when every rank's device and driver support it (`region.mc` is then the multicast
+        pointer); otherwise `region.mc` is None and only the peer mappings exist."""
+        if multicast and self._world > 1 and self._vmm_enabled():
+            region = self._allocate_vmm(int(nbytes))
+            if region is not None:
+                return region
         nbytes = (int(nbytes) + 255) & ~255
         ptr, handle = _C._peer_alloc(nbytes, self._device)
         handles = self.exchange_objects(handle)
         ptrs = [ptr if r == self._rank else _C._peer_open(handles[r], self._device) for r in range(self._world)]
         self.exchange_objects(b"mapped")  # nobody touches a region before everyone has mapped it
         return SymmetricRegion(nbytes, ptrs, self._rank)
+
+    # ------------------------------------------------- shareable allocations
+    def _agree(self, ok):
+        """True only if every rank reports success (keeps the ranks on the same code path)."""
+        return all(v == b"ok" for v in self.exchange_objects(b"ok" if ok else b"no"))
+
+    def _vmm_enabled(self):
+        if self._vmm is None:
+            want = os.environ.get("ORTHON_NVLS", "1") != "0"
+            caps = _C._vmm_supported(self._device) if want else {"fd_handles": False, "multicast": False}
+            self._vmm = self._agree(bool(caps["fd_handles"]) and bool(caps["multicast"]))
+        return self._vmm
+
+    def _exchange_fds(self, fds):
+        """All-gather of file descriptors through a Unix socket owned by rank 0 (SCM_RIGHTS).
+        Returns, for every rank, this process's duplicates of that rank's descriptors."""
+        tag = f"p2p/fd/{self._generation}/{self._xseq}"
+        self._xseq += 1
+        if self._rank == 0:
+            name = f"\0orthon-b200-fd-{os.getpid()}-{self._generation}-{self._xseq}".encode()
+            srv = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+            srv.settimeout(RENDEZVOUS_TIMEOUT_SECONDS)
+            srv.bind(name)
+            srv.listen(self._world)
+            self._store.set(tag, name.hex().encode())
+            gathered, conns = {0: list(fds)}, []
+            try:
+                for _ in range(self._world - 1):
+                    conn, _ = srv.accept()
+                    conn.settimeout(RENDEZVOUS_TIMEOUT_SECONDS)
+                    msg, got, _, _ = socket.recv_fds(conn, 256, 16)
+                    head = json.loads(msg.decode())
+                    if len(got) != head["n"]:
+                        raise RuntimeError("file-descriptor exchange: truncated message")
+                    gathered[int(head["rank"])] = list(got)
+                    conns.append(conn)
+                counts = [len(gathered[r]) for r in range(self._world)]
+                flat = [fd for r in range(self._world) for fd in gathered[r]]
+                for conn in conns:
+                    socket.send_fds(conn, [json.dumps({"counts": counts}).encode()], flat)
+                    conn.recv(1)  # the peer has received its duplicates
+            finally:
+                for conn in conns:
+                    conn.close()
+                srv.close()
+                self._store.delete(tag)
+            return [gathered[r] for r in range(self._world)]
+        self._store.wait_for([tag], RENDEZVOUS_TIMEOUT_SECONDS)
+        name = bytes.fromhex(self._store.get(tag).decode())
+        cli = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+        cli.settimeout(RENDEZVOUS_TIMEOUT_SECONDS)
+        try:
+            cli.connect(name)
+            socket.send_fds(cli, [json.dumps({"rank": self._rank, "n": len(fds)}).encode()], list(fds))
+            msg, got, _, _ = socket.recv_fds(cli, 1024, 16 * self._world)
+            counts = json.loads(msg.decode())["counts"]
+            cli.send(b"k")
+        finally:
+            cli.close()
+        if len(got) != sum(counts):
+            raise RuntimeError("file-descriptor exchange: truncated reply")
+        out, pos = [], 0
+        for c in counts:
+            out.append(list(got[pos:pos + c]))
+            pos += c
+        return out
+
+    def _allocate_vmm(self, nbytes):
+        """cuMemCreate allocation per rank, mapped on every rank and bound to a multicast object.
+        Returns None (on every rank) if any step is unavailable, so the caller can fall back."""
+        dev, world, rank = self._device, self._world, self._rank
+        grans = self.exchange_objects(str(_C._vmm_granularity(dev, world, True)).encode())
+        gran = max(int(g) for g in grans)
+        size = (nbytes + gran - 1) // gran * gran
+        mine, mc_id, err = None, None, None
+        own_fds = []
+        try:
+            mine = _C._vmm_alloc(size, gran, dev)  # (id, ptr, fd)
+            own_fds.append(mine[2])
+            if rank == 0:
+                mc_id, mc_fd = _C._mc_create(world, size, dev)
+                own_fds.append(mc_fd)
+        except RuntimeError as exc:
+            err = exc
+        if not self._agree(err is None):
+            for fd in own_fds:
+                _C._close_fd(fd)
+            self._vmm = False
+            return None
+        every = self._exchange_fds(own_fds)
+        ptrs, ok = [], True
+        try:
+            for r in range(world):
+                ptrs.append(mine[1] if r == rank else _C._vmm_import(every[r][0], size, gran, dev)[1])
+            if rank != 0:
+                mc_id = _C._mc_import(every[0][1], size, dev)
+            _C._mc_add_device(mc_id, dev)
+        except RuntimeError:
+            ok = False
+        finally:
+            for fd in set(fd for row in every for fd in row) | set(own_fds):
+                _C._close_fd(fd)
+        if not self._agree(ok):  # also the "every device has been added" barrier
+            self._vmm = False
+            return None
+        mc_ptr = None
+        try:
+            mc_ptr = _C._mc_bind_map(mc_id, mine[0], gran, dev)
+        except RuntimeError:
+            ok = False
+        if not self._agree(ok):
+            mc_ptr = None  # peer mappings stay usable; only the multicast view is dropped
+        return SymmetricRegion(size, ptrs, rank, mc=mc_ptr)
 
     def next_epoch(self):
         self._epoch += 1
@@ -201,6 +331,7 @@ class PeerBackend(Backend):
             self.exchange_objects(b"bye")
         except Exception:  # noqa: BLE001
             pass
+        _C._vmm_release_all()
         _C._peer_release_all()
 
 

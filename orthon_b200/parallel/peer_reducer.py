@@ -14,7 +14,13 @@ the kernel's flag exchange (every rank must launch the same buckets in the same 
 holds for models whose parameters all receive gradients); a parameter without a local gradient
 contributes zeros and receives the average; in "update" mode every parameter must have a
 gradient.
+
+Buckets of at least NVLS_MIN_BYTES go through the in-switch (multimem) variant of the kernel
+when the backend could bind the buckets to an NVLink multicast object; smaller ones use the
+one-shot / two-shot peer-load variants.
 """
+import os
+
 from .. import _C
 from .reducer import _ELEMENT_BYTES, make_buckets
 
@@ -30,11 +36,12 @@ def _align(n, a):
 
 class _Bucket:
     __slots__ = ("entries", "offsets", "n", "dtype", "grads", "staging", "flags", "grad_flat", "ready", "launched",
-                 "param_flat", "master_flat", "m_flat", "v_flat", "seg", "seg_host")
+                 "param_flat", "master_flat", "m_flat", "v_flat", "seg", "seg_host", "mc")
 
 
 class PeerReducer:
     ONESHOT_BYTES = 512 << 10
+    NVLS_MIN_BYTES = int(os.environ.get("ORTHON_NVLS_MIN_BYTES", 1 << 20))  # smaller buckets use peer loads
 
     @staticmethod
     def eligible(parameters, group):
@@ -75,12 +82,13 @@ class PeerReducer:
             grad_bytes += _align(b.n * esz, 256)
             stage_bytes += _align(b.n * 4, 256)
         flag_bytes = _align(_C._PEER_FLAG_BYTES, 256)
-        region = self.backend.allocate_symmetric(grad_bytes + stage_bytes + flag_bytes * len(self.buckets))
+        region = self.backend.allocate_symmetric(grad_bytes + stage_bytes + flag_bytes * len(self.buckets), multicast=True)
         g_off, s_off, f_off = 0, grad_bytes, grad_bytes + stage_bytes
         for i, b in enumerate(self.buckets):
             b.grads = [ptr + g_off for ptr in region.ptrs]
             b.staging = [ptr + s_off for ptr in region.ptrs]
             b.flags = [ptr + f_off for ptr in region.ptrs]
+            b.mc = (region.mc + g_off) if getattr(region, "mc", None) else 0
             b.grad_flat = _C._tensor_from_ptr(b.grads[self.rank], [b.n], dtype, self.device)
             g_off += _align(b.n * esz, 256)
             s_off += _align(b.n * 4, 256)
@@ -115,7 +123,8 @@ class PeerReducer:
         scale = hyper.pop("grad_scale", 1.0) / self.world
         if b.seg is not None and self.mode != "average":
             hyper["seg_end"], hyper["seg_wd"] = b.seg
-        oneshot = b.n * _ELEMENT_BYTES[b.dtype] <= self.ONESHOT_BYTES
+        nbytes = b.n * _ELEMENT_BYTES[b.dtype]
+        oneshot = nbytes <= self.ONESHOT_BYTES
         status, found_inf = self.backend.status_tensors()
         _C._stream_fence(self.device, 0, 1)  # communication stream waits for the gradients
         fused = self.mode != "average"
@@ -124,7 +133,8 @@ class PeerReducer:
                         master=b.master_flat if fused else None, m=b.m_flat if self.mode == "adam" else None,
                         v=b.v_flat if self.mode == "adam" else None,
                         model=b.param_flat if (fused and b.param_flat is not None and b.master_flat is not b.param_flat) else None,
-                        hyper=hyper, status=status, found_inf=found_inf, stream_kind=1)
+                        hyper=hyper, status=status, found_inf=found_inf, stream_kind=1,
+                        mc_grads=b.mc if (b.mc and not oneshot and nbytes >= self.NVLS_MIN_BYTES) else 0)
         b.launched = True
         self.launch_count += 1
 

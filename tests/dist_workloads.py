@@ -112,3 +112,57 @@ def single_process_reference(world, steps, dtype="float32", optimizer="sgd", lr=
             p.set_grad(ob.from_numpy((g / world).astype(np.float32)))
         opt.step()
     return np.concatenate([p.numpy().reshape(-1) for p in params])
+
+
+def nvls_reduce(rank, backend, dtype, n):
+    """Kernel-level check of the in-switch (multimem) reducer against the peer-load reducer on
+    the same multicast-bound region.  Returns {"skipped": reason} where NVLS is unavailable."""
+    import os
+    os.environ["ORTHON_NVLS"] = "1"
+    import orthon_b200.distributed as dist
+    from orthon_b200 import _C
+    from orthon_b200.distributed import _state
+    be = _state.get_active().backend
+    ws = dist.get_world_size()
+    dev = f"cuda:{rank}"
+    esz = 4 if dtype == "float32" else 2
+    flag_bytes = (_C._PEER_FLAG_BYTES + 255) & ~255
+    region = be.allocate_symmetric(n * esz + n * 4 + flag_bytes, multicast=True)
+    if region.mc is None:
+        return {"skipped": "no multicast mapping on this box"}
+    grads = list(region.ptrs)
+    staging = [p + n * esz for p in region.ptrs]
+    flags = [p + n * esz + n * 4 for p in region.ptrs]
+    grad_t = _C._tensor_from_ptr(region.local, [n], dtype, rank)
+    status, found = be.status_tensors()
+    rng = np.random.default_rng(7)
+    base = rng.standard_normal(n).astype(np.float32)
+    out = {}
+
+    def fill():
+        grad_t._copy_flat_range_from(0, _C.from_numpy(base * (rank + 1), dtype).to(dev), 0, n)
+        _C.cuda_synchronize()
+        dist.barrier()
+
+    for name, mc in (("nvls", region.mc), ("peer", 0)):
+        fill()
+        _C._peer_reduce(rank, ws, rank, grads, staging, flags, n, dtype, be.next_epoch(), 1.0 / ws, "average", False,
+                        status=status, found_inf=found, stream_kind=0, mc_grads=mc)
+        _C.cuda_synchronize()
+        dist.barrier()
+        out[name] = np.asarray(grad_t.tolist(), dtype=np.float32)
+    # Fused Adam through the NVLS variant: one step from zero state.
+    fill()
+    master = _C._zeros_on([n], "float32", dev)
+    m, v = _C._zeros_on([n], "float32", dev), _C._zeros_on([n], "float32", dev)
+    model = None if dtype == "float32" else _C._zeros_on([n], dtype, dev)
+    _C._peer_reduce(rank, ws, rank, grads, staging, flags, n, dtype, be.next_epoch(), 1.0 / ws, "adam", False,
+                    master=master, m=m, v=v, model=model,
+                    hyper=dict(lr=1e-2, beta1=0.9, beta2=0.999, eps=1e-8, bias_c1=0.1, bias_c2=0.001),
+                    status=status, found_inf=found, stream_kind=0, mc_grads=region.mc)
+    _C.cuda_synchronize()
+    be.check_status()
+    dist.barrier()
+    expect = base * sum(r + 1 for r in range(ws)) / ws
+    return {"nvls": out["nvls"].tolist(), "peer": out["peer"].tolist(), "expect": expect.tolist(),
+            "master": master.tolist(), "found_inf": int(found.tolist()[0])}

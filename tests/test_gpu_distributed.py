@@ -61,3 +61,24 @@ def test_peer_amp_bf16_with_scaler():
         assert np.allclose(np.asarray(masters), ref, atol=0.05)
         assert np.allclose(np.asarray(model_vals), np.asarray(masters), atol=0.02)
     assert res[0][0] == res[1][0]
+
+
+@needs2
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_nvls_reducer_matches_peer_reducer(dtype):
+    n = 3 * (1 << 18) + 64  # not a multiple of the per-rank slice granularity
+    res = dist.spawn(W.nvls_reduce, args=("p2p", dtype, n), nprocs=2, backend="p2p")
+    if "skipped" in res[0]:
+        pytest.skip(res[0]["skipped"])
+    tol = 1e-6 if dtype == "float32" else 2e-2
+    for r in res:
+        expect = np.asarray(r["expect"], dtype=np.float32)
+        assert np.allclose(np.asarray(r["nvls"]), expect, atol=tol, rtol=tol)
+        assert np.allclose(np.asarray(r["peer"]), expect, atol=tol, rtol=tol)
+        assert r["found_inf"] == 0
+        # One Adam step from zero moments moves every weight by -lr * sign(g) (bias-corrected).
+        g = expect
+        step = np.asarray(r["master"], dtype=np.float32)
+        nz = np.abs(g) > 1e-2
+        assert np.allclose(step[nz], -1e-2 * np.sign(g[nz]), atol=2e-4)
+    assert res[0]["nvls"] == res[1]["nvls"]  # every rank holds the same bits

@@ -236,3 +236,25 @@ def test_adam_fused_matches_formula():
     opt.step()
     close(p, tp, "float32", 10)
     close(model, tp, "bfloat16")
+
+
+def test_diagnostic_routes():
+    from orthon_b200 import _diagnostics as diag
+    rng = np.random.default_rng(21)
+    a, b = rng.standard_normal((256, 192)), rng.standard_normal((192, 320))
+    xa, xb = dev_tensor(a, "bfloat16"), dev_tensor(b, "bfloat16")
+    ref = ref_round(a, "bfloat16") @ ref_round(b, "bfloat16")
+    close(diag.matmul_simt(xa, xb), ref, "bfloat16")
+    close(diag.matmul_tcgen05(xa, xb), ref, "bfloat16")
+    assert diag.matmul_dispatch_path(xa, xb) == "tcgen05_128x256"
+    assert diag.matmul_dispatch_path(dev_tensor(a, "float32"), dev_tensor(b, "float32")) == "simt"
+    with pytest.raises(RuntimeError):
+        diag.matmul_tcgen05(dev_tensor(a, "float32"), dev_tensor(b, "float32"))
+    x = rng.standard_normal((2, 8, 16, 16)); w = rng.standard_normal((16, 8, 3, 3)) * 0.2
+    xx, ww = dev_tensor(x, "bfloat16"), dev_tensor(w, "bfloat16")
+    y_direct = diag.conv2d_direct(xx, ww, None, (1, 1), (1, 1))
+    assert _C._conv2d_last_route() == "direct"
+    assert diag.conv2d_dispatch_path(xx, ww, None, (1, 1), (1, 1)) == "tcgen05_lowering"
+    y_auto = _C.conv2d(xx, ww, None, 1, 1, 1, 1)
+    ty = torch.nn.functional.conv2d(ref_round(x, "bfloat16"), ref_round(w, "bfloat16"), padding=1)
+    close(y_direct, ty, "bfloat16"); close(y_auto, ty, "bfloat16")
