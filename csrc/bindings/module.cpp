@@ -488,6 +488,11 @@ PYBIND11_MODULE(_C, m) {
     return std::string(names[cu::last_conv_route() & 3]);
   });
   m.def("_attention_qkv_fused", [](const Tensor& qkv, int64_t heads) { return cu::flash_attention_supported(qkv, heads); });
+  m.def("_mlp_gelu", [](const Tensor& x, const Tensor& w1, const py::object& b1, const Tensor& w2, const py::object& b2,
+                        const py::object& residual) {
+    auto opt = [](const py::object& o) { return o.is_none() ? Tensor() : o.cast<Tensor>(); };
+    return ops::mlp_gelu(x, w1, opt(b1), w2, opt(b2), opt(residual));
+  }, py::arg("x"), py::arg("w1"), py::arg("b1"), py::arg("w2"), py::arg("b2"), py::arg("residual") = py::none());
   m.def("_gemm", &ops::gemm, py::arg("a"), py::arg("trans_a"), py::arg("b"), py::arg("trans_b"));
   m.def("isfinite_all", &ops::isfinite_all);
   m.def("_isfinite_into", [](const Tensor& t, Tensor& flag) { ops::isfinite_into(t, flag); });

@@ -135,10 +135,16 @@ void linear_cpu(OpCall& c) {
       }
       for (int64_t j = 0; j < N; ++j) {
         T v = row[j];
-        if (pz) pz[i * N + j] = v;
+        if (pz)  // act 4 keeps the GELU derivative for the backward pass instead of the pre-activation
+          pz[i * N + j] = act == 4 ? T(0.5) * (T(1) + std::erf(v * T(0.70710678118654752440))) +
+                                         v * T(0.39894228040143267794) * std::exp(T(-0.5) * v * v)
+                                   : v;
         if (act == 1) v = v > T(0) ? v : T(0);
-        else if (act == 2) v = T(0.5) * v * (T(1) + std::erf(v * T(0.70710678118654752440)));
-        if (res.defined()) v += res.data_as<T>()[i * N + j];
+        else if (act == 2 || act == 4) v = T(0.5) * v * (T(1) + std::erf(v * T(0.70710678118654752440)));
+        if (res.defined()) {
+          const T aux = res.data_as<T>()[i * N + j];
+          v = act == 3 ? v * aux : v + aux;  // act 3: aux is a stored activation derivative
+        }
         py[i * N + j] = v;
       }
     }

@@ -88,6 +88,11 @@ __device__ __forceinline__ float apply_act(float v, int act) {
   return v;
 }
 
+// d/dz of 0.5 z (1 + erf(z / sqrt 2)).
+__device__ __forceinline__ float gelu_grad(float z) {
+  return 0.5f * (1.f + erff(z * 0.70710678118654752f)) + z * 0.3989422804014327f * __expf(-0.5f * z * z);
+}
+
 template <class T, int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -254,13 +259,13 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
           __syncwarp();
         }
-        auto emit = [&](T* base, uint8_t* tile, bool is_z) {
+        auto emit = [&](T* base, uint8_t* tile, bool is_z, const float* vals) {
           if (staged) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               Pack<T> pk;
 #pragma unroll
-              for (int j = 0; j < 8; ++j) pk.v[j] = from_f<T>(v[q * 8 + j]);
+              for (int j = 0; j < 8; ++j) pk.v[j] = from_f<T>(vals[q * 8 + j]);
               *reinterpret_cast<uint4*>(tile + lane * 128 + (((half * 4 + q) ^ (lane & 7)) << 4)) = *reinterpret_cast<uint4*>(&pk);
             }
             if (half == 1 || col0 + 32 >= p.N) {
@@ -278,14 +283,14 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (col0 + q * 8 < p.N) {
                   Pack<T> pk;
 #pragma unroll
-                  for (int j = 0; j < 8; ++j) pk.v[j] = from_f<T>(v[q * 8 + j]);
+                  for (int j = 0; j < 8; ++j) pk.v[j] = from_f<T>(vals[q * 8 + j]);
                   store_pack(base + c_off + col0 + q * 8, pk);
                 }
               }
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) base[c_off + col0 + j] = from_f<T>(v[j]);
+                if (col0 + j < p.N) base[c_off + col0 + j] = from_f<T>(vals[j]);
             }
           }
         };
@@ -308,31 +313,52 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               if (col0 + j < p.N) v[j] += to_f(bias[col0 + j]);
           }
         }
-        if (Zb) emit(Zb, ebuf, true);
-        if (p.act == 1) {
+        if (p.act == 4) {
+          // GELU forward that also returns its derivative (kept for the backward pass in place of
+          // the pre-activation): one erf serves both.
+          float d[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
-        } else if (p.act == 2) {
+          for (int j = 0; j < 32; ++j) {
+            const float cdf = 0.5f * (1.f + erff(v[j] * 0.70710678118654752f));
+            d[j] = cdf + v[j] * 0.3989422804014327f * __expf(-0.5f * v[j] * v[j]);
+            v[j] *= cdf;
+          }
+          if (Zb) emit(Zb, ebuf, true, d);
+        } else {
+          if (Zb) emit(Zb, ebuf, true, v);
+          if (p.act == 1) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = 0.5f * v[j] * (1.f + erff(v[j] * 0.70710678118654752f));
+            for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
+          } else if (p.act == 2) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0.5f * v[j] * (1.f + erff(v[j] * 0.70710678118654752f));
+          }
         }
         if (Rb && row_ok) {
+          // act 3: the result is acc * aux (aux = stored activation derivative: the input gradient
+          // of a GELU MLP); otherwise aux is a residual that is added.
+          float aux[32];
           if (vec) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              if (col0 + q * 8 < p.N) {
-                Pack<T> pr = load_pack(Rb + r_off + col0 + q * 8);
+              Pack<T> pr;
+              if (col0 + q * 8 < p.N) pr = load_pack(Rb + r_off + col0 + q * 8);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) v[q * 8 + j] += to_f(pr.v[j]);
-              }
+              for (int j = 0; j < 8; ++j) aux[q * 8 + j] = (col0 + q * 8 < p.N) ? to_f(pr.v[j]) : 0.f;
             }
           } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) v[j] += to_f(Rb[r_off + col0 + j]);
+            for (int j = 0; j < 32; ++j) aux[j] = (col0 + j < p.N) ? to_f(Rb[r_off + col0 + j]) : 0.f;
+          }
+          if (p.act == 3) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= aux[j];
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += aux[j];
           }
         }
-        emit(Cb, Zb ? ebuf + 4096 : ebuf + buf * 4096, false);
+        emit(Cb, Zb ? ebuf + 4096 : ebuf + buf * 4096, false, v);
         if (staged && !Zb && (half == 1 || col0 + 32 >= p.N)) buf ^= 1;
       }
       tc_fence_before();
@@ -398,9 +424,12 @@ __global__ void gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ 
       if (gm < M && gn < N) {
         float x = acc[i][j];
         if (bias) x += to_f(bias[bias_rows ? gm : gn]);
-        if (preact) preact[c_base + gm * ldc + gn] = from_f<T>(x);
-        x = apply_act(x, act);
-        if (residual) x += to_f(residual[r_base + gm * ldr + gn]);
+        if (preact) preact[c_base + gm * ldc + gn] = from_f<T>(act == 4 ? gelu_grad(x) : x);
+        x = apply_act(x, act == 4 ? 2 : act);
+        if (residual) {
+          const float aux = to_f(residual[r_base + gm * ldr + gn]);
+          x = (act == 3) ? x * aux : x + aux;
+        }
         C[c_base + gm * ldc + gn] = from_f<T>(x);
       }
     }

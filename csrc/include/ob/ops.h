@@ -78,6 +78,9 @@ enum class Act : int { None = 0, Relu = 1, Gelu = 2 };
 // y = act(x @ w + b) (+ residual).  x [..., in], w [in, out], b [out] or undefined.
 Tensor linear(const Tensor& x, const Tensor& w, const Tensor& b, Act act, const Tensor& residual);
 Tensor fused_linear_relu(const Tensor& x, const Tensor& w, const Tensor& b);
+// gelu(x @ w1 + b1) @ w2 + b2 (+ residual) as one autograd node: the backward multiplies by
+// gelu'(pre-activation) inside the epilogue of the input-gradient GEMM.
+Tensor mlp_gelu(const Tensor& x, const Tensor& w1, const Tensor& b1, const Tensor& w2, const Tensor& b2, const Tensor& residual);
 // Low-level GEMM used by formulas: C = op(A) @ op(B), 2-D or batched 3-D operands.
 Tensor gemm(const Tensor& a, bool trans_a, const Tensor& b, bool trans_b);
 

@@ -177,6 +177,83 @@ Tensor linear(const Tensor& x, const Tensor& w, const Tensor& b, Act act, const 
   return out;
 }
 
+namespace {
+// One raw Linear kernel call: y = act(x2 @ w + b) (+ aux), optional pre-activation output.
+// act 3 multiplies by aux instead of adding it; act 4 is GELU whose second output is the
+// derivative gelu'(pre-activation) instead of the pre-activation.
+void linear_raw(const Tensor& x2, const Tensor& w, const Tensor& b, int act, const Tensor& aux, Tensor& y, Tensor* preact) {
+  OpCall c;
+  c.in[0] = x2;
+  c.in[1] = w;
+  if (b.defined()) c.in[2] = b;
+  if (aux.defined()) c.in[3] = aux;
+  c.out[0] = y;
+  if (preact) c.out[1] = *preact;
+  c.i[0] = act;
+  run_kernel(OperatorId::Linear, x2.device(), x2.dtype(), c, w.is_contiguous() ? kContiguous : kStrided);
+}
+
+struct MlpNode : Node {
+  Tensor x2, w1, w2, z, h;
+  bool has_b1, has_b2, has_res;
+  Shape x_shape;
+  const char* name() const override { return "MlpGeluNode"; }
+  std::vector<Tensor> backward(const Tensor& g) override {
+    const int64_t E = w2.shape()[1], F = w1.shape()[1];
+    Tensor g2 = reshape(contiguous(g), {-1, E});
+    // dz = (g @ w2^T) * gelu'(z) in one GEMM (z holds the derivative saved by the forward).
+    Tensor dz = Tensor::empty({g2.shape()[0], F}, g2.dtype(), g2.device());
+    linear_raw(g2, transpose(w2, 0, 1), Tensor(), 3, z, dz, nullptr);
+    Tensor dw2 = gemm_raw(h, true, g2, false);
+    Tensor dx = reshape(gemm_raw(dz, false, w1, true), x_shape);
+    Tensor dw1 = gemm_raw(x2, true, dz, false);
+    std::vector<Tensor> out{dx, dw1, has_b1 ? sum(dz, 0, false) : Tensor(), dw2, has_b2 ? sum(g2, 0, false) : Tensor(),
+                            has_res ? g : Tensor()};
+    return out;
+  }
+  void release_saved() override { x2 = Tensor(); w1 = Tensor(); w2 = Tensor(); z = Tensor(); h = Tensor(); }
+};
+}  // namespace
+
+Tensor mlp_gelu(const Tensor& x, const Tensor& w1, const Tensor& b1, const Tensor& w2, const Tensor& b2, const Tensor& residual) {
+  if (!needs_graph({x, w1, b1, w2, b2, residual}))
+    return linear(linear(x, w1, b1, Act::Gelu, Tensor()), w2, b2, Act::None, residual);
+  check_same_device(x, w1, "mlp_gelu");
+  check_same_device(x, w2, "mlp_gelu");
+  check_same_dtype(x, w1, "mlp_gelu");
+  check_same_dtype(x, w2, "mlp_gelu");
+  if (w1.ndim() != 2 || w2.ndim() != 2 || x.ndim() < 1 || x.shape().back() != w1.shape()[0] || w1.shape()[1] != w2.shape()[0])
+    throw std::invalid_argument("mlp_gelu: expected x [..., in], w1 [in, hidden], w2 [hidden, out]");
+  const int64_t K = w1.shape()[0], F = w1.shape()[1], E = w2.shape()[1];
+  if ((b1.defined() && (b1.ndim() != 1 || b1.shape()[0] != F)) || (b2.defined() && (b2.ndim() != 1 || b2.shape()[0] != E)))
+    throw std::invalid_argument("mlp_gelu: bias shapes must be [hidden] and [out]");
+  Shape os(x.shape().begin(), x.shape().end() - 1);
+  os.push_back(E);
+  if (residual.defined() && residual.shape() != os) throw std::invalid_argument("mlp_gelu: residual shape must match the output");
+  default_dispatcher().check_dtype(OperatorId::Linear, x.device(), x.dtype());
+  Tensor x2 = reshape(contiguous(x.detach()), {-1, K});
+  const int64_t M = x2.shape()[0];
+  Tensor z = Tensor::empty({M, F}, x.dtype(), x.device()), h = Tensor::empty({M, F}, x.dtype(), x.device());
+  Tensor out = Tensor::empty(os, x.dtype(), x.device());
+  Tensor w1c = w1.detach(), w2c = w2.detach();
+  if (out.numel()) {
+    linear_raw(x2, w1c, b1.defined() ? b1.detach() : Tensor(), 4, Tensor(), h, &z);
+    Tensor out2 = Tensor::view_of(out, Layout(Shape{M, E}));
+    linear_raw(h, w2c, b2.defined() ? b2.detach() : Tensor(), 0,
+               residual.defined() ? reshape(contiguous(residual.detach()), {M, E}) : Tensor(), out2, nullptr);
+  }
+  auto n = std::make_shared<MlpNode>();
+  n->x2 = x2; n->w1 = w1c; n->w2 = w2c; n->z = z; n->h = h;
+  n->has_b1 = b1.defined(); n->has_b2 = b2.defined(); n->has_res = residual.defined();
+  n->x_shape = x.shape();
+  n->watch_version(x, "input");
+  n->watch_version(w1, "first weight");
+  n->watch_version(w2, "second weight");
+  n->set_inputs({x, w1, b1, w2, b2, residual});
+  attach(out, n);
+  return out;
+}
+
 Tensor fused_linear_relu(const Tensor& x, const Tensor& w, const Tensor& b) {
   if (x.ndim() != 2) throw std::invalid_argument("fused_linear_relu: input must be 2-D");
   return linear(x, w, b, Act::Relu, Tensor());

@@ -54,8 +54,7 @@ class Block(nn.Module):
         a = _C._attention_qkv(qkv, self.n_heads, None, True, self.scale)
         x = _C.linear(a, self.proj_weight, self.proj_bias, "none", x)
         h = self.ln2(x)
-        h = _C.linear(h, self.fc1_weight, self.fc1_bias, "gelu")
-        return _C.linear(h, self.fc2_weight, self.fc2_bias, "none", x)
+        return _C._mlp_gelu(h, self.fc1_weight, self.fc1_bias, self.fc2_weight, self.fc2_bias, x)
 
 
 class CausalLM(nn.Module):

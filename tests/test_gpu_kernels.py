@@ -258,3 +258,21 @@ def test_diagnostic_routes():
     y_auto = _C.conv2d(xx, ww, None, 1, 1, 1, 1)
     ty = torch.nn.functional.conv2d(ref_round(x, "bfloat16"), ref_round(w, "bfloat16"), padding=1)
     close(y_direct, ty, "bfloat16"); close(y_auto, ty, "bfloat16")
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_fused_mlp_gelu(dtype):
+    rng = np.random.default_rng(31)
+    M, E, F = 384, 256, 512
+    arrs = [rng.standard_normal((M, E)), rng.standard_normal((E, F)) * 0.05, rng.standard_normal((F,)) * 0.1,
+            rng.standard_normal((F, E)) * 0.05, rng.standard_normal((E,)) * 0.1]
+    xs = [dev_tensor(a, dtype, True) for a in arrs]
+    ts = [ref_round(a, dtype).requires_grad_(True) for a in arrs]
+    y = _C._mlp_gelu(xs[0], xs[1], xs[2], xs[3], xs[4], xs[0])
+    ty = torch.nn.functional.gelu(ts[0] @ ts[1] + ts[2]) @ ts[3] + ts[4] + ts[0]
+    close(y, ty, dtype, 2)
+    w = rng.standard_normal((M, E))
+    (y * dev_tensor(w, dtype)).sum().backward()
+    (ty * ref_round(w, dtype)).sum().backward()
+    for g, tg in zip(xs, ts):
+        close(g.grad, tg.grad, dtype, 8)

@@ -214,3 +214,28 @@ def test_mixed_precision_optimizer_cpu():
     before = next(iter(m.parameters())).tolist()
     scaler.step(opt)
     assert scaler.found_inf and scaler.scale_factor == 64.0 and next(iter(m.parameters())).tolist() == before
+
+
+def test_fused_mlp_matches_composed_linears():
+    """_mlp_gelu (one node, GELU gradient inside the input-gradient GEMM) against two linears."""
+    import numpy as np
+    from orthon_b200 import _C
+    rng = np.random.default_rng(3)
+    x_np = rng.standard_normal((5, 7, 12)).astype(np.float32)
+    w1_np, b1_np = rng.standard_normal((12, 20)).astype(np.float32) * 0.3, rng.standard_normal(20).astype(np.float32)
+    w2_np, b2_np = rng.standard_normal((20, 12)).astype(np.float32) * 0.3, rng.standard_normal(12).astype(np.float32)
+
+    def run(fused):
+        ts = [_C.from_numpy(a) for a in (x_np, w1_np, b1_np, w2_np, b2_np)]
+        for t in ts:
+            t.requires_grad_(True)
+        x, w1, b1, w2, b2 = ts
+        if fused:
+            y = _C._mlp_gelu(x, w1, b1, w2, b2, x)
+        else:
+            y = _C.linear(_C.linear(x, w1, b1, "gelu"), w2, b2, "none", x)
+        (y * y).sum().backward()
+        return [np.asarray(y.tolist())] + [np.asarray(t.grad.tolist()) for t in ts]
+
+    for a, b in zip(run(True), run(False)):
+        assert np.allclose(a, b, rtol=1e-5, atol=1e-5)
