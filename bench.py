@@ -2,7 +2,7 @@
 
     python bench.py --gpus N --steps K --warmup W [--impl ours|reference] [--model 1p3b|tiny|cnn]
 
-Model / config (BASELINE config 4): vocab 32000, d_model 2048, 24 layers, 16 heads, FFN 8192
+Model / config (the 1.3 B headline configuration): vocab 32000, d_model 2048, 24 layers, 16 heads, FFN 8192
 GELU, pre-LayerNorm, learned positions, seq 1024, batch 8 per GPU, bf16 compute with FP32-master
 Adam, DDP with 25 MB gradient buckets.  Token ids are uniform in [0, vocab); weights N(0, 0.02).
 Synthetic data, random-init weights.

@@ -144,7 +144,7 @@ def run_cnn(args):
             os.environ["ORTHON_NCCL_STORE_DIR"] = store
             dist.init_process_group("nccl", rank=rank, world_size=world, device=local)
         else:
-            dist.init_process_group()
+            dist.init_process_group("p2p", rank=rank, world_size=world, device=local)
     fw.manual_seed(0)
     model = build_cnn(fw)
     model.cast("bfloat16")

@@ -76,6 +76,53 @@ __global__ void col_sum_kernel(const T* __restrict__ in, float* __restrict__ par
   }
 }
 
+// Same reduction with 16-byte loads: every thread owns Pack<T>::N adjacent columns, a warp covers
+// 32 * N columns of one row (full 128-byte lines), 8 rows per block step, 4 steps in flight.
+// Requires inner % N == 0 and a 16-byte aligned input.
+template <class T>
+__global__ void col_sum_vec_kernel(const T* __restrict__ in, float* __restrict__ partial, T* __restrict__ out,
+                                   int64_t reduce, int64_t inner, int64_t chunk, int splits, float scale) {
+  constexpr int N = Pack<T>::N;
+  __shared__ float tile[8][32][N + 1];
+  const int64_t o = blockIdx.z;
+  const int s = blockIdx.y;
+  const int64_t k0 = (static_cast<int64_t>(blockIdx.x) * 32 + threadIdx.x) * N;
+  const int64_t begin = static_cast<int64_t>(s) * chunk;
+  int64_t end = begin + chunk;
+  if (end > reduce) end = reduce;
+  float acc[N];
+#pragma unroll
+  for (int j = 0; j < N; ++j) acc[j] = 0.f;
+  if (k0 < inner) {
+    const T* base = in + o * reduce * inner + k0;
+    int64_t r = begin + threadIdx.y;
+    for (; r + 24 < end; r += 32) {
+      Pack<T> p0 = load_pack(base + r * inner), p1 = load_pack(base + (r + 8) * inner), p2 = load_pack(base + (r + 16) * inner),
+              p3 = load_pack(base + (r + 24) * inner);
+#pragma unroll
+      for (int j = 0; j < N; ++j) acc[j] += (to_f(p0.v[j]) + to_f(p1.v[j])) + (to_f(p2.v[j]) + to_f(p3.v[j]));
+    }
+    for (; r < end; r += 8) {
+      Pack<T> p0 = load_pack(base + r * inner);
+#pragma unroll
+      for (int j = 0; j < N; ++j) acc[j] += to_f(p0.v[j]);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < N; ++j) tile[threadIdx.y][threadIdx.x][j] = acc[j];
+  __syncthreads();
+  if (threadIdx.y == 0 && k0 < inner) {
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      float total = 0.f;
+#pragma unroll
+      for (int y = 0; y < 8; ++y) total += tile[y][threadIdx.x][j];
+      if (splits == 1) out[o * inner + k0 + j] = from_f<T>(total * scale);
+      else partial[(o * splits + s) * inner + k0 + j] = total;
+    }
+  }
+}
+
 template <class T>
 __global__ void finalize_sum_kernel(const float* __restrict__ partial, T* __restrict__ out, int64_t outer,
                                     int64_t inner, int splits, float scale) {
@@ -122,7 +169,9 @@ void sum_launch(const T* in, T* out, int64_t outer, int64_t reduce, int64_t inne
     check_launch("row sum (split)");
     return;
   }
-  const int64_t col_blocks = (inner + 31) / 32;
+  constexpr int VN = Pack<T>::N;
+  const bool vec = VN > 1 && inner % VN == 0 && (reinterpret_cast<uintptr_t>(in) & 15u) == 0;
+  const int64_t col_blocks = vec ? (inner + 32 * VN - 1) / (32 * VN) : (inner + 31) / 32;
   int64_t want = (static_cast<int64_t>(sms) * 4 + col_blocks * outer - 1) / (col_blocks * outer);
   int64_t max_splits = (reduce + 63) / 64;
   int splits = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(std::min(want, max_splits), 512)));
@@ -131,13 +180,15 @@ void sum_launch(const T* in, T* out, int64_t outer, int64_t reduce, int64_t inne
   if (outer > 65535) throw std::invalid_argument("sum: outer extent too large for a strided reduction");
   dim3 grid(static_cast<unsigned>(col_blocks), static_cast<unsigned>(splits), static_cast<unsigned>(outer));
   if (splits == 1) {
-    col_sum_kernel<T><<<grid, dim3(32, 8), 0, st>>>(in, nullptr, out, reduce, inner, chunk, 1, scale);
+    if (vec) col_sum_vec_kernel<T><<<grid, dim3(32, 8), 0, st>>>(in, nullptr, out, reduce, inner, chunk, 1, scale);
+    else col_sum_kernel<T><<<grid, dim3(32, 8), 0, st>>>(in, nullptr, out, reduce, inner, chunk, 1, scale);
     check_launch("column sum");
     return;
   }
   ScratchLease lease(ref.device(), sizeof(float) * outer * splits * inner, st);
   float* partial = static_cast<float*>(lease.data());
-  col_sum_kernel<T><<<grid, dim3(32, 8), 0, st>>>(in, partial, out, reduce, inner, chunk, splits, scale);
+  if (vec) col_sum_vec_kernel<T><<<grid, dim3(32, 8), 0, st>>>(in, partial, out, reduce, inner, chunk, splits, scale);
+  else col_sum_kernel<T><<<grid, dim3(32, 8), 0, st>>>(in, partial, out, reduce, inner, chunk, splits, scale);
   finalize_sum_kernel<T><<<ew_grid(outer * inner, kThreads, sms), kThreads, 0, st>>>(partial, out, outer, inner, splits, scale);
   check_launch("column sum (split)");
 }

@@ -636,7 +636,20 @@ void gemm_dispatch(const Tensor& A_in, bool ta, const Tensor& B_in, bool tb, Ten
   }
   const bool a_mn = !(a.s_k == 1 || (a.k == 1 && a.s_mn != 1));
   const bool b_mn = !(b.s_k == 1 || (b.k == 1 && b.s_mn != 1));
-  const bool wide = N > 128;
+  // Tile width: 256 columns halve the A-operand traffic per flop, 128 columns give twice as many
+  // tiles; take the narrower tile when the wider one would leave a large part of the last wave
+  // of the persistent grid idle.
+  bool wide = N > 128;
+  if (wide) {
+    static const int force_bn = [] { const char* e = std::getenv("ORTHON_GEMM_BN"); return e ? std::atoi(e) : 0; }();
+    const long long sms = sm_count_for(C);
+    auto wave_eff = [&](int bn) {
+      const long long tiles = static_cast<long long>((M + BM - 1) / BM) * ((N + bn - 1) / bn) * nb0 * nb1;
+      return static_cast<double>(tiles) / static_cast<double>(((tiles + sms - 1) / sms) * sms);
+    };
+    if (force_bn == 128) wide = false;
+    else if (force_bn != 256 && wave_eff(128) * 0.93 > wave_eff(256)) wide = false;
+  }
   g_last_route.store(wide ? 3 : 2, std::memory_order_relaxed);
   if (dt == DType::BF16) {
     if (wide) launch_tc05<__nv_bfloat16, 256>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);

@@ -1,5 +1,5 @@
 """Small CNN on synthetic 3x32x32 images, bf16 AMP with a disabled GradScaler, DDP over every
-visible GPU through the peer-memory transport (BASELINE configuration 2).
+visible GPU through the peer-memory transport.
 
     python -m orthon_b200.distributed.run --nproc_per_node 2 --backend p2p examples/ddp_cnn_amp.py
     python examples/ddp_cnn_amp.py            # single GPU

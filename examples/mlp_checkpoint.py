@@ -1,5 +1,5 @@
 """MLP 784-256-128-10 on synthetic data: three SGD steps on the CPU, the same steps with
-two local DDP ranks, then a checkpoint round trip (BASELINE configuration 1).
+two local DDP ranks, then a checkpoint round trip.
 
     python examples/mlp_checkpoint.py
 """
