@@ -71,14 +71,17 @@ struct GemmParams {
   int* err;
 };
 
-template <int BN>
+// TM = rows of the CTA tile: 128 (one MMA row block, accumulators double-buffered across tiles) or
+// 256 (two MMA row blocks share every B stage, which halves the B bytes fetched per flop; the two
+// accumulators are drained one after the other so the next tile can start on the first).
+template <int BN, int TM>
 struct SmemLayout {
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
-  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kABytes = TM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBarrierBytes = 256;
   static constexpr int kEpiBytes = kEpilogueWarps * 2 * 4096;  // two 32x64 staging tiles per epilogue warp
+  static constexpr int kStages = (232448 - kEpiBytes - 256 - 1024) / kStageBytes > 6 ? 6 : (232448 - kEpiBytes - 256 - 1024) / kStageBytes;
+  static constexpr int kBarrierBytes = 256;
   static constexpr int kTotal = kStages * kStageBytes + kEpiBytes + kBarrierBytes + 1024;  // +1024 for manual alignment
 };
 
@@ -93,11 +96,12 @@ __device__ __forceinline__ float gelu_grad(float z) {
   return 0.5f * (1.f + erff(z * 0.70710678118654752f)) + z * 0.3989422804014327f * __expf(-0.5f * z * z);
 }
 
-template <class T, int BN>
+template <class T, int BN, int TM>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_z, GemmParams p) {
-  using L = SmemLayout<BN>;
+  using L = SmemLayout<BN, TM>;
+  constexpr int H = TM / BM;  // MMA row blocks per tile
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_smem = smem + L::kStages * L::kStageBytes;
@@ -108,10 +112,13 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+  const int tiles_m = (p.M + TM - 1) / TM, tiles_n = (p.N + BN - 1) / BN;
   const int tiles_per_batch = tiles_m * tiles_n;
   const long long total_tiles = static_cast<long long>(tiles_per_batch) * p.nb0 * p.nb1;
   const int num_kb = (p.K + BK - 1) / BK;
+  // Accumulator slot and use count of row block h of this CTA's it-th tile.
+  auto slot_of = [](int it, int h) { return H == 1 ? (it & 1) : h; };
+  auto use_of = [](int it) { return H == 1 ? (it >> 1) : it; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < L::kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -156,10 +163,10 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           uint8_t* sb = sa + L::kABytes;
           const int k0 = kb * BK;
           if (!p.a_mn) {
-            tma_load_4d(sa, &map_a, &full_bar[stage], k0, tm * BM, a1, a0);
+            tma_load_4d(sa, &map_a, &full_bar[stage], k0, tm * TM, a1, a0);
           } else {
 #pragma unroll
-            for (int c = 0; c < BM / 64; ++c) tma_load_4d(sa + c * (BK * 128), &map_a, &full_bar[stage], tm * BM + c * 64, k0, a1, a0);
+            for (int c = 0; c < TM / 64; ++c) tma_load_4d(sa + c * (BK * 128), &map_a, &full_bar[stage], tm * TM + c * 64, k0, a1, a0);
           }
           if (!p.b_mn) {
             tma_load_4d(sb, &map_b, &full_bar[stage], k0, tn * BN, c1, c0);
@@ -184,25 +191,36 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       bool ok = true;
       int it = 0;
       for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
-        const int acc = it & 1;
-        if (!mbar_wait(&tmem_empty[acc], ((it >> 1) & 1) ^ 1, p.err, kErrMma)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t tmem_d = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const uint32_t empty_parity = (use_of(it) & 1) ^ 1;
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, p.err, kErrMma)) { ok = false; break; }
           tc_fence_after();
+          if (kb == 0) {  // the accumulators must have been drained by the epilogue
+#pragma unroll
+            for (int h = 0; h < H; ++h)
+              if (ok && !mbar_wait(&tmem_empty[slot_of(it, h)], empty_parity, p.err, kErrMma)) ok = false;
+            if (!ok) break;
+            tc_fence_after();
+          }
           const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
           const uint32_t sb = sa + L::kABytes;
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t da = p.a_mn ? make_desc(sa + k * 2048, BK * 128, 1024) : make_desc(sa + k * 32, 16, 1024);
             const uint64_t db = p.b_mn ? make_desc(sb + k * 2048, BK * 128, 1024) : make_desc(sb + k * 32, 16, 1024);
-            umma_f16(tmem_d, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+            for (int h = 0; h < H; ++h) {
+              const uint32_t sah = sa + h * (BM * BK * 2);  // 128 rows further in either operand major
+              const uint64_t da = p.a_mn ? make_desc(sah + k * 2048, BK * 128, 1024) : make_desc(sah + k * 32, 16, 1024);
+              umma_f16(tmem_base + slot_of(it, h) * BN, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            }
           }
           umma_commit(&empty_bar[stage]);  // frees the slot once these MMAs have read it
           if (++stage == L::kStages) { stage = 0; phase ^= 1; }
         }
-        if (ok) umma_commit(&tmem_full[acc]);
+        if (ok) {
+#pragma unroll
+          for (int h = 0; h < H; ++h) umma_commit(&tmem_full[slot_of(it, h)]);
+        }
       }
     }
   } else {
@@ -233,10 +251,12 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       int bidx, tm, tn;
       decode_tile(t, bidx, tm, tn);
       const int b0 = bidx / p.nb1, b1 = bidx - b0 * p.nb1;
-      const int acc = it & 1;
-      if (!mbar_wait(&tmem_full[acc], (it >> 1) & 1, p.err, kErrEpilogue)) { ok = false; break; }
+#pragma unroll 1
+      for (int h = 0; h < H && ok; ++h) {
+      const int acc = slot_of(it, h);
+      if (!mbar_wait(&tmem_full[acc], use_of(it) & 1, p.err, kErrEpilogue)) { ok = false; break; }
       tc_fence_after();
-      const int row0 = tm * BM + quarter * 32;
+      const int row0 = tm * TM + h * BM + quarter * 32;
       const int row = row0 + lane;
       const bool row_ok = row < p.M;
       const long long c_off = b0 * p.c_bs0 + b1 * p.c_bs1 + static_cast<long long>(row) * p.ldc;
@@ -364,6 +384,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      }  // row block
     }
     if (staged) {
       if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -527,12 +548,12 @@ void launch_simt(const OperandView& a, const OperandView& b, Tensor& C, int M, i
   check_launch("gemm (SIMT)");
 }
 
-template <class T, int BN>
+template <class T, int BN, int TM>
 void launch_tc05(const OperandView& a, const OperandView& b, bool a_mn, bool b_mn, Tensor& C, int M, int N, int K,
                  int nb0, int nb1, long long ldc, long long c_bs0, long long c_bs1, const Epilogue& ep, cudaStream_t st) {
-  using L = SmemLayout<BN>;
+  using L = SmemLayout<BN, TM>;
   const DType dt = C.dtype();
-  const CUtensorMap ma = make_map(a, a_mn, BM, nb0, nb1, dt);
+  const CUtensorMap ma = make_map(a, a_mn, TM, nb0, nb1, dt);
   const CUtensorMap mb = make_map(b, b_mn, BN, nb0, nb1, dt);
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.nb0 = nb0; p.nb1 = nb1; p.a_mn = a_mn; p.b_mn = b_mn;
@@ -569,11 +590,11 @@ void launch_tc05(const OperandView& a, const OperandView& b, bool a_mn, bool b_m
   p.tma_store = tma_store ? 1 : 0;
   static std::once_flag once;
   std::call_once(once, [] {
-    OB_CUDA(cudaFuncSetAttribute(gemm_tc05_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    OB_CUDA(cudaFuncSetAttribute(gemm_tc05_kernel<T, BN, TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
   });
-  const long long tiles = static_cast<long long>((M + BM - 1) / BM) * ((N + BN - 1) / BN) * nb0 * nb1;
+  const long long tiles = static_cast<long long>((M + TM - 1) / TM) * ((N + BN - 1) / BN) * nb0 * nb1;
   const int grid = static_cast<int>(std::min<long long>(tiles, sm_count_for(C)));
-  gemm_tc05_kernel<T, BN><<<grid, kGemmThreads, L::kTotal, st>>>(ma, mb, mc, mz, p);
+  gemm_tc05_kernel<T, BN, TM><<<grid, kGemmThreads, L::kTotal, st>>>(ma, mb, mc, mz, p);
   check_launch("gemm_tc05");
 }
 
@@ -636,28 +657,33 @@ void gemm_dispatch(const Tensor& A_in, bool ta, const Tensor& B_in, bool tb, Ten
   }
   const bool a_mn = !(a.s_k == 1 || (a.k == 1 && a.s_mn != 1));
   const bool b_mn = !(b.s_k == 1 || (b.k == 1 && b.s_mn != 1));
-  // Tile width: 256 columns halve the A-operand traffic per flop, 128 columns give twice as many
-  // tiles; take the narrower tile when the wider one would leave a large part of the last wave
-  // of the persistent grid idle.
+  // Tile width: 256 columns whenever the problem is wider than one 128-column tile.  Narrow tiles
+  // fill the last wave of the persistent grid better but run at about two thirds of the wide
+  // tile's rate (measured on 8192 x 2048 x 8192: 900 against 1330 TFLOP/s), so they never pay.
   bool wide = N > 128;
-  if (wide) {
+  {
     static const int force_bn = [] { const char* e = std::getenv("ORTHON_GEMM_BN"); return e ? std::atoi(e) : 0; }();
-    const long long sms = sm_count_for(C);
-    auto wave_eff = [&](int bn) {
-      const long long tiles = static_cast<long long>((M + BM - 1) / BM) * ((N + bn - 1) / bn) * nb0 * nb1;
-      return static_cast<double>(tiles) / static_cast<double>(((tiles + sms - 1) / sms) * sms);
-    };
-    if (force_bn == 128) wide = false;
-    else if (force_bn != 256 && wave_eff(128) * 0.93 > wave_eff(256)) wide = false;
+    if (force_bn == 128) wide = false;  // measurement switch
   }
   g_last_route.store(wide ? 3 : 2, std::memory_order_relaxed);
-  if (dt == DType::BF16) {
-    if (wide) launch_tc05<__nv_bfloat16, 256>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);
-    else launch_tc05<__nv_bfloat16, 128>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);
-  } else {
-    if (wide) launch_tc05<__half, 256>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);
-    else launch_tc05<__half, 128>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);
-  }
+  // 256-row tiles (two MMA row blocks per B stage) when the reduction is long enough to amortise
+  // their non-overlapped epilogue (measured: K >= 4096) and they fill the waves of the persistent
+  // grid at least to 80 %.
+  static const int force_tm = [] { const char* e = std::getenv("ORTHON_GEMM_TM"); return e ? std::atoi(e) : 0; }();
+  const long long sms = sm_count_for(C);
+  const long long tiles256 = static_cast<long long>((M + 255) / 256) * ((N + 255) / 256) * nb0 * nb1;
+  const double eff256 = static_cast<double>(tiles256) / static_cast<double>(((tiles256 + sms - 1) / sms) * sms);
+  const bool tall = wide && force_tm != 128 && (force_tm == 256 || (M >= 512 && K >= 4096 && eff256 >= 0.8));
+  if (tall) g_last_route.store(3, std::memory_order_relaxed);
+#define OB_GEMM_LAUNCH(TT)                                                                                           \
+  do {                                                                                                               \
+    if (tall) launch_tc05<TT, 256, 256>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);          \
+    else if (wide) launch_tc05<TT, 256, 128>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);     \
+    else launch_tc05<TT, 128, 128>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);               \
+  } while (0)
+  if (dt == DType::BF16) OB_GEMM_LAUNCH(__nv_bfloat16);
+  else OB_GEMM_LAUNCH(__half);
+#undef OB_GEMM_LAUNCH
 }
 
 void k_matmul(OpCall& c) {
