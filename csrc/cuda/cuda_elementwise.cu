@@ -298,6 +298,87 @@ __global__ void adam_kernel(float* __restrict__ p, float* __restrict__ m, float*
   }
 }
 
+// 16-byte accesses: loads and stores of 8 consecutive elements of any of the element types.
+template <class E>
+__device__ __forceinline__ void load8(const E* p, float* out) {
+  if (sizeof(E) == 4) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w; out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+  } else {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const E* e = reinterpret_cast<const E*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) out[k] = to_f(e[k]);
+  }
+}
+template <class E>
+__device__ __forceinline__ void store8(E* p, const float* in) {
+  if (sizeof(E) == 4) {
+    *reinterpret_cast<float4*>(p) = make_float4(in[0], in[1], in[2], in[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(in[4], in[5], in[6], in[7]);
+  } else {
+    uint4 raw;
+    E* e = reinterpret_cast<E*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) e[k] = from_f<E>(in[k]);
+    *reinterpret_cast<uint4*>(p) = raw;
+  }
+}
+
+// Vector form of adam_kernel over the first n8 * 8 elements (every pointer 16-byte aligned).
+template <class G, class M>
+__global__ void adam_vec_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
+                                const G* __restrict__ g, M* __restrict__ model, int64_t n8, AdamArgs a) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += stride) {
+    const int64_t e = i * 8;
+    float gr[8], mi[8], vi[8], w[8];
+    load8(g + e, gr);
+    load8(m + e, mi);
+    load8(v + e, vi);
+    load8(p + e, w);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float gk = gr[k] * a.gs;
+      mi[k] = mi[k] + (a.b1 - 1.f) * mi[k];
+      mi[k] = mi[k] + (1.f - a.b1) * gk;
+      vi[k] = vi[k] + (a.b2 - 1.f) * vi[k];
+      vi[k] = vi[k] + (1.f - a.b2) * (gk * gk);
+      const float denom = sqrtf(vi[k] * a.inv_bc2) + a.eps;
+      if (a.wd != 0.f) w[k] = w[k] + (-a.lr * a.wd) * w[k];
+      w[k] = w[k] + (-a.lr * a.inv_bc1) * (mi[k] / denom);
+    }
+    store8(m + e, mi);
+    store8(v + e, vi);
+    store8(p + e, w);
+    if (model != nullptr) store8(model + e, w);
+  }
+}
+
+template <class G, class M>
+__global__ void sgd_vec_kernel(float* __restrict__ p, const G* __restrict__ g, M* __restrict__ model, int64_t n8,
+                               float lr, float wd, float gs) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += stride) {
+    const int64_t e = i * 8;
+    float gr[8], w[8];
+    load8(g + e, gr);
+    load8(p + e, w);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (wd != 0.f) w[k] = w[k] + (-lr * wd) * w[k];
+      w[k] = w[k] + (-lr) * (gr[k] * gs);
+    }
+    store8(p + e, w);
+    if (model != nullptr) store8(model + e, w);
+  }
+}
+
+inline bool aligned16(const void* a, const void* b = nullptr, const void* c = nullptr, const void* d = nullptr, const void* e = nullptr) {
+  return ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c) |
+           reinterpret_cast<uintptr_t>(d) | reinterpret_cast<uintptr_t>(e)) & 15u) == 0;
+}
+
 template <class G, class M>
 __global__ void sgd_kernel(float* __restrict__ p, const G* __restrict__ g, M* __restrict__ model, int64_t n,
                            float lr, float wd, float gs) {
@@ -618,19 +699,25 @@ void adam_with_grad(OpCall& c) {
                    static_cast<float>(c.f[4]), static_cast<float>(1.0 / c.f[5]), static_cast<float>(1.0 / c.f[6]),
                    static_cast<float>(c.f[7])};
   const int64_t n = p.numel();
-  const int grid = ew_grid(n, kThreads, sm_count_for(p));
   cudaStream_t st = stream_of(c);
   float *pp = p.data_as<float>(), *pm = m.data_as<float>(), *pv = v.data_as<float>();
   const G* pg = g.data_as<G>();
-  if (!c.in[4].defined()) {
-    adam_kernel<G, float><<<grid, kThreads, 0, st>>>(pp, pm, pv, pg, static_cast<float*>(nullptr), n, a);
-  } else if (c.in[4].dtype() == DType::BF16) {
-    adam_kernel<G, __nv_bfloat16><<<grid, kThreads, 0, st>>>(pp, pm, pv, pg, c.in[4].data_as<__nv_bfloat16>(), n, a);
-  } else if (c.in[4].dtype() == DType::F16) {
-    adam_kernel<G, __half><<<grid, kThreads, 0, st>>>(pp, pm, pv, pg, c.in[4].data_as<__half>(), n, a);
-  } else {
-    adam_kernel<G, float><<<grid, kThreads, 0, st>>>(pp, pm, pv, pg, c.in[4].data_as<float>(), n, a);
-  }
+  void* pmodel = c.in[4].defined() ? c.in[4].data() : nullptr;
+  // Bulk in 8-element vectors, the (at most 7-element) tail with the scalar kernel.
+  const int64_t n8 = aligned16(pp, pm, pv, pg, pmodel) ? n / 8 : 0;
+  const int64_t done = n8 * 8, rest = n - done;
+  const int sms = sm_count_for(p);
+  auto launch = [&](auto model_ptr) {
+    using MT = std::remove_pointer_t<decltype(model_ptr)>;
+    if (n8 > 0) adam_vec_kernel<G, MT><<<ew_grid(n8, kThreads, sms), kThreads, 0, st>>>(pp, pm, pv, pg, model_ptr, n8, a);
+    if (rest > 0)
+      adam_kernel<G, MT><<<ew_grid(rest, kThreads, sms), kThreads, 0, st>>>(pp + done, pm + done, pv + done, pg + done,
+                                                                           model_ptr ? model_ptr + done : model_ptr, rest, a);
+  };
+  if (!c.in[4].defined()) launch(static_cast<float*>(nullptr));
+  else if (c.in[4].dtype() == DType::BF16) launch(c.in[4].data_as<__nv_bfloat16>());
+  else if (c.in[4].dtype() == DType::F16) launch(c.in[4].data_as<__half>());
+  else launch(c.in[4].data_as<float>());
   check_launch("adam_step");
 }
 
@@ -648,13 +735,25 @@ void sgd_with_grad(OpCall& c) {
   Tensor& p = c.in[0];
   const Tensor& g = c.in[1];
   const int64_t n = p.numel();
-  const int grid = ew_grid(n, kThreads, sm_count_for(p));
   cudaStream_t st = stream_of(c);
   const float lr = static_cast<float>(c.f[0]), wd = static_cast<float>(c.f[1]), gs = static_cast<float>(c.f[2]);
-  if (!c.in[2].defined()) sgd_kernel<G, float><<<grid, kThreads, 0, st>>>(p.data_as<float>(), g.data_as<G>(), static_cast<float*>(nullptr), n, lr, wd, gs);
-  else if (c.in[2].dtype() == DType::BF16) sgd_kernel<G, __nv_bfloat16><<<grid, kThreads, 0, st>>>(p.data_as<float>(), g.data_as<G>(), c.in[2].data_as<__nv_bfloat16>(), n, lr, wd, gs);
-  else if (c.in[2].dtype() == DType::F16) sgd_kernel<G, __half><<<grid, kThreads, 0, st>>>(p.data_as<float>(), g.data_as<G>(), c.in[2].data_as<__half>(), n, lr, wd, gs);
-  else sgd_kernel<G, float><<<grid, kThreads, 0, st>>>(p.data_as<float>(), g.data_as<G>(), c.in[2].data_as<float>(), n, lr, wd, gs);
+  float* pp = p.data_as<float>();
+  const G* pg = g.data_as<G>();
+  void* pmodel = c.in[2].defined() ? c.in[2].data() : nullptr;
+  const int64_t n8 = aligned16(pp, pg, pmodel) ? n / 8 : 0;
+  const int64_t done = n8 * 8, rest = n - done;
+  const int sms = sm_count_for(p);
+  auto launch = [&](auto model_ptr) {
+    using MT = std::remove_pointer_t<decltype(model_ptr)>;
+    if (n8 > 0) sgd_vec_kernel<G, MT><<<ew_grid(n8, kThreads, sms), kThreads, 0, st>>>(pp, pg, model_ptr, n8, lr, wd, gs);
+    if (rest > 0)
+      sgd_kernel<G, MT><<<ew_grid(rest, kThreads, sms), kThreads, 0, st>>>(pp + done, pg + done, model_ptr ? model_ptr + done : model_ptr,
+                                                                          rest, lr, wd, gs);
+  };
+  if (!c.in[2].defined()) launch(static_cast<float*>(nullptr));
+  else if (c.in[2].dtype() == DType::BF16) launch(c.in[2].data_as<__nv_bfloat16>());
+  else if (c.in[2].dtype() == DType::F16) launch(c.in[2].data_as<__half>());
+  else launch(c.in[2].data_as<float>());
   check_launch("sgd_step");
 }
 

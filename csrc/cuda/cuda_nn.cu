@@ -688,6 +688,68 @@ bool ln_fast_ok(const OpCall& c, int64_t D, int* threads, int* chunks) {
   return true;
 }
 
+// One warp per row: CH packs per lane (pack index c * 32 + lane, so every load is a full line),
+// statistics by shuffles only.  Four rows per block.  Requires D == CH * 32 * Pack<T>::N.
+template <class T, int CH>
+__global__ void __launch_bounds__(128) layernorm_fwd_warp(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ b,
+                                                          T* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd,
+                                                          int64_t R, float eps) {
+  constexpr int N = Pack<T>::N;
+  constexpr int D = CH * 32 * N;
+  const int lane = threadIdx.x & 31;
+  const int64_t r = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+  if (r >= R) return;
+  const T* row = x + r * D;
+  float v[CH][N];
+  float s = 0.f;
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const Pack<T> pk = load_pack(row + (c * 32 + lane) * N);
+#pragma unroll
+    for (int k = 0; k < N; ++k) { v[c][k] = to_f(pk.v[k]); s += v[c][k]; }
+  }
+  const float m = warp_sum(s) * (1.f / D);
+  float q = 0.f;
+#pragma unroll
+  for (int c = 0; c < CH; ++c)
+#pragma unroll
+    for (int k = 0; k < N; ++k) { const float z = v[c][k] - m; q += z * z; }
+  const float rs = rsqrtf(warp_sum(q) * (1.f / D) + eps);
+  if (lane == 0) { mean[r] = m; rstd[r] = rs; }
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int off = (c * 32 + lane) * N;
+    Pack<T> pw, pb, out;
+    if (w) pw = load_pack(w + off);
+    if (b) pb = load_pack(b + off);
+#pragma unroll
+    for (int k = 0; k < N; ++k) {
+      float o = (v[c][k] - m) * rs;
+      if (w) o *= to_f(pw.v[k]);
+      if (b) o += to_f(pb.v[k]);
+      out.v[k] = from_f<T>(o);
+    }
+    store_pack(y + r * D + off, out);
+  }
+}
+
+template <class T>
+bool layernorm_fwd_warp_launch(const T* x, const T* w, const T* b, T* y, float* mean, float* rstd, int64_t R, int64_t D, float eps,
+                               cudaStream_t st) {
+  constexpr int N = Pack<T>::N;
+  if (D % (32 * N) != 0) return false;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(b)) & 15u)
+    return false;
+  const unsigned grid = static_cast<unsigned>((R + 3) / 4);
+  switch (D / (32 * N)) {
+    case 1: layernorm_fwd_warp<T, 1><<<grid, 128, 0, st>>>(x, w, b, y, mean, rstd, R, eps); return true;
+    case 2: layernorm_fwd_warp<T, 2><<<grid, 128, 0, st>>>(x, w, b, y, mean, rstd, R, eps); return true;
+    case 4: layernorm_fwd_warp<T, 4><<<grid, 128, 0, st>>>(x, w, b, y, mean, rstd, R, eps); return true;
+    case 8: layernorm_fwd_warp<T, 8><<<grid, 128, 0, st>>>(x, w, b, y, mean, rstd, R, eps); return true;
+    default: return false;
+  }
+}
+
 template <class T>
 void k_layernorm(OpCall& c) {
   const Tensor& x = c.in[0];
@@ -695,6 +757,12 @@ void k_layernorm(OpCall& c) {
   if (R > 2147483647LL) throw std::invalid_argument("layer_norm: too many rows");
   const T* fw = c.in[1].defined() ? c.in[1].data_as<T>() : nullptr;
   const T* fb = c.in[2].defined() ? c.in[2].data_as<T>() : nullptr;
+  if (x.is_contiguous() && c.out[0].is_contiguous() &&
+      layernorm_fwd_warp_launch<T>(x.data_as<T>(), fw, fb, c.out[0].data_as<T>(), c.out[1].data_as<float>(), c.out[2].data_as<float>(), R,
+                                   D, static_cast<float>(c.f[0]), stream_of(c))) {
+    check_launch("layer_norm");
+    return;
+  }
   int fth = 0, fch = 0;
   if (ln_fast_ok<T>(c, D, &fth, &fch)) {
     cudaStream_t st = stream_of(c);

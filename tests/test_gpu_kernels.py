@@ -34,7 +34,12 @@ def close(actual, expected, dtype, scale=1.0):
     tol = TOL[dtype] * scale
     err = (a - e).abs().max().item()
     ref = e.abs().max().item()
-    assert err <= tol * max(1.0, ref), f"max err {err} vs tol {tol * max(1.0, ref)}"
+    if not err <= tol * max(1.0, ref):
+        import inspect
+        where = inspect.stack()[1]
+        bad = int((a - e).abs().argmax().item())
+        raise AssertionError(f"line {where.lineno}: max err {err} vs tol {tol * max(1.0, ref)} at flat index {bad} of {a.numel()} "
+                             f"(got {a.reshape(-1)[bad].item()}, want {e.reshape(-1)[bad].item()})")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
