@@ -52,7 +52,8 @@ std::atomic<int> g_last_route{0};  // 1 = simt, 2 = tcgen05 128x128, 3 = tcgen05
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int kEpilogueWarps = 4;
-constexpr int kGemmThreads = 32 * (2 + kEpilogueWarps);
+// TMA warp, MMA warp, four epilogue warps per MMA row block of the tile.
+constexpr int gemm_threads(int tile_rows) { return 32 * (2 + kEpilogueWarps * (tile_rows / 128)); }
 
 enum : int { kErrProducer = 1, kErrMma = 2, kErrEpilogue = 3 };
 
@@ -97,7 +98,7 @@ __device__ __forceinline__ float gelu_grad(float z) {
 }
 
 template <class T, int BN, int TM>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(gemm_threads(TM), 1)
 gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_z, GemmParams p) {
   using L = SmemLayout<BN, TM>;
@@ -245,7 +246,10 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     // by the tensor map), or (b) direct 16-byte / scalar stores when the output is not TMA-friendly.
     const bool staged = p.tma_store != 0;
     const bool vec = staged || (vec_ok && (p.N % 8 == 0));
-    uint8_t* ebuf = epi_smem + (warp - 2) * 8192;
+    // Staging: two 4 KB tiles per warp with one row block, one per warp with two (the row blocks
+    // are then drained concurrently by their own four warps).
+    uint8_t* ebuf = epi_smem + (warp - 2) * (H == 1 ? 8192 : 4096);
+    const int my_h = (warp - 2) >> 2;
     int buf = 0;
     for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
       int bidx, tm, tn;
@@ -253,6 +257,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int b0 = bidx / p.nb1, b1 = bidx - b0 * p.nb1;
 #pragma unroll 1
       for (int h = 0; h < H && ok; ++h) {
+      if (H == 2 && h != my_h) continue;
       const int acc = slot_of(it, h);
       if (!mbar_wait(&tmem_full[acc], use_of(it) & 1, p.err, kErrEpilogue)) { ok = false; break; }
       tc_fence_after();
@@ -274,7 +279,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (staged && half == 0) {
           // The tile about to be overwritten must have been read by its previous store.
           if (lane == 0) {
-            if (Zb) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            if (Zb || H == 2) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
             else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
           }
           __syncwarp();
@@ -378,8 +383,8 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             for (int j = 0; j < 32; ++j) v[j] += aux[j];
           }
         }
-        emit(Cb, Zb ? ebuf + 4096 : ebuf + buf * 4096, false, v);
-        if (staged && !Zb && (half == 1 || col0 + 32 >= p.N)) buf ^= 1;
+        emit(Cb, H == 2 ? ebuf : (Zb ? ebuf + 4096 : ebuf + buf * 4096), false, v);
+        if (H == 1 && staged && !Zb && (half == 1 || col0 + 32 >= p.N)) buf ^= 1;
       }
       tc_fence_before();
       __syncwarp();
@@ -594,7 +599,7 @@ void launch_tc05(const OperandView& a, const OperandView& b, bool a_mn, bool b_m
   });
   const long long tiles = static_cast<long long>((M + TM - 1) / TM) * ((N + BN - 1) / BN) * nb0 * nb1;
   const int grid = static_cast<int>(std::min<long long>(tiles, sm_count_for(C)));
-  gemm_tc05_kernel<T, BN, TM><<<grid, kGemmThreads, L::kTotal, st>>>(ma, mb, mc, mz, p);
+  gemm_tc05_kernel<T, BN, TM><<<grid, gemm_threads(TM), L::kTotal, st>>>(ma, mb, mc, mz, p);
   check_launch("gemm_tc05");
 }
 
@@ -667,13 +672,15 @@ void gemm_dispatch(const Tensor& A_in, bool ta, const Tensor& B_in, bool tb, Ten
   }
   g_last_route.store(wide ? 3 : 2, std::memory_order_relaxed);
   // 256-row tiles (two MMA row blocks per B stage) when the reduction is long enough to amortise
-  // their non-overlapped epilogue (measured: K >= 4096) and they fill the waves of the persistent
+  // their epilogue, which overlaps the next tile only partly (measured: K >= 2048) and they fill the waves of the persistent
   // grid at least to 80 %.
   static const int force_tm = [] { const char* e = std::getenv("ORTHON_GEMM_TM"); return e ? std::atoi(e) : 0; }();
   const long long sms = sm_count_for(C);
   const long long tiles256 = static_cast<long long>((M + 255) / 256) * ((N + 255) / 256) * nb0 * nb1;
   const double eff256 = static_cast<double>(tiles256) / static_cast<double>(((tiles256 + sms - 1) / sms) * sms);
-  const bool tall = wide && force_tm != 128 && (force_tm == 256 || (M >= 512 && K >= 4096 && eff256 >= 0.8));
+  static const int tall_min_k = [] { const char* e = std::getenv("ORTHON_GEMM_TALL_MIN_K"); return e ? std::atoi(e) : 2048; }();
+  const bool tall = wide && force_tm != 128 && !ep.preact.defined() &&
+                    (force_tm == 256 || (M >= 512 && K >= tall_min_k && eff256 >= 0.8));
   if (tall) g_last_route.store(3, std::memory_order_relaxed);
 #define OB_GEMM_LAUNCH(TT)                                                                                           \
   do {                                                                                                               \
