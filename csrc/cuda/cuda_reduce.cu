@@ -123,16 +123,39 @@ __global__ void col_sum_vec_kernel(const T* __restrict__ in, float* __restrict__
   }
 }
 
+// Second pass of the row sums: out[o] = scale * sum_s partial[o * splits + s].
+template <class T>
+__global__ void finalize_rows_kernel(const float* __restrict__ partial, T* __restrict__ out, int64_t outer, int splits, float scale) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t o = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; o < outer; o += stride) {
+    float total = 0.f;
+    for (int s = 0; s < splits; ++s) total += partial[o * splits + s];
+    out[o] = from_f<T>(total * scale);
+  }
+}
+
+// Second pass: out[o, k] = scale * sum_s partial[o, s, k].  Block (32, 8): 32 adjacent outputs,
+// eight groups striding over the splits (enough loads in flight for a few hundred KB), then a
+// fixed-order sum of the eight partials.  grid = (ceil(inner / 32), outer).
 template <class T>
 __global__ void finalize_sum_kernel(const float* __restrict__ partial, T* __restrict__ out, int64_t outer,
                                     int64_t inner, int splits, float scale) {
-  const int64_t n = outer * inner;
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
-    const int64_t o = i / inner, k = i - o * inner;
+  __shared__ float tile[8][33];
+  const int64_t o = blockIdx.y;
+  const int64_t k = static_cast<int64_t>(blockIdx.x) * 32 + threadIdx.x;
+  float acc = 0.f;
+  if (k < inner) {
+    const float* base = partial + o * splits * inner + k;
+#pragma unroll 4
+    for (int s = threadIdx.y; s < splits; s += 8) acc += base[static_cast<int64_t>(s) * inner];
+  }
+  tile[threadIdx.y][threadIdx.x] = acc;
+  __syncthreads();
+  if (threadIdx.y == 0 && k < inner) {
     float total = 0.f;
-    for (int s = 0; s < splits; ++s) total += partial[(o * splits + s) * inner + k];
-    out[i] = from_f<T>(total * scale);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) total += tile[j][threadIdx.x];
+    out[o * inner + k] = from_f<T>(total * scale);
   }
 }
 
@@ -165,7 +188,7 @@ void sum_launch(const T* in, T* out, int64_t outer, int64_t reduce, int64_t inne
     ScratchLease lease(ref.device(), sizeof(float) * outer * splits, st);
     float* partial = static_cast<float*>(lease.data());
     row_sum_kernel<T><<<dim3(splits, static_cast<unsigned>(outer)), kThreads, 0, st>>>(in, partial, out, reduce, chunk, splits, scale);
-    finalize_sum_kernel<T><<<ew_grid(outer, kThreads, sms), kThreads, 0, st>>>(partial, out, outer, 1, splits, scale);
+    finalize_rows_kernel<T><<<ew_grid(outer, kThreads, sms), kThreads, 0, st>>>(partial, out, outer, splits, scale);
     check_launch("row sum (split)");
     return;
   }
@@ -189,7 +212,7 @@ void sum_launch(const T* in, T* out, int64_t outer, int64_t reduce, int64_t inne
   float* partial = static_cast<float*>(lease.data());
   if (vec) col_sum_vec_kernel<T><<<grid, dim3(32, 8), 0, st>>>(in, partial, out, reduce, inner, chunk, splits, scale);
   else col_sum_kernel<T><<<grid, dim3(32, 8), 0, st>>>(in, partial, out, reduce, inner, chunk, splits, scale);
-  finalize_sum_kernel<T><<<ew_grid(outer * inner, kThreads, sms), kThreads, 0, st>>>(partial, out, outer, inner, splits, scale);
+  finalize_sum_kernel<T><<<dim3(static_cast<unsigned>((inner + 31) / 32), static_cast<unsigned>(outer)), dim3(32, 8), 0, st>>>(partial, out, outer, inner, splits, scale);
   check_launch("column sum (split)");
 }
 
