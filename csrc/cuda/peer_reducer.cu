@@ -1,19 +1,22 @@
 // Peer-memory gradient reducer for one node of NVLink/NVSwitch-connected GPUs.
 //
 // Every rank maps every other rank's gradient bucket, float32 staging bucket and flag block
-// (CUDA IPC).  One kernel launch per bucket and per rank then does, with plain peer loads and
-// stores (no NCCL call and no bulk-tensor copies):
+// (CUDA IPC, or cuMemCreate allocations shared by file descriptor).  One kernel launch per
+// bucket and per rank then does, without any NCCL call or bulk-tensor copy:
 //
 //   two-shot   entry barrier -> each rank reduces its 1/world slice by reading that slice from
-//              every peer, multiplies by `scale` (1/world_size x 1/loss_scale), checks for
-//              inf/NaN and pushes the float32 result into every rank's staging bucket ->
-//              barrier -> every rank applies the FP32-master Adam / SGD update to the whole
-//              bucket from its local staging copy and refreshes the low-precision model copy.
-//              In "average only" mode the reduced slice is pushed straight back into every
-//              rank's gradient bucket instead (no staging, no optimizer).
+//              every peer (8 / world vectors of every rank in flight per thread), multiplies by
+//              `scale` (1/world_size x 1/loss_scale), checks for inf/NaN and writes the result,
+//              in the gradient dtype, into that slice of every rank's bucket -> barrier ->
+//              every rank applies the FP32-master Adam / SGD update to the whole bucket from
+//              its local copy and refreshes the low-precision model copy ("average" mode stops
+//              after the barrier).
 //   one-shot   entry barrier -> every rank reads the whole bucket from every peer and reduces it
-//              into its local staging copy (lowest latency for small buckets) -> barrier (all
-//              reads done, inf/NaN verdict known) -> update or write-back from the local copy.
+//              into its local float32 staging copy (lowest latency for small buckets) -> barrier
+//              (all reads done, inf/NaN verdict known) -> update or write-back from that copy.
+//   NVLS       same protocol as two-shot, with the slice reduced by multimem.ld_reduce and
+//              re-broadcast by multimem.st through the multicast mapping of the buckets: the
+//              NVSwitch adds and replicates, each GPU moves S instead of 2 S (w-1)/w bytes.
 //
 // Barriers are per-CTA flag words in peer memory written with st.release.sys and polled with
 // ld.acquire.sys; CTA b only ever depends on CTA b of the other ranks, and the grid is small
@@ -226,6 +229,28 @@ __device__ __forceinline__ bool reduce_range(const PeerArgs& a, long long lo, lo
   return bad;
 }
 
+// Optimizer update from the reduced gradients in the local bucket (two-shot and NVLS variants).
+// CTA b consumes, in every slice, exactly the vectors CTA b of the slice's owner produced: the
+// barrier between the phases only pairs CTAs of the same index.
+template <class GT>
+__device__ __forceinline__ void update_from_bucket(const PeerArgs& a) {
+  constexpr int VEC = Pack<GT>::N;
+  const GT* red = static_cast<const GT*>(a.grads[a.rank]);
+  const long long stride = static_cast<long long>(gridDim.x) * kPeerThreads;
+  for (int s = 0; s < a.world; ++s) {
+    const long long lo = min(a.n, static_cast<long long>(s) * a.per), hi = min(a.n, lo + a.per);
+    const long long nvec = (hi - lo) / VEC;
+    for (long long vi = static_cast<long long>(blockIdx.x) * kPeerThreads + threadIdx.x; vi < nvec; vi += stride) {
+      const long long e = lo + vi * VEC;
+      const Pack<GT> in = load_pack(red + e);
+      float g[VEC];
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) g[k] = to_f(in.v[k]);
+      apply_update<GT, VEC>(a, e, g);
+    }
+  }
+}
+
 template <class GT, int W>
 __global__ void __launch_bounds__(kPeerThreads) peer_reduce_kernel(PeerArgs a) {
   constexpr int VEC = Pack<GT>::N;  // 16 bytes of gradients per access
@@ -246,28 +271,16 @@ __global__ void __launch_bounds__(kPeerThreads) peer_reduce_kernel(PeerArgs a) {
     });
   } else {
     const long long lo = min(a.n, static_cast<long long>(a.rank) * a.per), hi = min(a.n, lo + a.per);
-    if (a.mode == kModeAverage) {
-      // The reduced slice goes straight back into every rank's bucket in the gradient dtype.
-      bad = reduce_range<GT, W>(a, lo, (hi - lo) / VEC, [&](long long e, const float* acc) {
-        Pack<GT> out;
+    // The reduced slice goes straight back into every rank's bucket in the gradient dtype (no
+    // other rank reads this slice); a fused optimizer then reads the local bucket.
+    bad = reduce_range<GT, W>(a, lo, (hi - lo) / VEC, [&](long long e, const float* acc) {
+      Pack<GT> out;
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) out.v[k] = from_f<GT>(acc[k]);
+      for (int k = 0; k < VEC; ++k) out.v[k] = from_f<GT>(acc[k]);
 #pragma unroll
-        for (int s = 0; s < R; ++s)
-          if (s < world) store_pack(const_cast<GT*>(static_cast<const GT*>(a.grads[s])) + e, out);
-      });
-    } else {
-      // The optimizer wants fp32: push the reduced slice into every rank's fp32 staging.
-      bad = reduce_range<GT, W>(a, lo, (hi - lo) / VEC, [&](long long e, const float* acc) {
-#pragma unroll
-        for (int s = 0; s < R; ++s)
-          if (s < world) {
-#pragma unroll
-            for (int k = 0; k < VEC; k += 4)
-              *reinterpret_cast<float4*>(a.staging[s] + e + k) = *reinterpret_cast<const float4*>(acc + k);
-          }
-      });
-    }
+      for (int s = 0; s < R; ++s)
+        if (s < world) store_pack(const_cast<GT*>(static_cast<const GT*>(a.grads[s])) + e, out);
+    });
   }
   if (bad) atomicExch(&s_bad, 1);
   __syncthreads();
@@ -304,19 +317,7 @@ __global__ void __launch_bounds__(kPeerThreads) peer_reduce_kernel(PeerArgs a) {
         apply_update<GT, VEC>(a, vi * VEC, g);
       }
     } else {
-      // CTA b consumes, in every slice, exactly the vectors CTA b of the slice's owner produced.
-      for (int s = 0; s < a.world; ++s) {
-        const long long lo = min(a.n, static_cast<long long>(s) * a.per), hi = min(a.n, lo + a.per);
-        const long long nvec = (hi - lo) / VEC;
-        for (long long vi = static_cast<long long>(blockIdx.x) * kPeerThreads + threadIdx.x; vi < nvec;
-             vi += static_cast<long long>(G) * kPeerThreads) {
-          const long long e = lo + vi * VEC;
-          float g[VEC];
-#pragma unroll
-          for (int k = 0; k < VEC; k += 4) *reinterpret_cast<float4*>(g + k) = *reinterpret_cast<const float4*>(red + e + k);
-          apply_update<GT, VEC>(a, e, g);
-        }
-      }
+      update_from_bucket<GT>(a);
     }
   }
 }
@@ -395,17 +396,7 @@ __global__ void __launch_bounds__(kPeerThreads) nvls_reduce_kernel(PeerArgs a) {
   const bool any_inf = ld_acquire_sys(inf_word(a.flags[a.rank])) == a.epoch;
   if (any_inf && threadIdx.x == 0 && blockIdx.x == 0) atomicExch(a.found_inf, 1);
 
-  if (a.mode != kModeAverage && !any_inf) {
-    const GT* red = static_cast<const GT*>(a.grads[a.rank]);
-    const long long all = a.n / VEC;
-    for (long long vi = static_cast<long long>(blockIdx.x) * kPeerThreads + threadIdx.x; vi < all; vi += stride) {
-      const Pack<GT> in = load_pack(red + vi * VEC);
-      float g[VEC];
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) g[k] = to_f(in.v[k]);
-      apply_update<GT, VEC>(a, vi * VEC, g);
-    }
-  }
+  if (a.mode != kModeAverage && !any_inf) update_from_bucket<GT>(a);
 }
 
 __global__ void peer_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long n16) {

@@ -16,8 +16,8 @@ contributes zeros and receives the average; in "update" mode every parameter mus
 gradient.
 
 Buckets of at least NVLS_MIN_BYTES go through the in-switch (multimem) variant of the kernel
-when the backend could bind the buckets to an NVLink multicast object; smaller ones use the
-one-shot / two-shot peer-load variants.
+when the backend could bind the buckets to an NVLink multicast object and the group has at least
+NVLS_MIN_WORLD ranks; everything else uses the one-shot / two-shot peer-load variants.
 """
 import os
 
@@ -42,6 +42,10 @@ class _Bucket:
 class PeerReducer:
     ONESHOT_BYTES = 512 << 10
     NVLS_MIN_BYTES = int(os.environ.get("ORTHON_NVLS_MIN_BYTES", 1 << 20))  # smaller buckets use peer loads
+    # In-switch reduction halves the bytes each GPU moves only as the world grows (S against
+    # 2 S (w-1)/w); measured on this hardware it loses to peer loads at 2 GPUs (392 against 683 GB/s
+    # at 1 GB) and ties at 4, so it is the default from 8 ranks.
+    NVLS_MIN_WORLD = int(os.environ.get("ORTHON_NVLS_MIN_WORLD", 8))
 
     @staticmethod
     def eligible(parameters, group):
@@ -134,7 +138,8 @@ class PeerReducer:
                         v=b.v_flat if self.mode == "adam" else None,
                         model=b.param_flat if (fused and b.param_flat is not None and b.master_flat is not b.param_flat) else None,
                         hyper=hyper, status=status, found_inf=found_inf, stream_kind=1,
-                        mc_grads=b.mc if (b.mc and not oneshot and nbytes >= self.NVLS_MIN_BYTES) else 0)
+                        mc_grads=b.mc if (b.mc and not oneshot and nbytes >= self.NVLS_MIN_BYTES
+                                          and self.world >= self.NVLS_MIN_WORLD) else 0)
         b.launched = True
         self.launch_count += 1
 
