@@ -317,11 +317,9 @@ PYBIND11_MODULE(_C, m) {
       .def("cast", [](const Tensor& t, const py::object& d) { return ops::cast(t, dtype_from_py(d)); })
       .def("sum", [](const Tensor& t, const py::object& dim, bool keep) { return ops::sum(t, opt_dim(dim), keep); }, py::arg("dim") = py::none(), py::arg("keepdim") = false)
       .def("mean", [](const Tensor& t, const py::object& dim, bool keep) { return ops::mean(t, opt_dim(dim), keep); }, py::arg("dim") = py::none(), py::arg("keepdim") = false)
-      .def("max", [](const Tensor& t, const py::object& dim, bool keep) -> py::object {
-        auto r = ops::max(t, opt_dim(dim), keep);
-        if (dim.is_none()) return py::cast(r.first);
-        return py::make_tuple(r.first, r.second);
-      }, py::arg("dim") = py::none(), py::arg("keepdim") = false)
+      // Values only, as in the reference (bindings/tensor_bindings.cpp:693-697); indices come from argmax.
+      .def("max", [](const Tensor& t, const py::object& dim, bool keep) { return ops::max(t, opt_dim(dim), keep).first; },
+           py::arg("dim") = py::none(), py::arg("keepdim") = false)
       .def("argmax", [](const Tensor& t, const py::object& dim, bool keep) { return ops::argmax(t, opt_dim(dim), keep); }, py::arg("dim") = py::none(), py::arg("keepdim") = false)
       .def("neg", &ops::neg).def("relu", &ops::relu).def("sigmoid", &ops::sigmoid).def("tanh", &ops::tanh)
       .def("leaky_relu", &ops::leaky_relu, py::arg("negative_slope") = 0.01)
@@ -420,11 +418,8 @@ PYBIND11_MODULE(_C, m) {
   m.def("contiguous", &ops::contiguous);
   m.def("sum", [](const Tensor& t, const py::object& dim, bool keep) { return ops::sum(t, opt_dim(dim), keep); }, py::arg("tensor"), py::arg("dim") = py::none(), py::arg("keepdim") = false);
   m.def("mean", [](const Tensor& t, const py::object& dim, bool keep) { return ops::mean(t, opt_dim(dim), keep); }, py::arg("tensor"), py::arg("dim") = py::none(), py::arg("keepdim") = false);
-  m.def("max", [](const Tensor& t, const py::object& dim, bool keep) -> py::object {
-    auto r = ops::max(t, opt_dim(dim), keep);
-    if (dim.is_none()) return py::cast(r.first);
-    return py::make_tuple(r.first, r.second);
-  }, py::arg("tensor"), py::arg("dim") = py::none(), py::arg("keepdim") = false);
+  m.def("max", [](const Tensor& t, const py::object& dim, bool keep) { return ops::max(t, opt_dim(dim), keep).first; },
+        py::arg("tensor"), py::arg("dim") = py::none(), py::arg("keepdim") = false);
   m.def("argmax", [](const Tensor& t, const py::object& dim, bool keep) { return ops::argmax(t, opt_dim(dim), keep); }, py::arg("tensor"), py::arg("dim") = py::none(), py::arg("keepdim") = false);
   m.def("neg", &ops::neg); m.def("relu", &ops::relu); m.def("sigmoid", &ops::sigmoid); m.def("tanh", &ops::tanh);
   m.def("leaky_relu", &ops::leaky_relu, py::arg("tensor"), py::arg("negative_slope") = 0.01);
@@ -571,6 +566,10 @@ PYBIND11_MODULE(_C, m) {
   m.def("_memory_pool_set_enabled", [](bool on) { MemoryPool::instance().set_enabled(on); });
   m.def("_memory_pool_enabled", [] { return MemoryPool::instance().enabled(); });
   m.def("_memory_pool_set_max_cached_bytes", [](uint64_t n) { MemoryPool::instance().set_max_cached_bytes(n); });
+  m.def("_memory_pool_max_cached_bytes", [] { return MemoryPool::instance().max_cached_bytes(); });
+  // Names of the reference's diagnostics surface (python/orthon/_diagnostics.py:8-17).
+  m.def("_memory_pool_clear_cache", [] { MemoryPool::instance().clear(); });
+  m.def("_memory_pool_reset_stats", [] { MemoryPool::instance().reset_peak(); });
   m.def("_scratch_pool_stats", [] {
     const ScratchPoolStats s = ScratchLease::stats();
     py::dict d;

@@ -132,6 +132,7 @@ class MemoryPool {
   void set_enabled(bool on);
   bool enabled() const { return enabled_; }
   void set_max_cached_bytes(uint64_t n);
+  uint64_t max_cached_bytes() const;
   static size_t round_size(size_t bytes);
 
  private:

@@ -373,6 +373,11 @@ void MemoryPool::set_max_cached_bytes(uint64_t n) {
   if (stats_.cached_bytes > max_cached_) evict_locked(max_cached_);
 }
 
+uint64_t MemoryPool::max_cached_bytes() const {
+  std::lock_guard<std::mutex> lock(mu_);
+  return max_cached_;
+}
+
 // ----------------------------------------------------------------- ScratchLease
 namespace {
 std::mutex g_scratch_mu;

@@ -12,7 +12,9 @@ from . import _C
 memory_pool_set_enabled = _C._memory_pool_set_enabled
 memory_pool_enabled = _C._memory_pool_enabled
 memory_pool_set_max_cached_bytes = _C._memory_pool_set_max_cached_bytes
+memory_pool_max_cached_bytes = _C._memory_pool_max_cached_bytes
 memory_pool_stats = _C._memory_pool_stats
+memory_pool_reset_stats = _C._memory_pool_reset_stats
 memory_pool_reset_peak = _C._memory_pool_reset_peak
 memory_pool_clear_cache = _C._memory_pool_clear
 memory_pool_scratch_stats = _C._scratch_pool_stats

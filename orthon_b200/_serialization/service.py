@@ -3,10 +3,10 @@ prepares the model, then the optimizer (told where the model's parameters will l
 then commits, model first, with reverse rollback on failure.
 (reference project: python/orthon/_serialization/service.py:44-82, transaction.py:23-84)"""
 from .. import _C
-from .._state import PreparedLoad, commit_prepared
 from .archive import Archive, fspath, write_archive
 from .codec import Decoder, Encoder
 from .format import FORMAT_ID, FORMAT_VERSION, fail
+from .transaction import RestoreTransaction
 
 
 def _device(spec, api):
@@ -18,23 +18,6 @@ def _device(spec, api):
         except Exception as exc:  # noqa: BLE001
             raise ValueError(f"{api}: unknown map_location {spec!r} ({exc})") from None
     raise TypeError(f"{api}: map_location must be a device string or Device, got {type(spec)!r}")
-
-
-def _generic_participant(owner, state, map_location):
-    """Duck-typed recipient: snapshot its public state, restore through load_state_dict."""
-    import copy
-    before = copy.copy(owner.state_dict())
-
-    def commit():
-        try:
-            owner.load_state_dict(state, map_location=map_location)
-        except TypeError:
-            owner.load_state_dict(state)
-
-    def rollback():
-        owner.load_state_dict(before)
-
-    return PreparedLoad(commit, rollback)
 
 
 def save_checkpoint(path, model=None, optimizer=None, metadata=None):
@@ -77,21 +60,17 @@ def load_checkpoint(path, model=None, optimizer=None, map_location=None):
             fail("model section is not a Tensor state mapping")
         if not isinstance(restored["metadata"], dict):
             fail("metadata section is not a mapping")
-    participants, placement = [], None
-    if model is not None:
-        if sections["model"] is None:
-            fail("checkpoint has no model section")
-        prep = getattr(model, "_prepare_load_state_dict", None)
-        part = prep(ms, map_location=target) if prep is not None else _generic_participant(model, ms, target)
-        placement = part.placement
-        participants.append(part)
-    if optimizer is not None:
-        if sections["optimizer"] is None:
-            fail("checkpoint has no optimizer section")
-        prep = getattr(optimizer, "_prepare_load_state_dict", None)
-        if prep is not None:
-            participants.append(prep(restored["optimizer"], map_location=target, placement=placement))
-        else:
-            participants.append(_generic_participant(optimizer, restored["optimizer"], target))
-    commit_prepared(participants)
+    if model is not None and sections["model"] is None:
+        fail("checkpoint has no model section")
+    if optimizer is not None and sections["optimizer"] is None:
+        fail("checkpoint has no optimizer section")
+    RestoreTransaction.prepare(model, ms, optimizer, restored["optimizer"], map_location=target).commit()
     return restored["metadata"]
+
+
+class SerializationService:
+    """Object form of the two entry points (what `checkpoint.save_checkpoint` / `load_checkpoint`
+    delegate to); kept separate from the codec and the archive so either can be replaced."""
+
+    save = staticmethod(save_checkpoint)
+    load = staticmethod(load_checkpoint)

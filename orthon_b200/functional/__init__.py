@@ -49,3 +49,23 @@ from .._C import (  # noqa: E402,F401
     relu, sigmoid, tanh, leaky_relu, gelu, softmax, log_softmax, cross_entropy, nll_loss,
     dropout, embedding, conv2d, maxpool2d, linear, fused_linear_relu, matmul,
 )
+
+
+def exp(x):
+    return x.exp()
+
+
+def sum(x, dim=None, keepdim=False):  # noqa: A001 - mirrors the tensor method
+    return x.sum(dim, keepdim)
+
+
+def mean(x, dim=None, keepdim=False):
+    return x.mean(dim, keepdim)
+
+
+def max(x, dim=None, keepdim=False):  # noqa: A001
+    return x.max(dim, keepdim)
+
+
+def argmax(x, dim=None, keepdim=False):
+    return x.argmax(dim, keepdim)

@@ -83,7 +83,7 @@ def test_reductions(dtype):
     for d in range(3):
         close(x.sum(d), t.sum(d), dtype, 8)
         close(x.mean(d, True), t.mean(d, True), dtype)
-        v, i = x.max(d)
+        v, i = x.max(d), x.argmax(d)
         tv, ti = t.max(d)
         close(v, tv, dtype)
         assert i.tolist() == ti.flatten().tolist()

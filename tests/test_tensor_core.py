@@ -114,7 +114,7 @@ def test_broadcasting_and_scalars():
 
 def test_reductions_and_extrema_policy():
     a = t([[1, 5, 5], [np.nan, 2, np.nan]])
-    v, i = a.max(1)
+    v, i = a.max(1), a.argmax(1)
     assert v.tolist()[0] == 5 and i.tolist() == [1, 0]  # first max, first NaN wins
     assert np.isnan(v.tolist()[1])
     assert a.slice(0, 0, 1).sum().tolist() == [11.0]
