@@ -273,6 +273,47 @@ __global__ void max_kernel(const T* __restrict__ in, T* __restrict__ values, int
   }
 }
 
+// Row-wise extrema (inner == 1): one warp per row, 16-byte loads, (value, index) pairs merged with
+// shuffles under the same policy (first NaN wins, ties go to the smaller index).
+template <class T>
+__global__ void max_row_warp_kernel(const T* __restrict__ in, T* __restrict__ values, int64_t* __restrict__ indices,
+                                    int64_t rows, int64_t reduce) {
+  constexpr int N = Pack<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (row >= rows) return;
+  const T* base = in + row * reduce;
+  float bv = 0.f;
+  int64_t bi = -1;
+  const bool vec = (reduce % N == 0) && ((reinterpret_cast<uintptr_t>(base) & 15u) == 0);
+  if (vec) {
+    for (int64_t p = lane; p < reduce / N; p += 32) {
+      const Pack<T> pk = load_pack(base + p * N);
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        const float v = to_f(pk.v[k]);
+        const int64_t r = p * N + k;
+        if (bi < 0 || better(v, r, bv, bi)) { bv = v; bi = r; }
+      }
+    }
+  } else {
+    for (int64_t r = lane; r < reduce; r += 32) {
+      const float v = to_f(base[r]);
+      if (bi < 0 || better(v, r, bv, bi)) { bv = v; bi = r; }
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+    const int64_t oi = __shfl_xor_sync(0xffffffffu, bi, off);
+    if (oi >= 0 && (bi < 0 || better(ov, oi, bv, bi))) { bv = ov; bi = oi; }
+  }
+  if (lane == 0) {
+    values[row] = base[bi];
+    indices[row] = bi;
+  }
+}
+
 template <class T>
 __global__ void max_scatter_kernel(const T* __restrict__ g, const int64_t* __restrict__ idx, T* __restrict__ out,
                                    int64_t n_out, int64_t reduce, int64_t inner) {
@@ -288,6 +329,13 @@ void k_max(OpCall& c) {
   const int64_t outer = c.i[0], reduce = c.i[1], inner = c.i[2];
   const int64_t n_out = outer * inner;
   if (n_out > 2147483647LL) throw std::invalid_argument("max: too many outputs");
+  if (inner == 1 && reduce >= 64) {
+    const int64_t threads_total = n_out * 32;
+    max_row_warp_kernel<T><<<static_cast<unsigned>((threads_total + kThreads - 1) / kThreads), kThreads, 0, stream_of(c)>>>(
+        c.in[0].data_as<T>(), c.out[0].data_as<T>(), c.out[1].data_as<int64_t>(), n_out, reduce);
+    check_launch("max");
+    return;
+  }
   max_kernel<T><<<static_cast<unsigned>(n_out), kThreads, 0, stream_of(c)>>>(c.in[0].data_as<T>(), c.out[0].data_as<T>(),
                                                                            c.out[1].data_as<int64_t>(), reduce, inner);
   check_launch("max");
