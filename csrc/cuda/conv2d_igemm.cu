@@ -48,47 +48,51 @@ Geom make_geom(const Shape& x, const Shape& w, const int64_t* i) {
   return g;
 }
 
-// col[n][crs][p] = x[n][c][oh*sh-ph+r][ow*sw-pw+s]  (0 outside the image and in padded rows)
+// col[n][crs][p] = x[n][c][oh*sh-ph+r][ow*sw-pw+s]  (0 outside the image and in padded rows).
+// One block per (n, crs) row of the column matrix: the filter tap is decoded once per block, every
+// thread produces 8 consecutive output positions with 32-bit index arithmetic and one 16-byte
+// store (P is a multiple of 8 on this path).
 template <class T>
 __global__ void unfold_kernel(const T* __restrict__ x, T* __restrict__ col, Geom g) {
-  const int64_t total = static_cast<int64_t>(g.N) * g.CRSp * g.P;
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-    const int p = static_cast<int>(i % g.P);
-    const int crs = static_cast<int>((i / g.P) % g.CRSp);
-    const int n = static_cast<int>(i / (static_cast<int64_t>(g.P) * g.CRSp));
-    T v = from_f<T>(0.f);
-    if (crs < g.CRS) {
-      const int s = crs % g.S, r = (crs / g.S) % g.R, c = crs / (g.S * g.R);
-      const int ih = (p / g.OW) * g.sh - g.ph + r, iw = (p % g.OW) * g.sw - g.pw + s;
-      if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) v = x[((static_cast<int64_t>(n) * g.C + c) * g.H + ih) * g.W + iw];
+  const int crs = blockIdx.x, n = blockIdx.y;
+  T* out = col + (static_cast<int64_t>(n) * g.CRSp + crs) * g.P;
+  const bool live = crs < g.CRS;
+  const int s = crs % g.S, r = (crs / g.S) % g.R, c = crs / (g.S * g.R);
+  const T* img = x + (static_cast<int64_t>(n) * g.C + (live ? c : 0)) * g.H * g.W;
+  for (int v = threadIdx.x; v < g.P / 8; v += blockDim.x) {
+    Pack<T> pk;
+    int oh = (v * 8) / g.OW, ow = (v * 8) - oh * g.OW;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int ih = oh * g.sh - g.ph + r, iw = ow * g.sw - g.pw + s;
+      pk.v[e] = (live && ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) ? img[ih * g.W + iw] : from_f<T>(0.f);
+      if (++ow == g.OW) { ow = 0; ++oh; }
     }
-    col[i] = v;
+    store_pack(out + v * 8, pk);
   }
 }
 
 // dx[n][c][ih][iw] = sum over (r, s) of dcol[n][(c,r,s)][oh*OW+ow] where the window maps back.
+// grid = (ceil(H*W / 256), C, N): channel and image come from the block index, so the per-pixel
+// work is 32-bit arithmetic only.
 template <class T>
 __global__ void fold_kernel(const T* __restrict__ dcol, T* __restrict__ dx, Geom g) {
-  const int64_t total = static_cast<int64_t>(g.N) * g.C * g.H * g.W;
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-    const int iw = static_cast<int>(i % g.W), ih = static_cast<int>((i / g.W) % g.H);
-    const int c = static_cast<int>((i / (static_cast<int64_t>(g.W) * g.H)) % g.C);
-    const int n = static_cast<int>(i / (static_cast<int64_t>(g.W) * g.H * g.C));
-    float acc = 0.f;
-    for (int r = 0; r < g.R; ++r) {
-      const int th = ih + g.ph - r;
-      if (th < 0 || th % g.sh != 0 || th / g.sh >= g.OH) continue;
-      for (int s = 0; s < g.S; ++s) {
-        const int tw = iw + g.pw - s;
-        if (tw < 0 || tw % g.sw != 0 || tw / g.sw >= g.OW) continue;
-        const int crs = (c * g.R + r) * g.S + s;
-        acc += to_f(dcol[(static_cast<int64_t>(n) * g.CRSp + crs) * g.P + (th / g.sh) * g.OW + tw / g.sw]);
-      }
+  const int c = blockIdx.y, n = blockIdx.z;
+  const int pix = blockIdx.x * blockDim.x + threadIdx.x;
+  if (pix >= g.H * g.W) return;
+  const int ih = pix / g.W, iw = pix - ih * g.W;
+  const T* rows = dcol + (static_cast<int64_t>(n) * g.CRSp + static_cast<int64_t>(c) * g.R * g.S) * g.P;
+  float acc = 0.f;
+  for (int r = 0; r < g.R; ++r) {
+    const int th = ih + g.ph - r;
+    if (th < 0 || th % g.sh != 0 || th / g.sh >= g.OH) continue;
+    for (int s = 0; s < g.S; ++s) {
+      const int tw = iw + g.pw - s;
+      if (tw < 0 || tw % g.sw != 0 || tw / g.sw >= g.OW) continue;
+      acc += to_f(rows[static_cast<int64_t>(r * g.S + s) * g.P + (th / g.sh) * g.OW + tw / g.sw]);
     }
-    dx[i] = from_f<T>(acc);
   }
+  dx[(static_cast<int64_t>(n) * g.C + c) * g.H * g.W + pix] = from_f<T>(acc);
 }
 
 // wp[k][crs] = w[k][crs] for crs < CRS else 0
@@ -115,7 +119,7 @@ Tensor padded_weight(const Tensor& w, const Geom& g, cudaStream_t st) {
 template <class T>
 Tensor unfold(const Tensor& x, const Geom& g, cudaStream_t st) {
   Tensor col = Tensor::empty({g.N, g.CRSp, g.P}, x.dtype(), x.device());
-  unfold_kernel<T><<<ew_grid(col.numel(), kThreads, sm_count_for(x)), kThreads, 0, st>>>(x.data_as<T>(), col.data_as<T>(), g);
+  unfold_kernel<T><<<dim3(static_cast<unsigned>(g.CRSp), static_cast<unsigned>(g.N)), 128, 0, st>>>(x.data_as<T>(), col.data_as<T>(), g);
   return col;
 }
 
@@ -167,7 +171,8 @@ bool conv_dgrad_igemm(OpCall& c) {
   Tensor g3 = Tensor::view_of(gy, Layout(Shape{g.N, g.K, g.P}, Layout::contiguous_strides({g.N, g.K, g.P}), gy.offset()));
   Tensor dcol = Tensor::empty({g.N, g.CRSp, g.P}, gy.dtype(), gy.device());
   gemm_launch(broadcast_batch(wp, g.N), true, g3, false, dcol, Tensor(), false, st);
-  fold_kernel<T><<<ew_grid(dx.numel(), kThreads, sm_count_for(dx)), kThreads, 0, st>>>(dcol.data_as<T>(), dx.data_as<T>(), g);
+  fold_kernel<T><<<dim3(static_cast<unsigned>((g.H * g.W + kThreads - 1) / kThreads), static_cast<unsigned>(g.C), static_cast<unsigned>(g.N)), kThreads, 0, st>>>(
+      dcol.data_as<T>(), dx.data_as<T>(), g);
   check_launch("conv2d dgrad (tcgen05)");
   return true;
 }

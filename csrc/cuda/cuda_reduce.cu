@@ -49,6 +49,30 @@ __global__ void row_sum_kernel(const T* __restrict__ in, float* __restrict__ par
   }
 }
 
+// Short rows (inner == 1, a few thousand elements): one warp per row, shuffles only.
+template <class T>
+__global__ void row_sum_warp_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t rows, int64_t reduce, float scale) {
+  constexpr int N = Pack<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int64_t o = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (o >= rows) return;
+  const T* row = in + o * reduce;
+  float acc = 0.f;
+  int64_t i = 0;
+  if ((reinterpret_cast<uintptr_t>(row) & 15u) == 0) {
+    const int64_t nv = reduce / N;
+    for (int64_t v = lane; v < nv; v += 32) {
+      const Pack<T> p = load_pack(row + v * N);
+#pragma unroll
+      for (int k = 0; k < N; ++k) acc += to_f(p.v[k]);
+    }
+    i = nv * N;
+  }
+  for (int64_t j = i + lane; j < reduce; j += 32) acc += to_f(row[j]);
+  acc = warp_sum(acc);
+  if (lane == 0) out[o] = from_f<T>(acc * scale);
+}
+
 // in: [outer, reduce, inner] with inner > 1.  block = (32, 8); grid = (ceil(inner/32), splits, outer).
 template <class T>
 __global__ void col_sum_kernel(const T* __restrict__ in, float* __restrict__ partial, T* __restrict__ out,
@@ -177,6 +201,11 @@ void sum_launch(const T* in, T* out, int64_t outer, int64_t reduce, int64_t inne
         row_sum_kernel<T><<<dim3(1, static_cast<unsigned>(no)), kThreads, 0, st>>>(in + o0 * reduce, nullptr, out + o0,
                                                                                reduce, reduce, 1, scale);
       }
+      check_launch("row sum");
+      return;
+    }
+    if (splits == 1 && reduce <= 8192 && outer >= static_cast<int64_t>(sms) * 8) {
+      row_sum_warp_kernel<T><<<static_cast<unsigned>((outer * 32 + kThreads - 1) / kThreads), kThreads, 0, st>>>(in, out, outer, reduce, scale);
       check_launch("row sum");
       return;
     }

@@ -239,3 +239,27 @@ def test_fused_mlp_matches_composed_linears():
 
     for a, b in zip(run(True), run(False)):
         assert np.allclose(a, b, rtol=1e-5, atol=1e-5)
+
+
+def test_functional_reductions_and_max_returns_values():
+    import numpy as np
+    import orthon_b200.functional as F
+    from orthon_b200 import _C
+    x = _C.from_numpy(np.asarray([[1.0, 5.0, 2.0], [7.0, 0.0, 3.0]], dtype=np.float32))
+    assert F.sum(x).item() == 18.0 and np.allclose(F.mean(x, 1).tolist(), [8.0 / 3, 10.0 / 3], rtol=1e-6)
+    m = F.max(x, 1)
+    assert isinstance(m, _C.Tensor) and m.tolist() == [5.0, 7.0]  # values only; indices come from argmax
+    assert F.argmax(x, 1).tolist() == [1, 0] and F.max(x).item() == 7.0
+    assert np.allclose(F.exp(x).tolist(), np.exp([1, 5, 2, 7, 0, 3]), rtol=1e-6)
+
+
+def test_diagnostics_pool_switches():
+    from orthon_b200 import _diagnostics as diag
+    assert diag.memory_pool_enabled() in (True, False)
+    before = diag.memory_pool_max_cached_bytes()
+    diag.memory_pool_set_max_cached_bytes(1 << 20)
+    assert diag.memory_pool_max_cached_bytes() == 1 << 20
+    diag.memory_pool_set_max_cached_bytes(before)
+    stats = diag.memory_pool_stats()
+    assert {"current_bytes", "peak_bytes", "cached_bytes"} <= set(stats)
+    assert isinstance(diag.dispatch_kernels(), (list, tuple, dict))
