@@ -8,8 +8,9 @@
 //   backward: dQ, dK, dV from (qkv, O, LSE, dO) with the probabilities recomputed tile by tile
 //
 // Forward design (one CTA = one (batch, head) and 256 query rows, 320 threads):
-//   warp 0      TMA producer: Q (two 128-row tiles, once), then K_j / V_j tiles of 128 keys
-//   warp 1      one thread issues tcgen05.mma: S_w = Q_w K_j^T (TMEM, 128 fp32 columns per query
+//   warp 0      TMA producer: Q (two 128-row tiles, once), then K_j / V_j tiles of 64 keys through
+//               two 4-stage rings
+//   warp 1      one thread issues tcgen05.mma: S_w = Q_w K_j^T (TMEM, 64 fp32 columns per query
 //               tile) and O_w += P_w V_j (TMEM, D columns per query tile)
 //   warps 2-5   softmax group 0, warps 6-9 softmax group 1: one thread per query row reads its
 //               S row from TMEM, keeps the running max / sum (online softmax, base-2 exponent),
@@ -81,36 +82,42 @@ __device__ __forceinline__ uint4 pack8(const float* v) {
 }
 
 // ------------------------------------------------------------------ forward
+constexpr int kKeys = 64;  // keys per K / V tile of the forward kernel
+
+// Q (two 128-row tiles) stays resident; K and V stream through rings of kStages 64-key tiles each
+// (deep enough that the TMA latency of about 5000 cycles hides behind the MMAs of the tiles in
+// between); P holds one [128 x 64] probability tile per softmax group.
 template <int D>
 struct FwdSmem {
   static constexpr int kQBytes = kTile * D * 2;        // one query tile
-  static constexpr int kKVBytes = kTile * D * 2;       // one K or V tile
-  static constexpr int kPBytes = kTile * kTile * 2;    // one probability tile
-  static constexpr int kKStages = 2;
-  static constexpr int kVStages = (D == 128) ? 1 : 2;
+  static constexpr int kKVBytes = kKeys * D * 2;       // one K or V tile
+  static constexpr int kPBytes = kTile * kKeys * 2;    // one probability tile
+  static constexpr int kStages = 4;
   static constexpr int kQOff = 0;
   static constexpr int kKOff = kQOff + 2 * kQBytes;
-  static constexpr int kVOff = kKOff + kKStages * kKVBytes;
-  static constexpr int kPOff = kVOff + kVStages * kKVBytes;
+  static constexpr int kVOff = kKOff + kStages * kKVBytes;
+  static constexpr int kPOff = kVOff + kStages * kKVBytes;
   static constexpr int kBarOff = kPOff + 2 * kPBytes;
   static constexpr int kTotal = kBarOff + 256 + 1024;  // +1024 for manual alignment
+  static_assert(kTotal <= 232448, "exceeds the shared memory of one CTA");
 };
 
 constexpr int kFwdThreads = 320;
 
 template <class T, int D>
 __global__ void __launch_bounds__(kFwdThreads, 1)
-flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_o, FlashParams p) {
+flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q128, const __grid_constant__ CUtensorMap map_kv64,
+                 const __grid_constant__ CUtensorMap map_o, FlashParams p) {
   using L = FwdSmem<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
   uint64_t* q_full = bars;                      // 1
-  uint64_t* k_full = q_full + 1;                // kKStages
-  uint64_t* k_empty = k_full + L::kKStages;
-  uint64_t* v_full = k_empty + L::kKStages;     // kVStages
-  uint64_t* v_empty = v_full + L::kVStages;
-  uint64_t* s_full = v_empty + L::kVStages;     // 2
+  uint64_t* k_full = q_full + 1;                // kStages
+  uint64_t* k_empty = k_full + L::kStages;
+  uint64_t* v_full = k_empty + L::kStages;      // kStages
+  uint64_t* v_empty = v_full + L::kStages;
+  uint64_t* s_full = v_empty + L::kStages;      // 2
   uint64_t* p_full = s_full + 2;                // 2
   uint64_t* o_done = p_full + 2;                // 2
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
@@ -118,20 +125,23 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh = blockIdx.x, b = bh / p.H, h = bh - b * p.H;
   const int n_pairs = gridDim.y;
-  const int pair = n_pairs - 1 - static_cast<int>(blockIdx.y);  // heaviest (latest rows) first
-  const int n_tiles = (p.T + kTile - 1) / kTile;
-  // Number of key tiles each query tile needs.
+  const int pair = n_pairs - 1 - static_cast<int>(blockIdx.y);  // heaviest (latest rows) first for every head
+  const int n_qtiles = (p.T + kTile - 1) / kTile;
+  const int n_ktiles = (p.T + kKeys - 1) / kKeys;
+  // Number of key tiles each query tile needs (the causal mask ends at the tile's last row).
   auto tiles_for = [&](int w) {
     const int qt = 2 * pair + w;
-    return (qt >= n_tiles) ? 0 : (p.causal ? min(n_tiles, qt + 1) : n_tiles);
+    return (qt >= n_qtiles) ? 0 : (p.causal ? min(n_ktiles, 2 * qt + 2) : n_ktiles);
   };
   const int n_w0 = tiles_for(0), n_w1 = tiles_for(1);
   const int n_kv = max(n_w0, n_w1);
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < L::kKStages; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
-    for (int s = 0; s < L::kVStages; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+    for (int s = 0; s < L::kStages; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+    }
     for (int w = 0; w < 2; ++w) { mbar_init(&s_full[w], 1); mbar_init(&p_full[w], 4); mbar_init(&o_done[w], 1); }
     mbar_init_fence();
   }
@@ -140,8 +150,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  auto tmem_s = [&](int w) { return tmem_base + static_cast<uint32_t>(w) * 128u; };
-  auto tmem_o = [&](int w) { return tmem_base + 256u + static_cast<uint32_t>(w) * D; };
+  auto tmem_s = [&](int w) { return tmem_base + static_cast<uint32_t>(w) * kKeys; };
+  auto tmem_o = [&](int w) { return tmem_base + 2u * kKeys + static_cast<uint32_t>(w) * D; };
 
   const int col_q = h * D, col_k = p.E + h * D, col_v = 2 * p.E + h * D;
 
@@ -153,48 +163,51 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_const
       for (int w = 0; w < 2; ++w)
 #pragma unroll
         for (int c = 0; c < D / 64; ++c)
-          tma_load_3d(smem + L::kQOff + w * L::kQBytes + c * (kTile * 128), &map_qkv, q_full, col_q + c * 64,
+          tma_load_3d(smem + L::kQOff + w * L::kQBytes + c * (kTile * 128), &map_q128, q_full, col_q + c * 64,
                       (2 * pair + w) * kTile, b);
-      bool ok = true;
-      for (int j = 0; j < n_kv && ok; ++j) {
-        const int ks = j % L::kKStages, vs = j % L::kVStages;
-        if (!mbar_wait(&k_empty[ks], ((j / L::kKStages) & 1) ^ 1, p.err, kErrAttnProducer)) { ok = false; break; }
-        mbar_expect_tx(&k_full[ks], L::kKVBytes);
+      for (int j = 0; j < n_kv; ++j) {
+        const int st = j % L::kStages;
+        const uint32_t parity = ((j / L::kStages) & 1) ^ 1;
+        if (!mbar_wait(&k_empty[st], parity, p.err, kErrAttnProducer)) break;
+        mbar_expect_tx(&k_full[st], L::kKVBytes);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c)
-          tma_load_3d(smem + L::kKOff + ks * L::kKVBytes + c * (kTile * 128), &map_qkv, &k_full[ks], col_k + c * 64, j * kTile, b);
-        if (!mbar_wait(&v_empty[vs], ((j / L::kVStages) & 1) ^ 1, p.err, kErrAttnProducer)) { ok = false; break; }
-        mbar_expect_tx(&v_full[vs], L::kKVBytes);
+          tma_load_3d(smem + L::kKOff + st * L::kKVBytes + c * (kKeys * 128), &map_kv64, &k_full[st], col_k + c * 64, j * kKeys, b);
+        if (!mbar_wait(&v_empty[st], parity, p.err, kErrAttnProducer)) break;
+        mbar_expect_tx(&v_full[st], L::kKVBytes);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c)
-          tma_load_3d(smem + L::kVOff + vs * L::kKVBytes + c * (kTile * 128), &map_qkv, &v_full[vs], col_v + c * 64, j * kTile, b);
+          tma_load_3d(smem + L::kVOff + st * L::kKVBytes + c * (kKeys * 128), &map_kv64, &v_full[st], col_v + c * 64, j * kKeys, b);
       }
     }
   } else if (warp == 1) {
     // --------------------------------------------------------------- MMA issuer
     if (lane == 0 && n_kv > 0) {
       const bool bf = std::is_same<T, __nv_bfloat16>::value;
-      const uint32_t idesc_s = make_idesc(bf, 0, 0, kTile, kTile);  // S = Q K^T  (both K-major)
+      const uint32_t idesc_s = make_idesc(bf, 0, 0, kTile, kKeys);  // S = Q K^T  (both K-major)
       const uint32_t idesc_o = make_idesc(bf, 0, 1, kTile, D);      // O = P V    (V is MN-major)
-      auto issue_s = [&](int w, int ks) {
-        const uint32_t sq = smem_u32(smem + L::kQOff + w * L::kQBytes);
-        const uint32_t sk = smem_u32(smem + L::kKOff + ks * L::kKVBytes);
+      // Base descriptors once; every MMA then costs two adds (see desc_advance).
+      const uint64_t dq_base = make_desc(smem_u32(smem + L::kQOff), 16, 1024);
+      const uint64_t dk_base = make_desc(smem_u32(smem + L::kKOff), 16, 1024);
+      const uint64_t dp_base = make_desc(smem_u32(smem + L::kPOff), 16, 1024);
+      const uint64_t dv_base = make_desc(smem_u32(smem + L::kVOff), kKeys * 128, 1024);
+      auto issue_s = [&](int w, int st) {
+        const uint64_t dq = desc_advance(dq_base, w * L::kQBytes), dk = desc_advance(dk_base, st * L::kKVBytes);
+        const uint32_t d = tmem_s(w);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * (kTile * 128) + (kk % 4) * 32;
-          umma_f16(tmem_s(w), make_desc(sq + off, 16, 1024), make_desc(sk + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+          constexpr int kBlockA = kTile * 128, kBlockB = kKeys * 128;
+          umma_f16(d, desc_advance(dq, (kk / 4) * kBlockA + (kk % 4) * 32), desc_advance(dk, (kk / 4) * kBlockB + (kk % 4) * 32),
+                   idesc_s, kk > 0 ? 1u : 0u);
         }
         umma_commit(&s_full[w]);
       };
-      auto issue_o = [&](int w, int vs, bool accumulate) {
-        const uint32_t sp = smem_u32(smem + L::kPOff + w * L::kPBytes);
-        const uint32_t sv = smem_u32(smem + L::kVOff + vs * L::kKVBytes);
+      auto issue_o = [&](int w, int st, bool accumulate) {
+        const uint64_t dp = desc_advance(dp_base, w * L::kPBytes), dv = desc_advance(dv_base, st * L::kKVBytes);
+        const uint32_t d = tmem_o(w);
 #pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk) {
-          const uint32_t a_off = (kk / 4) * (kTile * 128) + (kk % 4) * 32;
-          umma_f16(tmem_o(w), make_desc(sp + a_off, 16, 1024), make_desc(sv + kk * 2048, kTile * 128, 1024), idesc_o,
-                   (accumulate || kk > 0) ? 1u : 0u);
-        }
+        for (int kk = 0; kk < kKeys / 16; ++kk)
+          umma_f16(d, desc_advance(dp, kk * 32), desc_advance(dv, kk * 2048), idesc_o, (accumulate || kk > 0) ? 1u : 0u);
         umma_commit(&o_done[w]);
       };
       bool ok = mbar_wait(q_full, 0, p.err, kErrAttnMma);
@@ -206,28 +219,28 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_const
         umma_commit(&k_empty[0]);
       }
       for (int j = 0; j < n_kv && ok; ++j) {
-        const int vs = j % L::kVStages, ks_next = (j + 1) % L::kKStages;
-        if (!mbar_wait(&v_full[vs], (j / L::kVStages) & 1, p.err, kErrAttnMma)) { ok = false; break; }
+        const int st = j % L::kStages, st_next = (j + 1) % L::kStages;
+        if (!mbar_wait(&v_full[st], (j / L::kStages) & 1, p.err, kErrAttnMma)) { ok = false; break; }
         bool k_ready = false;
         for (int w = 0; w < 2 && ok; ++w) {
           const int n_w = w ? n_w1 : n_w0;
           if (j < n_w) {
             if (!mbar_wait(&p_full[w], j & 1, p.err, kErrAttnMma)) { ok = false; break; }
             tc_fence_after();
-            issue_o(w, vs, j > 0);
+            issue_o(w, st, j > 0);
           }
           if (j + 1 < n_w) {
             if (!k_ready) {
-              if (!mbar_wait(&k_full[ks_next], ((j + 1) / L::kKStages) & 1, p.err, kErrAttnMma)) { ok = false; break; }
+              if (!mbar_wait(&k_full[st_next], ((j + 1) / L::kStages) & 1, p.err, kErrAttnMma)) { ok = false; break; }
               tc_fence_after();
               k_ready = true;
             }
-            issue_s(w, ks_next);  // P_w ready implies S_w has been read out
+            issue_s(w, st_next);  // P_w ready implies S_w has been read out
           }
         }
         if (!ok) break;
-        umma_commit(&v_empty[vs]);
-        if (j + 1 < n_kv) umma_commit(&k_empty[ks_next]);
+        umma_commit(&v_empty[st]);
+        if (j + 1 < n_kv) umma_commit(&k_empty[st_next]);
       }
     }
   } else {
@@ -235,7 +248,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_const
     const int w = (warp - 2) >> 2;        // query tile within the pair
     const int quarter = warp & 3;         // TMEM lane quarter of this warp
     const int r = quarter * 32 + lane;    // row within the query tile
-    const int q_row = (2 * pair + w) * kTile + r;
+    const int q_tile0 = (2 * pair + w) * kTile;
+    const int q_row = q_tile0 + r;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     uint8_t* sp = smem + L::kPOff + w * L::kPBytes;
     const int n_it = w ? n_w1 : n_w0;
@@ -244,34 +258,41 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_const
     for (int j = 0; j < n_it && ok; ++j) {
       if (!warp_wait(&s_full[w], j & 1, p.err, kErrAttnSoftmax)) { ok = false; break; }
       tc_fence_after();
-      float s[kTile];
-#pragma unroll
-      for (int c = 0; c < kTile / 32; ++c) tmem_ld32_nowait(tmem_s(w) + lane_off + c * 32, s + c * 32);
+      float s[kKeys];
+      tmem_ld32_nowait(tmem_s(w) + lane_off, s);
+      tmem_ld32_nowait(tmem_s(w) + lane_off + 32, s + 32);
       tmem_ld_wait();
-      // Mask: keys past the sequence end, and keys after the query on the diagonal tile.
-      const int key0 = j * kTile;
-      const bool diag = p.causal && (j == 2 * pair + w);
-      if (diag || key0 + kTile > p.T) {
+      // Mask: keys past the sequence end, and keys after the query on tiles that reach the diagonal.
+      const int key0 = j * kKeys;
+      const bool diag = p.causal && (key0 + kKeys - 1 > q_tile0);
+      if (diag || key0 + kKeys > p.T) {
         const int limit = diag ? min(q_row, p.T - 1) : p.T - 1;  // last visible key
 #pragma unroll
-        for (int c = 0; c < kTile; ++c)
+        for (int c = 0; c < kKeys; ++c)
           if (key0 + c > limit) s[c] = -INFINITY;
       }
-      float mx4[4] = {s[0], s[1], s[2], s[3]};  // four independent chains instead of one of 128
+      float mx4[4] = {s[0], s[1], s[2], s[3]};  // four independent chains instead of one of 64
 #pragma unroll
-      for (int c = 4; c < kTile; c += 4) {
+      for (int c = 4; c < kKeys; c += 4) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) mx4[i] = fmaxf(mx4[i], s[c + i]);
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      float m_new = fmaxf(m, mx * p.scale_log2);
-      if (m_new == -INFINITY) m_new = 0.f;  // fully masked row (only rows past the sequence end)
-      const float alpha = fast_exp2(m - m_new);
+      // `m` is the exponent offset in use (log2 units), not necessarily the running maximum: it is
+      // only moved, together with a rescale of the O accumulator, when some row of the warp has
+      // grown past it by more than 2^8.  Until then p = 2^(s - m) stays below 256, which both
+      // 16-bit formats hold, and the row sum and O stay consistent, so the result is unchanged;
+      // the TMEM round trip of the rescale leaves the per-tile critical path.
+      float m_cand = fmaxf(m, mx * p.scale_log2);
+      if (m_cand == -INFINITY) m_cand = 0.f;  // fully masked row (rows past the sequence end)
+      const bool move = (j == 0) || __any_sync(0xffffffffu, m_cand > m + 8.f);
+      const float m_new = move ? m_cand : m;
+      const float alpha = move ? fast_exp2(m - m_new) : 1.f;
       if (j > 0) {
         // P_{j-1} V has finished: the O accumulator is consistent and the P tile is free.
         if (!warp_wait(&o_done[w], (j - 1) & 1, p.err, kErrAttnSoftmax)) { ok = false; break; }
         tc_fence_after();
-        if (__any_sync(0xffffffffu, m_new > m)) {
+        if (move) {
 #pragma unroll 1
           for (int c = 0; c < D / 32; ++c) {
             float o[32];
@@ -285,14 +306,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_const
       }
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c8 = 0; c8 < kTile / 8; ++c8) {
+      for (int c8 = 0; c8 < kKeys / 8; ++c8) {
         float pv[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           pv[i] = fast_exp2(fmaf(s[c8 * 8 + i], p.scale_log2, -m_new));
           sum4[i & 3] += pv[i];
         }
-        *reinterpret_cast<uint4*>(sp + (c8 / 8) * (kTile * 128) + sw128_offset(r, c8 % 8)) = pack8<T>(pv);
+        *reinterpret_cast<uint4*>(sp + sw128_offset(r, c8)) = pack8<T>(pv);
       }
       l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
       m = m_new;
@@ -304,7 +325,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_const
     if (ok && n_it > 0 && warp_wait(&o_done[w], (n_it - 1) & 1, p.err, kErrAttnSoftmax)) {
       tc_fence_after();
       const float inv_l = 1.f / l;
-      // Stage this warp's 32 rows (the P tile is free now) and store them with TMA.
+      // Every MMA of this query tile has finished, so its Q tile is idle: stage this warp's 32 rows
+      // there and store them with TMA.
+      uint8_t* so = smem + L::kQOff + w * L::kQBytes;
 #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
         float o[32];
@@ -313,15 +336,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_const
         for (int i = 0; i < 32; ++i) o[i] *= inv_l;
 #pragma unroll
         for (int q = 0; q < 4; ++q)
-          *reinterpret_cast<uint4*>(sp + (c / 2) * (kTile * 128) + sw128_offset(r, (c % 2) * 4 + q)) = pack8<T>(o + q * 8);
+          *reinterpret_cast<uint4*>(so + (c / 2) * (kTile * 128) + sw128_offset(r, (c % 2) * 4 + q)) = pack8<T>(o + q * 8);
       }
       fence_async_smem();
       __syncwarp();
-      const int store_row = (2 * pair + w) * kTile + quarter * 32;
+      const int store_row = q_tile0 + quarter * 32;
       if (lane == 0 && store_row < p.T) {  // rows past the end of a partly covered box are clipped by TMA
 #pragma unroll
         for (int c = 0; c < D / 64; ++c)
-          tma_store_3d(&map_o, sp + c * (kTile * 128) + quarter * 32 * 128, h * D + c * 64, store_row, b);
+          tma_store_3d(&map_o, so + c * (kTile * 128) + quarter * 32 * 128, h * D + c * 64, store_row, b);
         tma_store_wait_all();
       }
       if (q_row < p.T) p.lse[(static_cast<long long>(b) * p.H + h) * p.T + q_row] = (m + log2f(l)) * 0.6931471805599453f;
@@ -364,7 +387,7 @@ constexpr int kSub = 64;  // rows of the streamed operand per step (N of the sco
 // Shared-memory plan of the backward kernels: two resident [128 x D] tiles, a ring of streamed
 // [64 x D] tile pairs (deep enough to hide the TMA latency behind the MMAs of the other ring
 // slots), and OPS double-buffered [128 x 64] operand tiles written by the softmax warps.
-template <int D, int OPS, int STAGES>
+template <int D, int OPS, int NBUF, int STAGES>
 struct BwdSmem {
   static constexpr int kBigBytes = kTile * D * 2;   // resident tile
   static constexpr int kSubBytes = kSub * D * 2;    // streamed tile
@@ -372,13 +395,15 @@ struct BwdSmem {
   static constexpr int kStages = STAGES;
   static constexpr int kBigOff = 0;                                   // two resident tiles
   static constexpr int kRingOff = kBigOff + 2 * kBigBytes;            // kStages x (two streamed tiles)
-  static constexpr int kOpOff = kRingOff + kStages * 2 * kSubBytes;   // [2 buffers][OPS tiles]
-  static constexpr int kBarOff = kOpOff + 2 * OPS * kOpBytes;
+  static constexpr int kOpBufs = NBUF;
+  static constexpr int kOpOff = kRingOff + kStages * 2 * kSubBytes;   // [NBUF buffers][OPS tiles]
+  static constexpr int kBarOff = kOpOff + NBUF * OPS * kOpBytes;
   static constexpr int kTotal = kBarOff + 256 + 1024;
   static_assert(kTotal <= 232448, "exceeds the shared memory of one CTA");
 };
-template <int D> using DkvSmem = BwdSmem<D, 2, (D == 128) ? 3 : 4>;
-template <int D> using DqSmem = BwdSmem<D, 1, 4>;
+// dK/dV: P^T and dS^T double-buffered (measured faster than a deeper ring with single buffers).
+template <int D> using DkvSmem = BwdSmem<D, 2, 2, (D == 128) ? 3 : 4>;
+template <int D> using DqSmem = BwdSmem<D, 1, 2, 4>;
 
 // dK, dV: one CTA per (batch, head, 128-key tile); streams 64-row query tiles.
 //   S^T = K Q^T, dP^T = V dO^T (TMEM, 64 columns each, double buffered); one thread per key row
@@ -451,20 +476,22 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gri
       const bool bf = std::is_same<T, __nv_bfloat16>::value;
       const uint32_t idesc_s = make_idesc(bf, 0, 0, kTile, kSub);  // [128 keys x 64 queries], both K-major
       const uint32_t idesc_a = make_idesc(bf, 0, 1, kTile, D);     // [128 keys x D], B operand MN-major
+      const uint64_t dk_base = make_desc(smem_u32(sk), 16, 1024), dv_base = make_desc(smem_u32(sv), 16, 1024);
+      const uint64_t ring_k = make_desc(smem_u32(smem + L::kRingOff), 16, 1024);            // streamed tiles as K-major B
+      const uint64_t ring_mn = make_desc(smem_u32(smem + L::kRingOff), kSub * 128, 1024);   // the same tiles as MN-major B
+      const uint64_t op_base = make_desc(smem_u32(smem + L::kOpOff), 16, 1024);
       auto issue_scores = [&](int buf, int st) {
-        const uint32_t a_k = smem_u32(sk), a_v = smem_u32(sv);
-        const uint32_t b_q = smem_u32(smem + L::kRingOff + st * 2 * L::kSubBytes), b_do = b_q + L::kSubBytes;
+        const uint64_t b_q = desc_advance(ring_k, st * 2 * L::kSubBytes), b_do = desc_advance(b_q, L::kSubBytes);
         const uint32_t d_s = tmem_base + buf * 128, d_dp = d_s + 64;
+        constexpr int kBlockA = kTile * 128, kBlockB = kSub * 128;
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t a_off = (kk / 4) * (kTile * 128) + (kk % 4) * 32, b_off = (kk / 4) * (kSub * 128) + (kk % 4) * 32;
-          umma_f16(d_s, make_desc(a_k + a_off, 16, 1024), make_desc(b_q + b_off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
-        }
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_f16(d_s, desc_advance(dk_base, (kk / 4) * kBlockA + (kk % 4) * 32), desc_advance(b_q, (kk / 4) * kBlockB + (kk % 4) * 32),
+                   idesc_s, kk > 0 ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t a_off = (kk / 4) * (kTile * 128) + (kk % 4) * 32, b_off = (kk / 4) * (kSub * 128) + (kk % 4) * 32;
-          umma_f16(d_dp, make_desc(a_v + a_off, 16, 1024), make_desc(b_do + b_off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
-        }
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_f16(d_dp, desc_advance(dv_base, (kk / 4) * kBlockA + (kk % 4) * 32), desc_advance(b_do, (kk / 4) * kBlockB + (kk % 4) * 32),
+                   idesc_s, kk > 0 ? 1u : 0u);
         umma_commit(&sdp_full[buf]);
       };
       bool ok = mbar_wait(kv_full, 0, p.err, kErrAttnMma) && mbar_wait(&ring_full[0], 0, p.err, kErrAttnMma);
@@ -482,16 +509,14 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gri
         }
         if (!mbar_wait(&pds_full[buf], (it >> 1) & 1, p.err, kErrAttnMma)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t a_p = smem_u32(smem + L::kOpOff + buf * 2 * L::kOpBytes), a_ds = a_p + L::kOpBytes;
-        const uint32_t b_q = smem_u32(smem + L::kRingOff + st * 2 * L::kSubBytes), b_do = b_q + L::kSubBytes;
+        const uint64_t a_p = desc_advance(op_base, buf * 2 * L::kOpBytes), a_ds = desc_advance(a_p, L::kOpBytes);
+        const uint64_t b_q = desc_advance(ring_mn, st * 2 * L::kSubBytes), b_do = desc_advance(b_q, L::kSubBytes);
 #pragma unroll
         for (int kk = 0; kk < kSub / 16; ++kk)
-          umma_f16(tmem_dv, make_desc(a_p + kk * 32, 16, 1024), make_desc(b_do + kk * 2048, kSub * 128, 1024), idesc_a,
-                   (it > 0 || kk > 0) ? 1u : 0u);
+          umma_f16(tmem_dv, desc_advance(a_p, kk * 32), desc_advance(b_do, kk * 2048), idesc_a, (it > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < kSub / 16; ++kk)
-          umma_f16(tmem_dk, make_desc(a_ds + kk * 32, 16, 1024), make_desc(b_q + kk * 2048, kSub * 128, 1024), idesc_a,
-                   (it > 0 || kk > 0) ? 1u : 0u);
+          umma_f16(tmem_dk, desc_advance(a_ds, kk * 32), desc_advance(b_q, kk * 2048), idesc_a, (it > 0 || kk > 0) ? 1u : 0u);
         umma_commit(&ring_empty[st]);
         umma_commit(&pds_free[buf]);
       }
@@ -656,20 +681,22 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid
       const bool bf = std::is_same<T, __nv_bfloat16>::value;
       const uint32_t idesc_s = make_idesc(bf, 0, 0, kTile, kSub);  // [128 queries x 64 keys], both K-major
       const uint32_t idesc_a = make_idesc(bf, 0, 1, kTile, D);     // [128 queries x D], K tile read MN-major
+      const uint64_t dq_base = make_desc(smem_u32(sq), 16, 1024), ddo_base = make_desc(smem_u32(sdo), 16, 1024);
+      const uint64_t ring_k = make_desc(smem_u32(smem + L::kRingOff), 16, 1024);            // streamed tiles as K-major B
+      const uint64_t ring_mn = make_desc(smem_u32(smem + L::kRingOff), kSub * 128, 1024);   // the same tiles as MN-major B
+      const uint64_t op_base = make_desc(smem_u32(smem + L::kOpOff), 16, 1024);
       auto issue_scores = [&](int buf, int st) {
-        const uint32_t a_q = smem_u32(sq), a_do = smem_u32(sdo);
-        const uint32_t b_k = smem_u32(smem + L::kRingOff + st * 2 * L::kSubBytes), b_v = b_k + L::kSubBytes;
+        const uint64_t b_k = desc_advance(ring_k, st * 2 * L::kSubBytes), b_v = desc_advance(b_k, L::kSubBytes);
         const uint32_t d_s = tmem_base + buf * 128, d_dp = d_s + 64;
+        constexpr int kBlockA = kTile * 128, kBlockB = kSub * 128;
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t a_off = (kk / 4) * (kTile * 128) + (kk % 4) * 32, b_off = (kk / 4) * (kSub * 128) + (kk % 4) * 32;
-          umma_f16(d_s, make_desc(a_q + a_off, 16, 1024), make_desc(b_k + b_off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
-        }
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_f16(d_s, desc_advance(dq_base, (kk / 4) * kBlockA + (kk % 4) * 32), desc_advance(b_k, (kk / 4) * kBlockB + (kk % 4) * 32),
+                   idesc_s, kk > 0 ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t a_off = (kk / 4) * (kTile * 128) + (kk % 4) * 32, b_off = (kk / 4) * (kSub * 128) + (kk % 4) * 32;
-          umma_f16(d_dp, make_desc(a_do + a_off, 16, 1024), make_desc(b_v + b_off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
-        }
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_f16(d_dp, desc_advance(ddo_base, (kk / 4) * kBlockA + (kk % 4) * 32), desc_advance(b_v, (kk / 4) * kBlockB + (kk % 4) * 32),
+                   idesc_s, kk > 0 ? 1u : 0u);
         umma_commit(&sdp_full[buf]);
       };
       bool ok = mbar_wait(q_full, 0, p.err, kErrAttnMma) && mbar_wait(&ring_full[0], 0, p.err, kErrAttnMma);
@@ -687,12 +714,11 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid
         }
         if (!mbar_wait(&ds_full[buf], (it >> 1) & 1, p.err, kErrAttnMma)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t a_ds = smem_u32(smem + L::kOpOff + buf * L::kOpBytes);
-        const uint32_t b_k = smem_u32(smem + L::kRingOff + st * 2 * L::kSubBytes);
+        const uint64_t a_ds = desc_advance(op_base, buf * L::kOpBytes);
+        const uint64_t b_k = desc_advance(ring_mn, st * 2 * L::kSubBytes);
 #pragma unroll
         for (int kk = 0; kk < kSub / 16; ++kk)
-          umma_f16(tmem_dq, make_desc(a_ds + kk * 32, 16, 1024), make_desc(b_k + kk * 2048, kSub * 128, 1024), idesc_a,
-                   (it > 0 || kk > 0) ? 1u : 0u);
+          umma_f16(tmem_dq, desc_advance(a_ds, kk * 32), desc_advance(b_k, kk * 2048), idesc_a, (it > 0 || kk > 0) ? 1u : 0u);
         umma_commit(&ring_empty[st]);
         umma_commit(&ds_free[buf]);
       }
@@ -788,6 +814,7 @@ void launch_fwd(const Tensor& qkv, Tensor& out, Tensor& lse, int B, int Tn, int 
   using L = FwdSmem<D>;
   const int E = H * D;
   const CUtensorMap mq = make_map3(qkv, 3 * E, Tn, B, kTile, "qkv");
+  const CUtensorMap mkv = make_map3(qkv, 3 * E, Tn, B, kKeys, "qkv");
   const CUtensorMap mo = make_map3(out, E, Tn, B, 32, "the output");
   FlashParams p{};
   p.B = B; p.H = H; p.T = Tn; p.E = E; p.causal = causal ? 1 : 0;
@@ -800,7 +827,7 @@ void launch_fwd(const Tensor& qkv, Tensor& out, Tensor& lse, int B, int Tn, int 
   });
   const int n_tiles = (Tn + kTile - 1) / kTile;
   dim3 grid(B * H, (n_tiles + 1) / 2);
-  flash_fwd_kernel<T, D><<<grid, kFwdThreads, L::kTotal, st>>>(mq, mo, p);
+  flash_fwd_kernel<T, D><<<grid, kFwdThreads, L::kTotal, st>>>(mq, mkv, mo, p);
   check_launch("flash_attention_forward");
 }
 
@@ -848,7 +875,7 @@ bool flash_attention_supported(const Tensor& qkv, int64_t heads) {
   const int64_t D = E / heads;
   if (D != 64 && D != 128) return false;
   if ((reinterpret_cast<uintptr_t>(qkv.data()) & 15u) != 0) return false;
-  if (qkv.shape()[0] * heads > 65535 * 32 || qkv.shape()[1] < 1) return false;
+  if (qkv.shape()[1] < 1 || qkv.shape()[1] > 65535 * 64) return false;  // sequence tiles are the grid's y extent
   static const bool off = [] { const char* e = std::getenv("ORTHON_ATTENTION"); return e != nullptr && std::string(e) == "composed"; }();
   return !off;
 }

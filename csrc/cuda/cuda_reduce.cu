@@ -195,17 +195,17 @@ void sum_launch(const T* in, T* out, int64_t outer, int64_t reduce, int64_t inne
     int64_t chunk = (reduce + splits - 1) / splits;
     chunk = (chunk + 7) & ~int64_t(7);  // keep chunk starts 16-byte aligned for 2-byte types
     splits = static_cast<int>((reduce + chunk - 1) / chunk);
+    if (splits == 1 && reduce <= 8192 && outer >= static_cast<int64_t>(sms) * 8) {
+      row_sum_warp_kernel<T><<<static_cast<unsigned>((outer * 32 + kThreads - 1) / kThreads), kThreads, 0, st>>>(in, out, outer, reduce, scale);
+      check_launch("row sum");
+      return;
+    }
     if (outer > 65535) {  // grid.y limit: fall back to one row per block in x
       for (int64_t o0 = 0; o0 < outer; o0 += 65535) {
         const int64_t no = std::min<int64_t>(65535, outer - o0);
         row_sum_kernel<T><<<dim3(1, static_cast<unsigned>(no)), kThreads, 0, st>>>(in + o0 * reduce, nullptr, out + o0,
                                                                                reduce, reduce, 1, scale);
       }
-      check_launch("row sum");
-      return;
-    }
-    if (splits == 1 && reduce <= 8192 && outer >= static_cast<int64_t>(sms) * 8) {
-      row_sum_warp_kernel<T><<<static_cast<unsigned>((outer * 32 + kThreads - 1) / kThreads), kThreads, 0, st>>>(in, out, outer, reduce, scale);
       check_launch("row sum");
       return;
     }

@@ -159,6 +159,12 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_b
   return d;
 }
 
+// The start-address field occupies the low 14 bits in 16-byte units, so moving a descriptor by a
+// byte offset inside shared memory is one 64-bit add.  The single thread that issues the MMAs is
+// the throughput limit of short-K tiles: rebuilding a descriptor per instruction (mask, shift,
+// three ors) costs more issue slots than the MMA itself.
+__device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t byte_offset) { return desc + (byte_offset >> 4); }
+
 // Instruction descriptor for kind::f16: fp32 accumulate, A/B element format (1 = bf16, 0 = f16),
 // operand majors (0 = K-major, 1 = MN-major), N >> 3, M >> 4.
 __device__ __forceinline__ uint32_t make_idesc(bool bf16, int a_mn, int b_mn, int m, int n) {

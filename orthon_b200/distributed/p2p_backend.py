@@ -98,7 +98,13 @@ class PeerBackend(Backend):
         when every rank's device and driver support it (`region.mc` is then the multicast
         pointer); otherwise `region.mc` is None and only the peer mappings exist."""
         if multicast and self._world > 1 and self._vmm_enabled():
-            region = self._allocate_vmm(int(nbytes))
+            try:
+                region = self._allocate_vmm(int(nbytes))
+            except (OSError, RuntimeError, ValueError):
+                region = None  # descriptor exchange or driver call failed here: use the IPC path
+                self._vmm = False
+            if not self._agree(region is not None):
+                region = None
             if region is not None:
                 return region
         nbytes = (int(nbytes) + 255) & ~255

@@ -16,8 +16,8 @@ contributes zeros and receives the average; in "update" mode every parameter mus
 gradient.
 
 Buckets of at least NVLS_MIN_BYTES go through the in-switch (multimem) variant of the kernel
-when the backend could bind the buckets to an NVLink multicast object and the group has at least
-NVLS_MIN_WORLD ranks; everything else uses the one-shot / two-shot peer-load variants.
+when ORTHON_NVLS_MIN_WORLD enables it for the group's size and the backend could bind the buckets
+to an NVLink multicast object; everything else uses the one-shot / two-shot peer-load variants.
 """
 import os
 
@@ -42,10 +42,11 @@ class _Bucket:
 class PeerReducer:
     ONESHOT_BYTES = 512 << 10
     NVLS_MIN_BYTES = int(os.environ.get("ORTHON_NVLS_MIN_BYTES", 1 << 20))  # smaller buckets use peer loads
-    # In-switch reduction halves the bytes each GPU moves only as the world grows (S against
-    # 2 S (w-1)/w); measured on this hardware it loses to peer loads at 2 GPUs (392 against 683 GB/s
-    # at 1 GB) and ties at 4, so it is the default from 8 ranks.
-    NVLS_MIN_WORLD = int(os.environ.get("ORTHON_NVLS_MIN_WORLD", 8))
+    # In-switch reduction moves S bytes per GPU and direction instead of 2 S (w-1)/w, which only
+    # pays as the world grows.  Measured on NVLink 5: 392 against 683 GB/s bus at 2 GPUs and a tie at
+    # 4 (683 against 668 at 1 GB, behind for 25 MB buckets); 8 ranks could not be measured.  So the
+    # peer-load kernels are the default everywhere and ORTHON_NVLS_MIN_WORLD=<ranks> opts in.
+    NVLS_MIN_WORLD = int(os.environ.get("ORTHON_NVLS_MIN_WORLD", 0))
 
     @staticmethod
     def eligible(parameters, group):
@@ -86,7 +87,8 @@ class PeerReducer:
             grad_bytes += _align(b.n * esz, 256)
             stage_bytes += _align(b.n * 4, 256)
         flag_bytes = _align(_C._PEER_FLAG_BYTES, 256)
-        region = self.backend.allocate_symmetric(grad_bytes + stage_bytes + flag_bytes * len(self.buckets), multicast=True)
+        use_nvls = 0 < self.NVLS_MIN_WORLD <= self.world
+        region = self.backend.allocate_symmetric(grad_bytes + stage_bytes + flag_bytes * len(self.buckets), multicast=use_nvls)
         g_off, s_off, f_off = 0, grad_bytes, grad_bytes + stage_bytes
         for i, b in enumerate(self.buckets):
             b.grads = [ptr + g_off for ptr in region.ptrs]
@@ -139,7 +141,7 @@ class PeerReducer:
                         model=b.param_flat if (fused and b.param_flat is not None and b.master_flat is not b.param_flat) else None,
                         hyper=hyper, status=status, found_inf=found_inf, stream_kind=1,
                         mc_grads=b.mc if (b.mc and not oneshot and nbytes >= self.NVLS_MIN_BYTES
-                                          and self.world >= self.NVLS_MIN_WORLD) else 0)
+                                          and 0 < self.NVLS_MIN_WORLD <= self.world) else 0)
         b.launched = True
         self.launch_count += 1
 
