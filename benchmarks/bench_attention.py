@@ -15,7 +15,7 @@ import numpy as np
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
-from benchmarks._timing import time_cuda  # noqa: E402
+from benchmarks._support.timing import time_cuda  # noqa: E402
 from orthon_b200 import _C  # noqa: E402
 
 

@@ -180,8 +180,8 @@ Tensor getitem(const Tensor& t, const py::object& key) {
 }
 
 void setitem(Tensor& t, const py::object& key, double value) {
-  if (grad_enabled() && t.requires_grad())
-    throw std::runtime_error("__setitem__: in-place modification of a tensor that requires grad is only allowed under no_grad()");
+  if (grad_enabled() && t.requires_grad() && !t.is_leaf())
+    throw std::runtime_error("__setitem__: in-place modification of a tensor with autograd history is only allowed under no_grad()");
   NoGradGuard g;
   Tensor view = getitem(t, key);
   const bool full_index = (py::isinstance<py::tuple>(key) ? static_cast<int>(key.cast<py::tuple>().size()) : 1) == t.ndim();
@@ -269,8 +269,8 @@ PYBIND11_MODULE(_C, m) {
       .def("item", &scalar_to_py)
       .def("get_item", [](const Tensor& t, const py::object& key) { return ops::read_scalar(t, flat_index(t, key)); })
       .def("set_item", [](Tensor& t, const py::object& key, double v) {
-        if (grad_enabled() && t.requires_grad())
-          throw std::runtime_error("set_item: in-place modification of a tensor that requires grad is only allowed under no_grad()");
+        if (grad_enabled() && t.requires_grad() && !t.is_leaf())
+          throw std::runtime_error("set_item: in-place modification of a tensor with autograd history is only allowed under no_grad()");
         ops::write_scalar(t, flat_index(t, key), v);
       })
       .def("fill_", [](Tensor& t, double v) { ops::fill_(t, v); return t; })

@@ -241,10 +241,14 @@ static Tensor scalar_op(OperatorId op, const Tensor& a, double s, bool is_mul) {
 Tensor add_scalar(const Tensor& a, double s) { return scalar_op(OperatorId::AddScalar, a, s, false); }
 Tensor mul_scalar(const Tensor& a, double s) { return scalar_op(OperatorId::MulScalar, a, s, true); }
 
+// In-place writes are value updates: they bump the buffer version and record no history
+// (reference project: src/ops/binary_ops.cpp:128-151, src/ops/fill_ops.cpp:51-61).  A leaf may be
+// written at any time (initialisation, optimizers).  A tensor that carries history may not be
+// written while gradients are recorded: the write would be invisible to its backward formula.
 static void check_inplace_allowed(const Tensor& a, const char* op) {
-  if (grad_enabled() && a.requires_grad())
+  if (grad_enabled() && a.requires_grad() && !a.is_leaf())
     throw std::runtime_error(std::string(op) +
-                             ": in-place modification of a tensor that requires grad is only allowed under no_grad()");
+                             ": in-place modification of a tensor with autograd history is only allowed under no_grad()");
 }
 
 Tensor& add_(Tensor& a, const Tensor& b, double alpha) {

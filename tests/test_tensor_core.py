@@ -132,11 +132,16 @@ def test_inplace_overlap_and_grad_rules():
     a.add_(a, alpha=1.0)
     assert a.tolist()[3] == 6.0
     p = t([1, 2], grad=True)
-    with pytest.raises(RuntimeError):
-        p.add_(p)
+    p.add_(p)  # a leaf is a plain value: in-place writes bump its version and record nothing
+    p.fill_(3.0)
+    p.set_item(1, 4.0)
+    assert p.tolist() == [3, 4] and p.is_leaf and p.requires_grad
+    h = p * 2.0
+    with pytest.raises(RuntimeError, match="autograd history"):
+        h.mul_(2.0)
     with ob.no_grad():
-        p.add_(p)
-    assert p.tolist() == [2, 4]
+        h.mul_(2.0)
+    assert h.tolist() == [12, 16]
 
 
 def test_getitem_setitem_and_scalar_access():
