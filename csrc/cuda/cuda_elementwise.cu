@@ -94,6 +94,33 @@ __global__ void map2_vec(const T* __restrict__ a, const T* __restrict__ b, T* __
     o[i] = from_f<T>(op(to_f(a[i]), to_f(b[i])));
 }
 
+// One operand has the output's shape, the other is broadcast along leading dimensions (MODE 1:
+// a bias row, index = linear % inner) or along trailing ones (MODE 2: one value per row, index =
+// linear / inner; a scalar is the case inner == n).  inner and n are multiples of the pack width,
+// so a pack never straddles a row.  SWAP: the broadcast operand is the left argument of op.
+template <class T, class Op, int MODE, bool SWAP>
+__global__ void map2_bcast_vec(const T* __restrict__ full, const T* __restrict__ small, T* __restrict__ o, int64_t n,
+                               int64_t inner, Op op) {
+  constexpr int N = Pack<T>::N;
+  const int64_t nv = n / N;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nv; i += stride) {
+    const int64_t lin = i * N;
+    Pack<T> pf = load_pack(full + lin), ps, po;
+    if (MODE == 1) {
+      ps = load_pack(small + lin % inner);
+    } else {
+      const T v = small[lin / inner];
+#pragma unroll
+      for (int k = 0; k < N; ++k) ps.v[k] = v;
+    }
+#pragma unroll
+    for (int k = 0; k < N; ++k)
+      po.v[k] = from_f<T>(SWAP ? op(to_f(ps.v[k]), to_f(pf.v[k])) : op(to_f(pf.v[k]), to_f(ps.v[k])));
+    store_pack(o + lin, po);
+  }
+}
+
 __device__ __forceinline__ void unpack(const Strided& s, int64_t lin, int64_t& o0, int64_t& o1, int64_t& o2) {
   o0 = o1 = o2 = 0;
 #pragma unroll 1
@@ -226,18 +253,51 @@ __global__ void add_inplace_strided(T* __restrict__ a, const T* __restrict__ b, 
   }
 }
 
+__device__ __forceinline__ float dropout_value(uint64_t x, float p, float scale) {
+  x += 0x9E3779B97F4A7C15ull;
+  x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+  x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+  x = x ^ (x >> 31);
+  const float r = static_cast<float>(static_cast<uint32_t>(x >> 40)) * (1.0f / 16777216.0f);
+  return r >= p ? scale : 0.f;
+}
+
+// Element i of the mask depends only on seed + i, so each thread produces one 16-byte pack.
 template <class T>
-__global__ void dropout_mask_kernel(T* __restrict__ o, int64_t n, float p, float scale, uint64_t seed) {
+__global__ void dropout_mask_kernel(T* __restrict__ o, int64_t n, float p, float scale, uint64_t seed, bool vec) {
+  constexpr int N = Pack<T>::N;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
-    uint64_t x = seed + static_cast<uint64_t>(i);
-    x += 0x9E3779B97F4A7C15ull;
-    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
-    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
-    x = x ^ (x >> 31);
-    const float r = static_cast<float>(static_cast<uint32_t>(x >> 40)) * (1.0f / 16777216.0f);
-    o[i] = from_f<T>(r >= p ? scale : 0.f);
+  const int64_t nv = vec ? n / N : 0;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nv; i += stride) {
+    Pack<T> po;
+#pragma unroll
+    for (int k = 0; k < N; ++k) po.v[k] = from_f<T>(dropout_value(seed + static_cast<uint64_t>(i * N + k), p, scale));
+    store_pack(o + i * N, po);
   }
+  for (int64_t i = nv * N + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+    o[i] = from_f<T>(dropout_value(seed + static_cast<uint64_t>(i), p, scale));
+}
+
+// Fused dropout: o[i] = x[i] * mask(seed + i) in one pass (the mask is never stored; the backward
+// pass runs the same kernel on the gradient).
+template <class T>
+__global__ void dropout_apply_kernel(const T* __restrict__ x, T* __restrict__ o, int64_t n, float p, float scale, uint64_t seed, bool vec) {
+  constexpr int N = Pack<T>::N;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t nv = vec ? n / N : 0;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nv; i += stride) {
+    const Pack<T> px = load_pack(x + i * N);
+    Pack<T> po;
+#pragma unroll
+    for (int k = 0; k < N; ++k) {
+      // The product is rounded from the rounded mask value, as the two-kernel form does.
+      const float m = to_f(from_f<T>(dropout_value(seed + static_cast<uint64_t>(i * N + k), p, scale)));
+      po.v[k] = from_f<T>(to_f(px.v[k]) * m);
+    }
+    store_pack(o + i * N, po);
+  }
+  for (int64_t i = nv * N + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+    o[i] = from_f<T>(to_f(x[i]) * to_f(from_f<T>(dropout_value(seed + static_cast<uint64_t>(i), p, scale))));
 }
 
 template <class T>
@@ -432,6 +492,54 @@ void launch_map1(OpCall& c, Op op) {
   check_launch("elementwise map");
 }
 
+// Fast path for `full (op) small` where `small` is a contiguous row (trailing dimensions of the
+// output), a contiguous column (leading dimensions, then ones) or a single value.  Returns false
+// when the operands do not have that form.
+template <class T, class Op>
+bool launch_map2_bcast(const Tensor& full, const Tensor& small, Tensor& o, cudaStream_t st, Op op, bool swap) {
+  constexpr int N = Pack<T>::N;
+  const int64_t n = o.numel();
+  if (n == 0 || n % N != 0 || full.shape() != o.shape() || !full.is_contiguous() || !small.is_contiguous() || !o.is_contiguous() ||
+      small.numel() >= n || small.numel() == 0 || !aligned16(full.data()) || !aligned16(o.data()))
+    return false;
+  const int nd = o.ndim(), sd = small.ndim();
+  if (sd > nd) return false;
+  Shape padded(nd, 1);
+  for (int i = 0; i < sd; ++i) padded[nd - sd + i] = small.shape()[i];
+  // Split point d: row form = ones before d, output sizes from d on; column form = output sizes
+  // before d, ones from d on.
+  int mode = 0;
+  int64_t inner = 1;
+  for (int d = 0; d <= nd && !mode; ++d) {
+    bool row = true, col = true;
+    for (int k = 0; k < nd; ++k) {
+      const int64_t want_row = k < d ? 1 : o.shape()[k], want_col = k < d ? o.shape()[k] : 1;
+      row = row && padded[k] == want_row;
+      col = col && padded[k] == want_col;
+    }
+    if (row || col) {
+      inner = 1;
+      for (int k = d; k < nd; ++k) inner *= o.shape()[k];
+      mode = row ? 1 : 2;
+    }
+  }
+  if (!mode || inner % N != 0) return false;
+  if (mode == 1 && !aligned16(small.data())) return false;
+  const int sms = sm_count_for(o);
+  const int grid = ew_grid(n / N, kThreads, sms);
+  const T* f = full.data_as<T>();
+  const T* sm = small.data_as<T>();
+  T* out = o.data_as<T>();
+  if (mode == 1) {
+    if (swap) map2_bcast_vec<T, Op, 1, true><<<grid, kThreads, 0, st>>>(f, sm, out, n, inner, op);
+    else map2_bcast_vec<T, Op, 1, false><<<grid, kThreads, 0, st>>>(f, sm, out, n, inner, op);
+  } else {
+    if (swap) map2_bcast_vec<T, Op, 2, true><<<grid, kThreads, 0, st>>>(f, sm, out, n, inner, op);
+    else map2_bcast_vec<T, Op, 2, false><<<grid, kThreads, 0, st>>>(f, sm, out, n, inner, op);
+  }
+  return true;
+}
+
 template <class T, class Op>
 void launch_map2(const Tensor& a, const Tensor& b, Tensor& o, cudaStream_t st, Op op) {
   const int64_t n = o.numel();
@@ -440,6 +548,7 @@ void launch_map2(const Tensor& a, const Tensor& b, Tensor& o, cudaStream_t st, O
       aligned16(a.data()) && aligned16(b.data()) && aligned16(o.data())) {
     map2_vec<T, Op><<<ew_grid(n / Pack<T>::N + 1, kThreads, sms), kThreads, 0, st>>>(a.data_as<T>(), b.data_as<T>(),
                                                                                      o.data_as<T>(), n, op);
+  } else if (launch_map2_bcast<T>(a, b, o, st, op, false) || launch_map2_bcast<T>(b, a, o, st, op, true)) {
   } else {
     const Shape sa = bstrides(a, o.shape()), sb = bstrides(b, o.shape());
     const Strided s = make_strided(o.shape(), &o.strides(), &sa, &sb);
@@ -612,8 +721,17 @@ template <class T>
 void k_dropout_mask(OpCall& c) {
   Tensor& o = c.out[0];
   const float p = static_cast<float>(c.f[0]);
-  dropout_mask_kernel<T><<<ew_grid(o.numel(), kThreads, sm_count_for(o)), kThreads, 0, stream_of(c)>>>(
-      o.data_as<T>(), o.numel(), p, 1.0f / (1.0f - p), static_cast<uint64_t>(c.i[0]));
+  if (c.in[0].defined()) {  // fused form: out = in * mask
+    const Tensor& x = c.in[0];
+    const bool vec2 = aligned16(o.data()) && aligned16(x.data());
+    dropout_apply_kernel<T><<<ew_grid(vec2 ? o.numel() / Pack<T>::N + 1 : o.numel(), kThreads, sm_count_for(o)), kThreads, 0, stream_of(c)>>>(
+        x.data_as<T>(), o.data_as<T>(), o.numel(), p, 1.0f / (1.0f - p), static_cast<uint64_t>(c.i[0]), vec2);
+    check_launch("dropout");
+    return;
+  }
+  const bool vec = aligned16(o.data());
+  dropout_mask_kernel<T><<<ew_grid(vec ? o.numel() / Pack<T>::N + 1 : o.numel(), kThreads, sm_count_for(o)), kThreads, 0, stream_of(c)>>>(
+      o.data_as<T>(), o.numel(), p, 1.0f / (1.0f - p), static_cast<uint64_t>(c.i[0]), vec);
   check_launch("dropout_mask");
 }
 

@@ -34,11 +34,25 @@ __global__ void row_sum_kernel(const T* __restrict__ in, float* __restrict__ par
   int64_t i = begin;
   if ((reinterpret_cast<uintptr_t>(row + begin) & 15u) == 0) {
     const int64_t nv = (end - begin) / N;
-    for (int64_t v = threadIdx.x; v < nv; v += blockDim.x) {
+    // Four independent 16-byte loads per thread and step keep enough bytes in flight to cover
+    // the DRAM latency; the four partial sums are combined in a fixed order.
+    float a4[4] = {0.f, 0.f, 0.f, 0.f};
+    int64_t v = threadIdx.x;
+    for (; v + 3 * static_cast<int64_t>(blockDim.x) < nv; v += 4 * static_cast<int64_t>(blockDim.x)) {
+      Pack<T> p[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) p[u] = load_pack(row + begin + (v + u * static_cast<int64_t>(blockDim.x)) * N);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int k = 0; k < N; ++k) a4[u] += to_f(p[u].v[k]);
+    }
+    for (; v < nv; v += blockDim.x) {
       Pack<T> p = load_pack(row + begin + v * N);
 #pragma unroll
-      for (int k = 0; k < N; ++k) acc += to_f(p.v[k]);
+      for (int k = 0; k < N; ++k) a4[0] += to_f(p.v[k]);
     }
+    acc = (a4[0] + a4[1]) + (a4[2] + a4[3]);
     i = begin + nv * N;
   }
   for (int64_t j = i + threadIdx.x; j < end; j += blockDim.x) acc += to_f(row[j]);
@@ -147,15 +161,18 @@ __global__ void col_sum_vec_kernel(const T* __restrict__ in, float* __restrict__
   }
 }
 
-// Second pass of the row sums: out[o] = scale * sum_s partial[o * splits + s].
+// Second pass of the row sums: out[o] = scale * sum_s partial[o * splits + s].  One warp per
+// row: lane l adds partials l, l + 32, ... in order, then a shuffle tree combines the lanes, so
+// the result does not depend on scheduling.
 template <class T>
 __global__ void finalize_rows_kernel(const float* __restrict__ partial, T* __restrict__ out, int64_t outer, int splits, float scale) {
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t o = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; o < outer; o += stride) {
-    float total = 0.f;
-    for (int s = 0; s < splits; ++s) total += partial[o * splits + s];
-    out[o] = from_f<T>(total * scale);
-  }
+  const int lane = threadIdx.x & 31;
+  const int64_t o = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (o >= outer) return;
+  float total = 0.f;
+  for (int s = lane; s < splits; s += 32) total += partial[o * splits + s];
+  total = warp_sum(total);
+  if (lane == 0) out[o] = from_f<T>(total * scale);
 }
 
 // Second pass: out[o, k] = scale * sum_s partial[o, s, k].  Block (32, 8): 32 adjacent outputs,
@@ -217,7 +234,7 @@ void sum_launch(const T* in, T* out, int64_t outer, int64_t reduce, int64_t inne
     ScratchLease lease(ref.device(), sizeof(float) * outer * splits, st);
     float* partial = static_cast<float*>(lease.data());
     row_sum_kernel<T><<<dim3(splits, static_cast<unsigned>(outer)), kThreads, 0, st>>>(in, partial, out, reduce, chunk, splits, scale);
-    finalize_rows_kernel<T><<<ew_grid(outer, kThreads, sms), kThreads, 0, st>>>(partial, out, outer, splits, scale);
+    finalize_rows_kernel<T><<<static_cast<unsigned>((outer * 32 + kThreads - 1) / kThreads), kThreads, 0, st>>>(partial, out, outer, splits, scale);
     check_launch("row sum (split)");
     return;
   }

@@ -664,11 +664,14 @@ void gemm_dispatch(const Tensor& A_in, bool ta, const Tensor& B_in, bool tb, Ten
   const bool b_mn = !(b.s_k == 1 || (b.k == 1 && b.s_mn != 1));
   // Tile width: 256 columns whenever the problem is wider than one 128-column tile.  Narrow tiles
   // fill the last wave of the persistent grid better but run at about two thirds of the wide
-  // tile's rate (measured on 8192 x 2048 x 8192: 900 against 1330 TFLOP/s), so they never pay.
+  // tile's rate (measured on 8192 x 2048 x 8192: 900 against 1330 TFLOP/s), so they pay only when
+  // the wide tiling would leave at least half of the SMs without a tile: then twice as many
+  // narrow tiles still fit in one wave and each finishes sooner.
   bool wide = N > 128;
   {
     static const int force_bn = [] { const char* e = std::getenv("ORTHON_GEMM_BN"); return e ? std::atoi(e) : 0; }();
-    if (force_bn == 128) wide = false;  // measurement switch
+    const long long tiles_wide = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256) * nb0 * nb1;
+    if (force_bn == 128 || (force_bn != 256 && wide && tiles_wide * 2 <= sm_count_for(C))) wide = false;
   }
   g_last_route.store(wide ? 3 : 2, std::memory_order_relaxed);
   // 256-row tiles (two MMA row blocks per B stage) when the reduction is long enough to amortise

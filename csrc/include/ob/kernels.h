@@ -19,7 +19,7 @@
 //  NllLossBackward    in0=grad in1=targets out0=dlogp[N,C] i0=reduction
 //  Embedding          in0=indices in1=weight[V,D] out0[...,D]
 //  EmbeddingBackward  in0=indices in1=grad out0=dW[V,D] (zeroed by kernel)
-//  DropoutMask        out0 f0=p i0=seed bits
+//  DropoutMask        out0 f0=p i0=seed bits; CUDA only: in0 (optional, packed) -> out0 = in0 * mask
 //  Conv2d             in0=x in1=w in2=bias? out0 i0=sh i1=sw i2=ph i3=pw
 //  Conv2dBackwardInput  in0=grad in1=w out0=dx i0..i3
 //  Conv2dBackwardWeight in0=grad in1=x out0=dw i0..i3

@@ -383,9 +383,51 @@ Tensor dropout_mask(const Shape& shape, double p, uint64_t seed, DType dtype, De
   return mask;
 }
 
+namespace {
+Tensor dropout_apply_cuda(const Tensor& x, double p, uint64_t seed) {
+  Tensor out = Tensor::empty(x.shape(), x.dtype(), x.device());
+  if (out.numel()) {
+    OpCall c;
+    c.in[0] = x;
+    c.out[0] = out;
+    c.f[0] = p;
+    c.i[0] = static_cast<int64_t>(seed);
+    run_kernel(OperatorId::DropoutMask, x.device(), x.dtype(), c);
+  }
+  return out;
+}
+// Backward of the fused CUDA dropout: the same mask, recomputed from (p, seed), applied to the gradient.
+struct DropoutNode : Node {
+  double p = 0.0;
+  uint64_t seed = 0;
+  const char* name() const override { return "DropoutNode"; }
+  std::vector<Tensor> backward(const Tensor& g) override { return {dropout_apply_cuda(contiguous(g), p, seed)}; }
+};
+}  // namespace
+
+// CPU: mask tensor times input (reference project: src/ops/unary_ops.cpp:150-166).  CUDA: one
+// fused pass over a packed input, same random stream, no mask tensor kept for backward.
 Tensor dropout(const Tensor& a, double p, uint64_t seed) {
-  Tensor mask = dropout_mask(a.shape(), p, seed, a.dtype(), a.device());
-  return mul(a, mask);
+  if (!a.device().is_cuda()) {
+    Tensor mask = dropout_mask(a.shape(), p, seed, a.dtype(), a.device());
+    return mul(a, mask);
+  }
+  if (!(p >= 0.0 && p < 1.0)) throw std::invalid_argument("dropout: p must be in [0, 1)");
+  default_dispatcher().check_dtype(OperatorId::DropoutMask, a.device(), a.dtype());
+  Tensor x = a;
+  if (!a.is_contiguous()) {
+    NoGradGuard guard;
+    x = contiguous(a);
+  }
+  Tensor out = dropout_apply_cuda(x, p, seed);
+  if (needs_graph({a})) {
+    auto n = std::make_shared<DropoutNode>();
+    n->p = p;
+    n->seed = seed;
+    n->set_inputs({a});
+    attach(out, n);
+  }
+  return out;
 }
 
 // ----------------------------------------------------------------------- shape

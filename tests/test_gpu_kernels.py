@@ -251,7 +251,9 @@ def test_diagnostic_routes():
     ref = ref_round(a, "bfloat16") @ ref_round(b, "bfloat16")
     close(diag.matmul_simt(xa, xb), ref, "bfloat16")
     close(diag.matmul_tcgen05(xa, xb), ref, "bfloat16")
-    assert diag.matmul_dispatch_path(xa, xb) == "tcgen05_128x256"
+    assert diag.matmul_dispatch_path(xa, xb) == "tcgen05_128x128"  # four wide tiles would leave most SMs idle
+    big_a, big_b = dev_tensor(rng.standard_normal((2048, 64)), "bfloat16"), dev_tensor(rng.standard_normal((64, 2560)), "bfloat16")
+    assert diag.matmul_dispatch_path(big_a, big_b) == "tcgen05_128x256"
     assert diag.matmul_dispatch_path(dev_tensor(a, "float32"), dev_tensor(b, "float32")) == "simt"
     with pytest.raises(RuntimeError):
         diag.matmul_tcgen05(dev_tensor(a, "float32"), dev_tensor(b, "float32"))
@@ -281,3 +283,55 @@ def test_fused_mlp_gelu(dtype):
     (ty * ref_round(w, dtype)).sum().backward()
     for g, tg in zip(xs, ts):
         close(g.grad, tg.grad, dtype, 8)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+def test_broadcast_fast_paths(dtype):
+    """Row, column and single-value operands on either side, including shapes whose rows are
+    not a multiple of the 16-byte pack (generic route)."""
+    rng = np.random.default_rng(5)
+    cases = [((64, 256), (256,)), ((64, 256), (1, 256)), ((64, 256), (64, 1)), ((64, 256), (1,)), ((4, 8, 64), (8, 64)),
+             ((4, 8, 64), (4, 1, 1)), ((4, 8, 64), (4, 8, 1)), ((33, 100), (100,)), ((33, 100), (33, 1)), ((7, 5), (5,))]
+    for full_shape, small_shape in cases:
+        f, s = rng.standard_normal(full_shape), rng.standard_normal(small_shape)
+        tf, ts = dev_tensor(f, dtype), dev_tensor(s, dtype)
+        rf, rs = ref_round(f, dtype), ref_round(s, dtype)
+        close(ob.add(tf, ts), rf + rs, dtype)
+        close(ob.add(ts, tf), rs + rf, dtype)
+        close(ob.mul(tf, ts), rf * rs, dtype, scale=2.0)
+        close(ob.sub(ts, tf), rs - rf, dtype)   # broadcast operand on the left of a composite
+        close(ob.div(tf, ob.add(ob.mul(ts, ts), ob.ones([1]).to("cuda:0").cast(dtype))), rf / (rs * rs + 1), dtype, scale=4.0)
+
+
+def test_dropout_mask_matches_cpu_stream_for_every_alignment():
+    for n in (1, 7, 8, 1000, 4096 + 3):
+        for dtype in ("float32", "bfloat16"):
+            x = np.ones(n, dtype=np.float32)
+            cpu = ob.dropout(ob.from_numpy(x), 0.3, 99).tolist()
+            gpu = ob.dropout(dev_tensor(x, dtype), 0.3, 99)
+            got = torch.tensor(gpu.numpy().astype(np.float32))
+            want = ref_round(np.asarray(cpu, dtype=np.float32), dtype)
+            assert (got == 0).tolist() == (want == 0).tolist(), (n, dtype)
+            assert torch.allclose(got, want, rtol=1e-2)
+    # Fused forward and recomputed-mask backward against the CPU composite (mask tensor times input).
+    rng = np.random.default_rng(8)
+    for dtype in ("float32", "bfloat16"):
+        x = rng.standard_normal((37, 24))
+        cx = ob.from_numpy(ref_round(x, dtype).numpy()).requires_grad_(True)
+        gx = dev_tensor(x, dtype, requires_grad=True)
+        w = rng.standard_normal((37, 24))
+        (ob.dropout(cx, 0.25, 7) * ob.from_numpy(ref_round(w, dtype).numpy())).sum().backward()
+        (ob.dropout(gx, 0.25, 7) * dev_tensor(w, dtype)).sum().backward()
+        close(ob.dropout(gx, 0.25, 7), torch.tensor(ob.dropout(cx, 0.25, 7).numpy()), dtype)
+        close(gx.grad, torch.tensor(cx.grad.numpy()), dtype, scale=2.0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_full_sum_long_rows(dtype):
+    rng = np.random.default_rng(6)
+    for n in (1 << 20, (1 << 20) + 13, 5000):
+        x = rng.standard_normal(n) * 0.1
+        t = dev_tensor(x, dtype)
+        want = ref_round(x, dtype).double().sum().float()
+        close(t.sum(), want.reshape(1), dtype, scale=8.0)
+        close(t.reshape([1, n]).mean(1), (want / n).reshape(1), dtype)
