@@ -22,6 +22,8 @@ void copy_d2h_async(Tensor& dst, const Tensor& src);
 unsigned int take_index_errors();
 int take_gemm_error(int device);
 void set_gemm_route(int route);
+void set_float32_matmul_precision(int level);
+int float32_matmul_precision();
 int last_gemm_route();
 void set_conv_route(int route);
 int last_conv_route();
@@ -463,6 +465,12 @@ PYBIND11_MODULE(_C, m) {
   }, py::arg("qkv"), py::arg("heads"), py::arg("mask") = py::none(), py::arg("causal") = false, py::arg("scale") = 1.0,
      py::arg("dropout_p") = 0.0, py::arg("seed") = py::int_(0));
   // Diagnostics (reference project: bindings/ops_bindings.cpp:300-363, src/diagnostics/matmul.cpp).
+  m.def("set_float32_matmul_precision", [](const std::string& level) {
+    if (level == "highest") cu::set_float32_matmul_precision(0);
+    else if (level == "high") cu::set_float32_matmul_precision(1);
+    else throw std::invalid_argument("set_float32_matmul_precision: expected 'highest' or 'high'");
+  }, "float32 matmul / linear on CUDA: 'highest' = float32 FMA kernel (default), 'high' = large products as bfloat16 piece products on the tensor cores");
+  m.def("get_float32_matmul_precision", [] { return std::string(cu::float32_matmul_precision() ? "high" : "highest"); });
   m.def("_matmul_force_route", [](const std::string& route) {
     if (route == "auto") cu::set_gemm_route(0);
     else if (route == "simt") cu::set_gemm_route(1);

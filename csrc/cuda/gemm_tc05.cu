@@ -48,6 +48,18 @@ using namespace tc05;
 // Diagnostic route control: 0 = planner decides, 1 = force the SIMT kernel, 2 = require tcgen05.
 std::atomic<int> g_force_route{0};
 std::atomic<int> g_last_route{0};  // 1 = simt, 2 = tcgen05 128x128, 3 = tcgen05 128x256
+// float32 products: 0 = "highest" (every product on the exact float32 FMA kernel), 1 = "high" (large products as
+// bfloat16 piece products on the tensor cores).  Initial value from ORTHON_FLOAT32_MATMUL.
+std::atomic<int> g_f32_precision{-1};
+int f32_precision() {
+  int v = g_f32_precision.load(std::memory_order_relaxed);
+  if (v < 0) {
+    const char* e = std::getenv("ORTHON_FLOAT32_MATMUL");
+    v = (e != nullptr && std::string(e) == "high") ? 1 : 0;
+    g_f32_precision.store(v, std::memory_order_relaxed);
+  }
+  return v;
+}
 
 constexpr int BM = 128;
 constexpr int BK = 64;
@@ -64,6 +76,7 @@ struct GemmParams {
   int a_bc, b_bc;               // 1 = operand is shared by every batch entry (batch stride 0)
   int bias_rows;                // 1 = bias is indexed by output row instead of column
   int tma_store;                // 1 = epilogue stages tiles in shared memory and stores them with TMA
+  int out_f32;                  // 1 = C and bias are float32 (operands are bfloat16 pieces of float32 values)
   void* C; long long ldc, c_bs0, c_bs1;
   const void* bias;             // [N] or null
   const void* residual; long long ldr, r_bs0, r_bs1;
@@ -267,7 +280,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const long long c_off = b0 * p.c_bs0 + b1 * p.c_bs1 + static_cast<long long>(row) * p.ldc;
       const long long r_off = b0 * p.r_bs0 + b1 * p.r_bs1 + static_cast<long long>(row) * p.ldr;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
-      const float bias_row = (bias && p.bias_rows && row_ok) ? to_f(bias[row]) : 0.f;
+      const float bias_row = (bias && p.bias_rows && row_ok && !p.out_f32) ? to_f(bias[row]) : 0.f;
 #pragma unroll 1
       for (int sub = 0; sub < BN / 32; ++sub) {
         const int col0 = tn * BN + sub * 32;
@@ -275,6 +288,35 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         float v[32];
         tmem_ld32(taddr + sub * 32, v);
         if (row0 >= p.M) continue;  // uniform: none of this warp's rows exist
+        if (p.out_f32) {
+          // Float32 output: bias and activation in float, each lane stores its 32 columns (one
+          // 128-byte line) directly.
+          const float* bias_f = static_cast<const float*>(p.bias);
+          if (bias_f) {
+            const float br = (p.bias_rows && row_ok) ? bias_f[row] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += p.bias_rows ? br : ((col0 + j < p.N) ? bias_f[col0 + j] : 0.f);
+          }
+          if (p.act == 1) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
+          } else if (p.act == 2) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0.5f * v[j] * (1.f + erff(v[j] * 0.70710678118654752f));
+          }
+          if (row_ok) {
+            float* dst = static_cast<float*>(p.C) + c_off + col0;
+            if (col0 + 32 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) reinterpret_cast<float4*>(dst)[q] = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) dst[j] = v[j];
+            }
+          }
+          continue;
+        }
         const int half = sub & 1;
         if (staged && half == 0) {
           // The tile about to be overwritten must have been read by its previous store.
@@ -461,6 +503,52 @@ __global__ void gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ 
     }
 }
 
+// ------------------------------------------------------ float32 through tcgen05
+// A float32 value x is the exact sum of three bfloat16 pieces: hi = bf16(x), mid = bf16(x - hi),
+// lo = bf16(x - hi - mid).  A product a * b is then the sum of nine piece products, each exact in
+// float32; the six largest (hi*hi, hi*mid, mid*hi, mid*mid, hi*lo, lo*hi) carry it to about
+// 2^-23 relative.  Laying the pieces side by side along K turns the float32 GEMM into one
+// bfloat16 GEMM with a six times longer reduction and float32 accumulation in tensor memory:
+//   A' = [hi | hi | mid | mid | hi | lo]   (M x 6K)      B' = [hi | mid | hi | mid | lo | hi]   (N x 6K)
+// This kernel writes one operand in that form, K-major and packed, from any strided source
+// (tile transpose through shared memory keeps both sides coalesced).  ROLE 0 = A', 1 = B'.
+template <int ROLE>
+__global__ void split3_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int MN, int K, long long s_mn,
+                              long long s_k, long long bs0, long long bs1, int nb1, int Kp, int mn_fast) {
+  __shared__ float tile[32][33];  // [k][mn]
+  const int b0 = blockIdx.z / nb1, b1 = blockIdx.z - b0 * nb1;
+  src += b0 * bs0 + b1 * bs1;
+  dst += static_cast<long long>(blockIdx.z) * MN * Kp;
+  const int k0 = blockIdx.x * 32, mn0 = blockIdx.y * 32;
+  const int tx = threadIdx.x, ty = threadIdx.y;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int slow = ty + j * 8;
+    const int k = k0 + (mn_fast ? slow : tx), mn = mn0 + (mn_fast ? tx : slow);
+    const float x = (k < K && mn < MN) ? src[mn * s_mn + k * s_k] : 0.f;
+    tile[mn_fast ? slow : tx][mn_fast ? tx : slow] = x;
+  }
+  __syncthreads();
+  const int k = k0 + tx;
+  if (k >= K) return;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int mn = mn0 + ty + j * 8;
+    if (mn >= MN) continue;
+    const float x = tile[tx][ty + j * 8];
+    const __nv_bfloat16 hi = __float2bfloat16_rn(x);
+    const float r1 = x - __bfloat162float(hi);
+    const __nv_bfloat16 mid = __float2bfloat16_rn(r1);
+    const __nv_bfloat16 lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+    __nv_bfloat16* row = dst + static_cast<long long>(mn) * Kp + k;
+    if (ROLE == 0) {
+      row[0] = hi; row[K] = hi; row[2LL * K] = mid; row[3LL * K] = mid; row[4LL * K] = hi; row[5LL * K] = lo;
+    } else {
+      row[0] = hi; row[K] = mid; row[2LL * K] = hi; row[3LL * K] = mid; row[4LL * K] = lo; row[5LL * K] = hi;
+    }
+  }
+}
+
 // ---------------------------------------------------------------- host side
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -555,9 +643,10 @@ void launch_simt(const OperandView& a, const OperandView& b, Tensor& C, int M, i
 
 template <class T, int BN, int TM>
 void launch_tc05(const OperandView& a, const OperandView& b, bool a_mn, bool b_mn, Tensor& C, int M, int N, int K,
-                 int nb0, int nb1, long long ldc, long long c_bs0, long long c_bs1, const Epilogue& ep, cudaStream_t st) {
+                 int nb0, int nb1, long long ldc, long long c_bs0, long long c_bs1, const Epilogue& ep, cudaStream_t st,
+                 bool out_f32 = false) {
   using L = SmemLayout<BN, TM>;
-  const DType dt = C.dtype();
+  const DType dt = out_f32 ? DType::BF16 : C.dtype();  // operand type of the tensor maps
   const CUtensorMap ma = make_map(a, a_mn, TM, nb0, nb1, dt);
   const CUtensorMap mb = make_map(b, b_mn, BN, nb0, nb1, dt);
   GemmParams p{};
@@ -587,7 +676,8 @@ void launch_tc05(const OperandView& a, const OperandView& b, bool a_mn, bool b_m
   };
   CUtensorMap mc = ma, mz = ma;
   static const bool direct_store = [] { const char* e = std::getenv("ORTHON_GEMM_STORE"); return e != nullptr && std::string(e) == "direct"; }();
-  bool tma_store = !direct_store && out_map(p.C, &mc);
+  bool tma_store = !direct_store && !out_f32 && out_map(p.C, &mc);
+  p.out_f32 = out_f32 ? 1 : 0;
   if (tma_store && p.preact != nullptr) tma_store = out_map(p.preact, &mz);
   if (tma_store && p.residual != nullptr &&
       ((reinterpret_cast<uintptr_t>(p.residual) & 15u) || p.ldr % 8 != 0 || p.r_bs0 % 8 != 0 || p.r_bs1 % 8 != 0)) tma_store = false;
@@ -632,9 +722,51 @@ void gemm_dispatch(const Tensor& A_in, bool ta, const Tensor& B_in, bool tb, Ten
 
   const int force = g_force_route.load(std::memory_order_relaxed);
   if (dt == DType::F32) {
-    if (force == 2) throw std::runtime_error("matmul diagnostics: the tcgen05 route needs float16 or bfloat16 operands");
-    g_last_route.store(1, std::memory_order_relaxed);
-    launch_simt<float>(a, b, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);
+    // Under the "high" float32 precision setting, large products go through the tensor cores as
+    // six bfloat16 piece products (see split3_kernel); small ones, and epilogues with a residual
+    // or a stored pre-activation, stay on the float32 FMA kernel, as does everything under the
+    // default "highest" setting.  The piece products are exact, but tensor memory accumulates by
+    // truncation, once per 16 elements of the reduction: the relative error grows to about
+    // 1.3e-8 * K (1e-5 at K = 1024) where the FMA kernel stays near 1e-6.
+    static const long long split_min = [] { const char* e = std::getenv("ORTHON_GEMM_F32_SPLIT_MIN"); return e ? std::atoll(e) : (1LL << 22); }();
+    const bool can_split = Runtime::instance().cuda(C.device().index).supports_tcgen05() && !ep.residual.defined() &&
+                           !ep.preact.defined() && ep.act <= 2 && static_cast<long long>(K) * 6 + 8 < (1LL << 31);
+    const bool split = can_split && force != 1 && (force == 2 || (f32_precision() == 1 && static_cast<long long>(M) * N * K >= split_min));
+    if (!split) {
+      if (force == 2) throw std::runtime_error("matmul diagnostics: this float32 problem cannot take the tcgen05 route");
+      g_last_route.store(1, std::memory_order_relaxed);
+      launch_simt<float>(a, b, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);
+      return;
+    }
+    const int Kp = static_cast<int>((static_cast<long long>(K) * 6 + 7) / 8 * 8);
+    auto split_operand = [&](const OperandView& o, int role, Tensor& holder) {
+      const int nb = o.bcast ? 1 : nb0 * nb1;
+      holder = Tensor::empty({static_cast<int64_t>(nb), o.mn, static_cast<int64_t>(Kp)}, DType::BF16, C.device());
+      if (Kp != K * 6) OB_CUDA(cudaMemsetAsync(holder.data(), 0, holder.nbytes(), st));
+      const int mn_fast = (o.s_mn == 1 && o.s_k != 1) ? 1 : 0;
+      dim3 grid(static_cast<unsigned>((o.k + 31) / 32), static_cast<unsigned>((o.mn + 31) / 32), static_cast<unsigned>(nb));
+      auto* dst = static_cast<__nv_bfloat16*>(holder.data());
+      const auto* src = static_cast<const float*>(o.ptr);
+      const long long sb0 = o.bcast ? 0 : o.bs0, sb1 = o.bcast ? 0 : o.bs1;
+      const int inner_nb = o.bcast ? 1 : nb1;
+      if (role == 0) split3_kernel<0><<<grid, dim3(32, 8), 0, st>>>(src, dst, static_cast<int>(o.mn), static_cast<int>(o.k), o.s_mn, o.s_k, sb0, sb1, inner_nb, Kp, mn_fast);
+      else split3_kernel<1><<<grid, dim3(32, 8), 0, st>>>(src, dst, static_cast<int>(o.mn), static_cast<int>(o.k), o.s_mn, o.s_k, sb0, sb1, inner_nb, Kp, mn_fast);
+      check_launch("gemm float32 split");
+      OperandView v{};
+      v.ptr = holder.data();
+      v.mn = o.mn; v.k = Kp; v.s_mn = Kp; v.s_k = 1;
+      v.bs1 = o.bcast ? 0 : o.mn * static_cast<long long>(Kp);
+      v.bs0 = o.bcast ? 0 : v.bs1 * nb1;
+      v.bcast = o.bcast;
+      return v;
+    };
+    Tensor a_pieces, b_pieces;
+    if (a.mn > 65535LL * 32 || b.mn > 65535LL * 32) throw std::invalid_argument("matmul: float32 operand too tall for the split kernel grid");
+    const OperandView a6 = split_operand(a, 0, a_pieces), b6 = split_operand(b, 1, b_pieces);
+    const bool wide32 = N > 128;
+    g_last_route.store(wide32 ? 3 : 2, std::memory_order_relaxed);
+    if (wide32) launch_tc05<__nv_bfloat16, 256, 128>(a6, b6, false, false, C, M, N, Kp, nb0, nb1, ldc, c_bs0, c_bs1, ep, st, true);
+    else launch_tc05<__nv_bfloat16, 128, 128>(a6, b6, false, false, C, M, N, Kp, nb0, nb1, ldc, c_bs0, c_bs1, ep, st, true);
     return;
   }
   // Operands that TMA cannot describe are packed once (the packed copy is K-major).
@@ -740,6 +872,8 @@ bool tc05_encode_map(CUtensorMap* out, DType dt, int rank, void* base, const uin
 // Diagnostics (reference project: src/diagnostics/matmul.cpp:14-87): force a route, read the
 // route the last matmul took.
 void set_gemm_route(int route) { g_force_route.store(route, std::memory_order_relaxed); }
+void set_float32_matmul_precision(int level) { g_f32_precision.store(level ? 1 : 0, std::memory_order_relaxed); }
+int float32_matmul_precision() { return f32_precision(); }
 int last_gemm_route() { return g_last_route.load(std::memory_order_relaxed); }
 
 // Reads and clears the GEMM error word of a device (0 = no error).  Synchronizes the device.

@@ -23,6 +23,7 @@ from ._C import (  # noqa: F401
     neg, relu, sigmoid, tanh, leaky_relu, gelu, exp, log, sqrt, reciprocal,
     dropout, embedding, to, cast, matmul, linear, fused_linear_relu,
     cuda_enabled, cuda_available, cuda_device_count, cuda_synchronize,
+    set_float32_matmul_precision, get_float32_matmul_precision,
     is_grad_enabled, set_grad_enabled,
     softmax, log_softmax, cross_entropy, nll_loss, conv2d, maxpool2d,
     _amp_unscale_to_float32_and_check, _amp_copy_master_to_model_,

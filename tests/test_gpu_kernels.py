@@ -254,9 +254,23 @@ def test_diagnostic_routes():
     assert diag.matmul_dispatch_path(xa, xb) == "tcgen05_128x128"  # four wide tiles would leave most SMs idle
     big_a, big_b = dev_tensor(rng.standard_normal((2048, 64)), "bfloat16"), dev_tensor(rng.standard_normal((64, 2560)), "bfloat16")
     assert diag.matmul_dispatch_path(big_a, big_b) == "tcgen05_128x256"
-    assert diag.matmul_dispatch_path(dev_tensor(a, "float32"), dev_tensor(b, "float32")) == "simt"
-    with pytest.raises(RuntimeError):
-        diag.matmul_tcgen05(dev_tensor(a, "float32"), dev_tensor(b, "float32"))
+    # float32: the FMA kernel by default; under "high" precision large products run as bfloat16
+    # piece products on the tensor cores and small ones stay where they were
+    small_a, small_b = dev_tensor(a[:64, :64], "float32"), dev_tensor(b[:64, :64], "float32")
+    fa, fb = dev_tensor(a, "float32"), dev_tensor(b, "float32")
+    assert ob.get_float32_matmul_precision() == "highest"
+    assert diag.matmul_dispatch_path(fa, fb) == "simt"
+    ob.set_float32_matmul_precision("high")
+    try:
+        assert diag.matmul_dispatch_path(small_a, small_b) == "simt"
+        assert diag.matmul_dispatch_path(fa, fb).startswith("tcgen05")
+    finally:
+        ob.set_float32_matmul_precision("highest")
+    with pytest.raises(ValueError):
+        ob.set_float32_matmul_precision("medium")
+    exact = torch.tensor(a, dtype=torch.float64) @ torch.tensor(b, dtype=torch.float64)
+    close(diag.matmul_tcgen05(fa, fb), exact, "float32")
+    close(diag.matmul_simt(fa, fb), exact, "float32")
     x = rng.standard_normal((2, 8, 16, 16)); w = rng.standard_normal((16, 8, 3, 3)) * 0.2
     xx, ww = dev_tensor(x, "bfloat16"), dev_tensor(w, "bfloat16")
     y_direct = diag.conv2d_direct(xx, ww, None, (1, 1), (1, 1))
@@ -335,3 +349,46 @@ def test_full_sum_long_rows(dtype):
         want = ref_round(x, dtype).double().sum().float()
         close(t.sum(), want.reshape(1), dtype, scale=8.0)
         close(t.reshape([1, n]).mean(1), (want / n).reshape(1), dtype)
+
+
+def test_float32_gemm_through_piece_products():
+    """float32 matmul / linear on the tensor-core route against a float64 product: error at the
+    float32 level for every operand major, batch form, odd reduction length and epilogue."""
+    from orthon_b200 import _diagnostics as diag
+    rng = np.random.default_rng(33)
+
+    def f64(x):
+        return torch.tensor(np.asarray(x, dtype=np.float32), dtype=torch.float64)
+
+    for (m, k, n) in [(256, 192, 320), (130, 191, 70), (512, 1024, 256), (64, 4096, 40)]:
+        a, b = rng.standard_normal((m, k)), rng.standard_normal((k, n))
+        ta, tb = dev_tensor(a, "float32", True), dev_tensor(b, "float32", True)
+        out = diag.matmul_tcgen05(ta, tb)
+        ref = f64(a) @ f64(b)
+        err = (torch.tensor(out.numpy(), dtype=torch.float64) - ref).abs().max().item() / ref.abs().max().item()
+        assert err < 3e-6 + 3e-8 * k, (m, k, n, err)   # truncating accumulation: grows with the reduction length
+    ob.set_float32_matmul_precision("high")
+    try:
+        _piece_product_api_checks(rng, f64)
+    finally:
+        ob.set_float32_matmul_precision("highest")
+
+
+def _piece_product_api_checks(rng, f64):
+    # transposed views (backward products) and gradients through the public matmul
+    a, b = rng.standard_normal((384, 256)), rng.standard_normal((256, 512))
+    ta, tb = dev_tensor(a, "float32", True), dev_tensor(b, "float32", True)
+    w = rng.standard_normal((384, 512))
+    (ob.matmul(ta, tb) * dev_tensor(w, "float32")).sum().backward()
+    assert _C._matmul_last_route().startswith("tcgen05")
+    close(ta.grad, f64(w) @ f64(b).T, "float32")
+    close(tb.grad, f64(a).T @ f64(w), "float32")
+    # batched, one operand shared by the batch
+    a3, b3 = rng.standard_normal((6, 128, 96)), rng.standard_normal((6, 96, 160))
+    close(ob.matmul(dev_tensor(a3, "float32"), dev_tensor(b3, "float32")), f64(a3) @ f64(b3), "float32")
+    # linear with bias and ReLU
+    x, wgt, bias = rng.standard_normal((300, 200)), rng.standard_normal((200, 150)) * 0.1, rng.standard_normal(150)
+    y = ob.fused_linear_relu(dev_tensor(x, "float32"), dev_tensor(wgt, "float32"), dev_tensor(bias, "float32"))
+    close(y, torch.relu(f64(x) @ f64(wgt) + f64(bias)), "float32")
+    y2 = ob.linear(dev_tensor(x, "float32"), dev_tensor(wgt, "float32"), dev_tensor(bias, "float32"))
+    close(y2, f64(x) @ f64(wgt) + f64(bias), "float32")
