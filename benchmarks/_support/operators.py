@@ -26,6 +26,9 @@ class Context:
         try:
             import torch
             self.torch = torch
+            # The comparison arm computes float32 in float32: no TF32 in its convolutions or products.
+            torch.backends.cudnn.allow_tf32 = False
+            torch.backends.cuda.matmul.allow_tf32 = False
         except ImportError:
             self.torch = None
 

@@ -8,7 +8,9 @@
 // with P = OH*OW and CRS = C*R*S padded to a multiple of 8 so that every TMA stride is a
 // multiple of 16 bytes.  The weight matrix is shared by all batch entries (batch stride 0),
 // transposed operands are MN-major descriptors, nothing is transposed in memory.  Used for
-// float16 / bfloat16 when P is a multiple of 8; other cases use the direct kernels.
+// every floating type when P is a multiple of 8; other cases use the direct kernels.  float32
+// products run on whichever GEMM route the float32 matmul precision setting selects (the FMA
+// kernel by default).
 // ORTHON_CUDA_CONV2D=direct forces the direct kernels.
 //
 // Replaces (reference project paths): src/backends/cuda/conv2d_cuda.cu:311-2121.
@@ -50,8 +52,8 @@ Geom make_geom(const Shape& x, const Shape& w, const int64_t* i) {
 
 // col[n][crs][p] = x[n][c][oh*sh-ph+r][ow*sw-pw+s]  (0 outside the image and in padded rows).
 // One block per (n, crs) row of the column matrix: the filter tap is decoded once per block, every
-// thread produces 8 consecutive output positions with 32-bit index arithmetic and one 16-byte
-// store (P is a multiple of 8 on this path).
+// thread produces one 16-byte pack of consecutive output positions (8 for 16-bit types, 4 for
+// float32) with 32-bit index arithmetic (P is a multiple of 8 on this path).
 template <class T>
 __global__ void unfold_kernel(const T* __restrict__ x, T* __restrict__ col, Geom g) {
   const int crs = blockIdx.x, n = blockIdx.y;
@@ -59,16 +61,17 @@ __global__ void unfold_kernel(const T* __restrict__ x, T* __restrict__ col, Geom
   const bool live = crs < g.CRS;
   const int s = crs % g.S, r = (crs / g.S) % g.R, c = crs / (g.S * g.R);
   const T* img = x + (static_cast<int64_t>(n) * g.C + (live ? c : 0)) * g.H * g.W;
-  for (int v = threadIdx.x; v < g.P / 8; v += blockDim.x) {
+  constexpr int N = Pack<T>::N;
+  for (int v = threadIdx.x; v < g.P / N; v += blockDim.x) {
     Pack<T> pk;
-    int oh = (v * 8) / g.OW, ow = (v * 8) - oh * g.OW;
+    int oh = (v * N) / g.OW, ow = (v * N) - oh * g.OW;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
+    for (int e = 0; e < N; ++e) {
       const int ih = oh * g.sh - g.ph + r, iw = ow * g.sw - g.pw + s;
       pk.v[e] = (live && ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) ? img[ih * g.W + iw] : from_f<T>(0.f);
       if (++ow == g.OW) { ow = 0; ++oh; }
     }
-    store_pack(out + v * 8, pk);
+    store_pack(out + v * N, pk);
   }
 }
 
@@ -140,7 +143,7 @@ bool conv_igemm_enabled(const Tensor& x, const Geom* unused = nullptr) {
   if (g_conv_force.load(std::memory_order_relaxed) == 1) return false;
   const char* env = std::getenv("ORTHON_CUDA_CONV2D");
   if (env && std::strcmp(env, "direct") == 0) return false;
-  if (x.dtype() != DType::BF16 && x.dtype() != DType::F16) return false;
+  if (x.dtype() != DType::BF16 && x.dtype() != DType::F16 && x.dtype() != DType::F32) return false;
   return Runtime::instance().cuda(x.device().index).supports_tcgen05();
 }
 
@@ -209,6 +212,9 @@ template bool conv_dgrad_igemm<__nv_bfloat16>(OpCall&);
 template bool conv_dgrad_igemm<__half>(OpCall&);
 template bool conv_wgrad_igemm<__nv_bfloat16>(OpCall&);
 template bool conv_wgrad_igemm<__half>(OpCall&);
+template bool conv_fprop_igemm<float>(OpCall&);
+template bool conv_dgrad_igemm<float>(OpCall&);
+template bool conv_wgrad_igemm<float>(OpCall&);
 
 }  // namespace cu
 }  // namespace ob

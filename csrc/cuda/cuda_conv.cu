@@ -13,9 +13,6 @@ namespace cu {
 template <class T> bool conv_fprop_igemm(OpCall& c);
 template <class T> bool conv_dgrad_igemm(OpCall& c);
 template <class T> bool conv_wgrad_igemm(OpCall& c);
-template <> inline bool conv_fprop_igemm<float>(OpCall&) { return false; }
-template <> inline bool conv_dgrad_igemm<float>(OpCall&) { return false; }
-template <> inline bool conv_wgrad_igemm<float>(OpCall&) { return false; }
 void note_conv_route(int route);  // diagnostics: 1 = direct kernels, 2 = tcgen05 lowering
 
 namespace {
