@@ -158,7 +158,8 @@ def main(argv=None):
         backend = args.backend or os.environ.get("ORTHON_DISTRIBUTED_BACKEND") or ("p2p" if args.device.startswith("cuda") else "local")
         args.backend = backend
         if world > 1:
-            dist.init_process_group(backend, rank=rank, world_size=world, device=int(os.environ.get("LOCAL_RANK", rank)))
+            kwargs = {"device": int(os.environ.get("LOCAL_RANK", rank))} if backend in ("p2p", "nccl") else {}
+            dist.init_process_group(backend, rank=rank, world_size=world, **kwargs)
         rows = worker(rank, vars(args))
         doc = report(rows, args, world) if rank == 0 else None
         if world > 1:

@@ -91,6 +91,11 @@ class _SingleRankBackend(Backend):
 
 def _local_factory(**kw):
     from .local_backend import LocalBackend
+    if kw.get("store") is None:
+        # Launched ranks (no spawn parent to hand over a store): the launcher's file store or a
+        # MASTER_ADDR / MASTER_PORT rendezvous.
+        from .store import store_from_env
+        kw["store"] = store_from_env(kw.get("rank"), kw.get("world_size"))
     return LocalBackend(**kw)
 
 

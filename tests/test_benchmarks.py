@@ -123,3 +123,15 @@ def test_ddp_benchmark_spawns_cpu_ranks():
     assert modes == ["single", "blocking", "bucketed", "overlap"]
     assert all(c["correctness"] == "loss-decreased" for c in doc["cases"])
     assert [c["ranks"] for c in doc["cases"]] == [1, 2, 2, 2]
+
+
+def test_ddp_benchmark_under_the_launcher_with_local_backend():
+    """Launched ranks have no spawn parent: the local backend takes its store from the launcher."""
+    import subprocess
+
+    cmd = [sys.executable, "-m", "orthon_b200.distributed.run", "--nproc_per_node", "2", "--backend", "local",
+           os.path.join(ROOT, "benchmarks", "benchmark_distributed_ddp.py"), "--width", "32", "--depth", "2", "--batch", "16",
+           "--steps", "2", "--warmup", "1", "--mode", "bucketed"]
+    out = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=240)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert "ddp/bucketed" in out.stdout and "ranks=2" in out.stdout
