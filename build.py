@@ -8,7 +8,7 @@ what changed.  The CUDA runtime is linked statically: the module imports on a
 machine without a GPU driver and shares the primary context with any other
 CUDA user in the process.
 
-Usage:  python build.py [-j N] [--verbose] [--ptxas-info]
+Usage:  python build.py [-j N] [--verbose] [--ptxas-info] [--tests]
 """
 from __future__ import annotations
 
@@ -87,6 +87,36 @@ def target_path() -> Path:
     return ROOT / "orthon_b200" / f"_C{sysconfig.get_config_var('EXT_SUFFIX')}"
 
 
+def build_native_tests(jobs: int | None = None, verbose: bool = False) -> Path:
+    """Links `build/ob_native_tests` from the extension's objects (all but the Python module
+    definition) and the sources under tests/cpp.  libpython satisfies the objects that carry
+    pybind11 bindings; no interpreter is started."""
+    build(jobs, verbose)
+    OBJ.mkdir(parents=True, exist_ok=True)
+    tests_dir = ROOT / "tests" / "cpp"
+    sources = sorted(tests_dir.glob("*.cpp"))
+    key = hashlib.sha256(_header_digest().encode())
+    for p in sorted(tests_dir.iterdir()):
+        key.update(p.read_bytes())
+    objs = sorted(o for o in OBJ.glob("*.o") if not o.name.startswith("bindings__module"))
+    key.update(" ".join(str(o) for o in objs).encode())
+    out = ROOT / "build" / "ob_native_tests"
+    stamp = OBJ / "native_tests.stamp"
+    if out.exists() and stamp.exists() and stamp.read_text() == key.hexdigest():
+        return out
+    version = sysconfig.get_config_var("LDVERSION")
+    cmd = [NVCC, *GENCODE, "-O1", "-std=c++17", *_includes(), f"-I{tests_dir}", "-o", str(out), *map(str, sources), *map(str, objs),
+           "-cudart", "static", f"-L{sysconfig.get_config_var('LIBDIR')}", f"-lpython{version}", "-lpthread", "-ldl", "-lrt"]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"native test link failed\n{res.stdout}\n{res.stderr}")
+    stamp.write_text(key.hexdigest())
+    print(f"[build] native tests -> {out.relative_to(ROOT)}")
+    return out
+
+
 def build(jobs: int | None = None, verbose: bool = False, ptxas: bool = False) -> Path:
     OBJ.mkdir(parents=True, exist_ok=True)
     sources = sorted(p for p in CSRC.rglob("*") if p.suffix in (".cpp", ".cu"))
@@ -124,9 +154,12 @@ if __name__ == "__main__":
     ap.add_argument("-j", type=int, default=None)
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--ptxas-info", action="store_true")
+    ap.add_argument("--tests", action="store_true", help="also link build/ob_native_tests from tests/cpp")
     a = ap.parse_args()
     try:
         build(a.j, a.verbose, a.ptxas_info)
+        if a.tests:
+            build_native_tests(a.j, a.verbose)
     except RuntimeError as e:
         print(e, file=sys.stderr)
         sys.exit(1)
