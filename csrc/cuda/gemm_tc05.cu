@@ -503,6 +503,96 @@ __global__ void gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ 
     }
 }
 
+// Large-tile SIMT kernel: 128 x 128 output tile, 16 x 16 threads, 8 x 8 outputs per thread (two
+// 4-wide row groups and two 4-wide column groups, so shared-memory reads are conflict-free
+// float4 accesses), reduction in steps of 16 with the next step's operands prefetched into
+// registers while the current one is multiplied.  Arbitrary element strides; the fast thread
+// index follows whichever stride of each operand is 1.
+template <class T>
+__global__ void __launch_bounds__(256, 1)
+gemm_simt128_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C, int M, int N, int K,
+                    long long a_sm, long long a_sk, long long b_sk, long long b_sn, long long ldc,
+                    int nb1, long long a_bs0, long long a_bs1, long long b_bs0, long long b_bs1,
+                    long long c_bs0, long long c_bs1, const T* __restrict__ bias, const T* __restrict__ residual,
+                    long long ldr, long long r_bs0, long long r_bs1, T* __restrict__ preact, int act, int bias_rows) {
+  constexpr int TK = 16;
+  __shared__ __align__(16) float As[TK][128 + 4];
+  __shared__ __align__(16) float Bs[TK][128 + 4];
+  const int b0 = blockIdx.z / nb1, b1 = blockIdx.z % nb1;
+  A += b0 * a_bs0 + b1 * a_bs1;
+  B += b0 * b_bs0 + b1 * b_bs1;
+  const long long c_base = b0 * c_bs0 + b1 * c_bs1;
+  const long long r_base = b0 * r_bs0 + b1 * r_bs1;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int m0 = blockIdx.y * 128, n0 = blockIdx.x * 128;
+  // Loader mapping: 2048 elements per operand tile, 8 per thread.  K-fast: 16 consecutive threads
+  // walk the reduction; MN-fast: 128 consecutive threads walk the rows / columns.
+  const bool a_kfast = a_sk == 1, b_kfast = b_sk == 1 && b_sn != 1;
+  float ra[8], rb[8];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int e = tid + j * 256;
+      const int ak = a_kfast ? (e & 15) : (e >> 7), am = a_kfast ? (e >> 4) : (e & 127);
+      const int gm = m0 + am, gk = k0 + ak;
+      ra[j] = (gm < M && gk < K) ? to_f(A[gm * a_sm + gk * a_sk]) : 0.f;
+      const int bk = b_kfast ? (e & 15) : (e >> 7), bn = b_kfast ? (e >> 4) : (e & 127);
+      const int gn = n0 + bn, gk2 = k0 + bk;
+      rb[j] = (gn < N && gk2 < K) ? to_f(B[gk2 * b_sk + gn * b_sn]) : 0.f;
+    }
+  };
+  auto stash = [&]() {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int e = tid + j * 256;
+      const int ak = a_kfast ? (e & 15) : (e >> 7), am = a_kfast ? (e >> 4) : (e & 127);
+      As[ak][am] = ra[j];
+      const int bk = b_kfast ? (e & 15) : (e >> 7), bn = b_kfast ? (e >> 4) : (e & 127);
+      Bs[bk][bn] = rb[j];
+    }
+  };
+  float acc[8][8] = {};
+  fetch(0);
+  for (int k0 = 0; k0 < K; k0 += TK) {
+    stash();
+    __syncthreads();
+    if (k0 + TK < K) fetch(k0 + TK);
+#pragma unroll
+    for (int kk = 0; kk < TK; ++kk) {
+      const float4 a_lo = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
+      const float4 a_hi = *reinterpret_cast<const float4*>(&As[kk][64 + ty * 4]);
+      const float4 b_lo = *reinterpret_cast<const float4*>(&Bs[kk][tx * 4]);
+      const float4 b_hi = *reinterpret_cast<const float4*>(&Bs[kk][64 + tx * 4]);
+      const float a[8] = {a_lo.x, a_lo.y, a_lo.z, a_lo.w, a_hi.x, a_hi.y, a_hi.z, a_hi.w};
+      const float b[8] = {b_lo.x, b_lo.y, b_lo.z, b_lo.w, b_hi.x, b_hi.y, b_hi.z, b_hi.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int gm = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+    if (gm >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int gn = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + (j - 4));
+      if (gn >= N) continue;
+      float x = acc[i][j];
+      if (bias) x += to_f(bias[bias_rows ? gm : gn]);
+      if (preact) preact[c_base + gm * ldc + gn] = from_f<T>(act == 4 ? gelu_grad(x) : x);
+      x = apply_act(x, act == 4 ? 2 : act);
+      if (residual) {
+        const float aux = to_f(residual[r_base + gm * ldr + gn]);
+        x = (act == 3) ? x * aux : x + aux;
+      }
+      C[c_base + gm * ldc + gn] = from_f<T>(x);
+    }
+  }
+}
+
 // ------------------------------------------------------ float32 through tcgen05
 // A float32 value x is the exact sum of three bfloat16 pieces: hi = bf16(x), mid = bf16(x - hi),
 // lo = bf16(x - hi - mid).  A product a * b is then the sum of nine piece products, each exact in
@@ -631,8 +721,21 @@ struct Epilogue {
 template <class T>
 void launch_simt(const OperandView& a, const OperandView& b, Tensor& C, int M, int N, int K, int nb0, int nb1,
                  long long ldc, long long c_bs0, long long c_bs1, const Epilogue& ep, cudaStream_t st) {
-  dim3 grid((N + 63) / 64, (M + 63) / 64, nb0 * nb1);
   const long long ldr = ep.residual.defined() ? ldc : 0;
+  // Large tiles once they fill the GPU at least once over; small problems keep the 64 x 64 tile
+  // for the sake of parallelism.
+  const long long big_tiles = static_cast<long long>((N + 127) / 128) * ((M + 127) / 128) * nb0 * nb1;
+  if (M >= 128 && N >= 128 && K >= 256 && big_tiles >= sm_count_for(C)) {  // short reductions do not amortise the 64-register prologue / epilogue
+    dim3 grid128((N + 127) / 128, (M + 127) / 128, nb0 * nb1);
+    gemm_simt128_kernel<T><<<grid128, 256, 0, st>>>(
+        static_cast<const T*>(a.ptr), static_cast<const T*>(b.ptr), C.data_as<T>(), M, N, K, a.s_mn, a.s_k, b.s_k, b.s_mn, ldc,
+        nb1, a.bs0, a.bs1, b.bs0, b.bs1, c_bs0, c_bs1, ep.bias.defined() ? ep.bias.data_as<T>() : nullptr,
+        ep.residual.defined() ? ep.residual.data_as<T>() : nullptr, ldr, c_bs0, c_bs1,
+        ep.preact.defined() ? ep.preact.data_as<T>() : nullptr, ep.act, ep.bias_rows ? 1 : 0);
+    check_launch("gemm (SIMT 128x128)");
+    return;
+  }
+  dim3 grid((N + 63) / 64, (M + 63) / 64, nb0 * nb1);
   gemm_simt_kernel<T><<<grid, dim3(16, 16), 0, st>>>(
       static_cast<const T*>(a.ptr), static_cast<const T*>(b.ptr), C.data_as<T>(), M, N, K, a.s_mn, a.s_k, b.s_k, b.s_mn, ldc,
       nb1, a.bs0, a.bs1, b.bs0, b.bs1, c_bs0, c_bs1, ep.bias.defined() ? ep.bias.data_as<T>() : nullptr,
