@@ -47,8 +47,15 @@ class NcclBackend(Backend):
             raise ValueError("nccl backend requires rank and world_size")
         if world_size < 1 or not 0 <= rank < world_size:
             raise ValueError("rank must be in [0, world_size)")
-        if not fake and not _C.nccl_enabled():
-            raise RuntimeError("this build cannot load NCCL")
+        if not fake:
+            # The copy that ships with the Python environment goes first: a process that later
+            # imports PyTorch (the MASTER_ADDR rendezvous store does) must not already hold an
+            # older system libnccl under the same soname.
+            path = _bundled_nccl()
+            if path:
+                _C._nccl_load(path)
+            if not _C.nccl_enabled():
+                raise RuntimeError("this build cannot load NCCL")
         self._rank, self._world = int(rank), int(world_size)
         self._device = int(rank if device is None else device)
         if not fake and self._device >= _C.cuda_device_count():
@@ -59,10 +66,6 @@ class NcclBackend(Backend):
             self._store = store if isinstance(store, Store) else ManagerStore(store)
         self._generation = self._store.add(f"nccl/generation/{self._rank}", 1) - 1
         self._xseq = 0
-        if not fake:
-            path = _bundled_nccl()
-            if path:
-                _C._nccl_load(path)
         uid_key = f"nccl/uid/{self._generation}"
         if self._rank == 0:
             uid = bytes(128) if fake else _C._nccl_unique_id()

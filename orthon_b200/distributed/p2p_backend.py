@@ -11,6 +11,7 @@ and broadcast inside the NVSwitch (`multimem`); ORTHON_NVLS=0 keeps to plain pee
 """
 import json
 import os
+import time
 import socket
 import struct
 
@@ -335,6 +336,14 @@ class PeerBackend(Backend):
         # Wait until every rank has stopped using the mappings before tearing them down.
         try:
             self.exchange_objects(b"bye")
+            # Rank 0 may host the rendezvous store: it leaves last, once every rank has finished
+            # reading (bounded wait).
+            done = f"p2p/bye/{self._generation}"
+            self._store.add(done, 1)
+            if self._rank == 0:
+                deadline = time.monotonic() + 5.0
+                while self._store.add(done, 0) < self._world and time.monotonic() < deadline:
+                    time.sleep(0.01)
         except Exception:  # noqa: BLE001
             pass
         _C._vmm_release_all()
