@@ -29,6 +29,8 @@
 // (head split by reshape + transpose + contiguous).
 #include <cuda.h>
 
+#include <cstdio>
+
 #include <mutex>
 
 #include "ob/cuda_common.cuh"
@@ -58,6 +60,9 @@ struct FlashParams {
   float* lse;        // [B, H, T]
   const float* delta;  // [B, H, T] (backward): sum_d dO * O
   int* err;
+  // Optional timeline of CTA (0, 0) of the dK/dV kernel: trace[it * 8 + slot] = clock64() at a phase
+  // boundary (ORTHON_ATTENTION_TRACE=1 prints it after the launch).  Null in normal runs.
+  long long* trace;
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -381,7 +386,13 @@ __global__ void attn_delta_kernel(const T* __restrict__ dout, const T* __restric
   }
 }
 
-constexpr int kBwdThreads = 320;  // TMA warp, MMA warp, two softmax groups of four warps
+// The conversion of scores into P / dS is latency-bound (TMEM loads, shuffles, shared-memory
+// stores and barrier hand-offs per tile), so the 64 columns of a step are spread over four
+// groups of four warps: each warp has half the serial work of a two-group split and twice as
+// many warps hide each other's stalls.
+constexpr int kBwdGroups = 4;
+constexpr int kCG = 64 / kBwdGroups;  // columns of the streamed sub-tile per group
+constexpr int kBwdThreads = 32 * (2 + 4 * kBwdGroups);  // TMA warp, MMA warp, the softmax groups
 constexpr int kSub = 64;  // rows of the streamed operand per step (N of the score MMAs)
 
 // Shared-memory plan of the backward kernels: two resident [128 x D] tiles, a ring of streamed
@@ -401,13 +412,17 @@ struct BwdSmem {
   static constexpr int kTotal = kBarOff + 256 + 1024;
   static_assert(kTotal <= 232448, "exceeds the shared memory of one CTA");
 };
-// dK/dV: P^T and dS^T double-buffered (measured faster than a deeper ring with single buffers).
-template <int D> using DkvSmem = BwdSmem<D, 2, 2, (D == 128) ? 3 : 4>;
-template <int D> using DqSmem = BwdSmem<D, 1, 2, 4>;
+// P^T / dS^T never touch shared memory: each softmax group packs its 16 columns to 16-bit pairs and
+// writes them over its own score columns in tensor memory, from where the accumulate MMAs read
+// them as the A operand.  That halves the shared-memory bytes per step (the limit of these
+// short-N products) and leaves room for a five-deep ring.
+template <int D> using DkvSmem = BwdSmem<D, 0, 0, 5>;
+template <int D> using DqSmem = BwdSmem<D, 0, 0, 5>;
 
 // dK, dV: one CTA per (batch, head, 128-key tile); streams 64-row query tiles.
 //   S^T = K Q^T, dP^T = V dO^T (TMEM, 64 columns each, double buffered); one thread per key row
-//   turns them into P^T and dS^T (shared memory); dV += P^T dO, dK += dS^T Q (TMEM).
+//   turns them into P^T and dS^T, packed to 16 bits over its own score columns (TMEM), which the
+//   accumulate MMAs read as their A operand; dV += P^T dO, dK += dS^T Q (TMEM).
 template <class T, int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_constant__ CUtensorMap map_qkv64,
@@ -423,9 +438,12 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gri
   uint64_t* pds_full = sdp_full + 2;             // 2
   uint64_t* pds_free = pds_full + 2;             // 2
   uint64_t* acc_done = pds_free + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+  uint64_t* acc_step = acc_done + 1;             // 2, trace only: accumulate MMAs of a step complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_step + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  long long* const trace = (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0) ? p.trace : nullptr;
+  auto stamp = [&](int it, int slot) { if (trace != nullptr && it < 32) trace[it * 8 + slot] = clock64(); };
   const int bh = blockIdx.x, b = bh / p.H, h = bh - b * p.H;
   const int jt = blockIdx.y;                 // key tile (128 keys); tile 0 is the heaviest under the causal mask
   const int key0 = jt * kTile;
@@ -436,8 +454,9 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gri
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int s = 0; s < L::kStages; ++s) { mbar_init(&ring_full[s], 1); mbar_init(&ring_empty[s], 1); }
-    for (int w = 0; w < 2; ++w) { mbar_init(&sdp_full[w], 1); mbar_init(&pds_full[w], 8); mbar_init(&pds_free[w], 1); }
+    for (int w = 0; w < 2; ++w) { mbar_init(&sdp_full[w], 1); mbar_init(&pds_full[w], 4 * kBwdGroups); mbar_init(&pds_free[w], 1); }
     mbar_init(acc_done, 1);
+    mbar_init(&acc_step[0], 1); mbar_init(&acc_step[1], 1);
     mbar_init_fence();
   }
   if (warp == 1) tmem_alloc(tmem_slot, 512);
@@ -451,6 +470,12 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gri
   uint8_t* sv = sk + L::kBigBytes;
 
   if (warp == 0) {
+    if (lane == 1 && trace != nullptr) {  // observer: completion time of each step's accumulate MMAs
+      for (int it = 0; it < n_it; ++it) {
+        if (!mbar_wait(&acc_step[it & 1], (it >> 1) & 1, p.err, kErrAttnProducer)) break;
+        stamp(it, 6);
+      }
+    }
     if (lane == 0 && n_it > 0) {
       mbar_expect_tx(kv_full, 2 * L::kBigBytes);
 #pragma unroll
@@ -461,6 +486,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gri
       for (int it = 0; it < n_it; ++it) {
         const int st = it % L::kStages;
         if (!mbar_wait(&ring_empty[st], ((it / L::kStages) & 1) ^ 1, p.err, kErrAttnProducer)) break;
+        stamp(it, 0);  // producer: ring slot free, loads issued
         mbar_expect_tx(&ring_full[st], 2 * L::kSubBytes);
         uint8_t* sq = smem + L::kRingOff + st * 2 * L::kSubBytes;
         uint8_t* sdo = sq + L::kSubBytes;
@@ -479,19 +505,19 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gri
       const uint64_t dk_base = make_desc(smem_u32(sk), 16, 1024), dv_base = make_desc(smem_u32(sv), 16, 1024);
       const uint64_t ring_k = make_desc(smem_u32(smem + L::kRingOff), 16, 1024);            // streamed tiles as K-major B
       const uint64_t ring_mn = make_desc(smem_u32(smem + L::kRingOff), kSub * 128, 1024);   // the same tiles as MN-major B
-      const uint64_t op_base = make_desc(smem_u32(smem + L::kOpOff), 16, 1024);
       auto issue_scores = [&](int buf, int st) {
         const uint64_t b_q = desc_advance(ring_k, st * 2 * L::kSubBytes), b_do = desc_advance(b_q, L::kSubBytes);
         const uint32_t d_s = tmem_base + buf * 128, d_dp = d_s + 64;
         constexpr int kBlockA = kTile * 128, kBlockB = kSub * 128;
+        // The two products alternate so that consecutive instructions never accumulate into the
+        // same columns (a dependent chain runs at the pipeline latency, not at its throughput).
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
+        for (int kk = 0; kk < D / 16; ++kk) {
           umma_f16(d_s, desc_advance(dk_base, (kk / 4) * kBlockA + (kk % 4) * 32), desc_advance(b_q, (kk / 4) * kBlockB + (kk % 4) * 32),
                    idesc_s, kk > 0 ? 1u : 0u);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
           umma_f16(d_dp, desc_advance(dv_base, (kk / 4) * kBlockA + (kk % 4) * 32), desc_advance(b_do, (kk / 4) * kBlockB + (kk % 4) * 32),
                    idesc_s, kk > 0 ? 1u : 0u);
+        }
         umma_commit(&sdp_full[buf]);
       };
       bool ok = mbar_wait(kv_full, 0, p.err, kErrAttnMma) && mbar_wait(&ring_full[0], 0, p.err, kErrAttnMma);
@@ -505,26 +531,30 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gri
           const int st1 = (it + 1) % L::kStages;
           if (!mbar_wait(&ring_full[st1], ((it + 1) / L::kStages) & 1, p.err, kErrAttnMma)) { ok = false; break; }
           tc_fence_after();
+          stamp(it + 1, 1);  // MMA thread: operands of step it+1 landed, score MMAs issued
           issue_scores((it + 1) & 1, st1);
         }
         if (!mbar_wait(&pds_full[buf], (it >> 1) & 1, p.err, kErrAttnMma)) { ok = false; break; }
         tc_fence_after();
-        const uint64_t a_p = desc_advance(op_base, buf * 2 * L::kOpBytes), a_ds = desc_advance(a_p, L::kOpBytes);
+        stamp(it, 2);  // MMA thread: P / dS of step it ready, accumulate MMAs issued
+        // A operands from tensor memory: group kk left P^T of its 16 queries in the first 8 columns of
+        // its own score range (dS^T likewise in the dP range).  The next scores written to this
+        // buffer are issued after these products by the same thread, so no extra barrier is needed.
+        const uint32_t a_p = tmem_base + buf * 128, a_ds = a_p + 64;
         const uint64_t b_q = desc_advance(ring_mn, st * 2 * L::kSubBytes), b_do = desc_advance(b_q, L::kSubBytes);
 #pragma unroll
-        for (int kk = 0; kk < kSub / 16; ++kk)
-          umma_f16(tmem_dv, desc_advance(a_p, kk * 32), desc_advance(b_do, kk * 2048), idesc_a, (it > 0 || kk > 0) ? 1u : 0u);
-#pragma unroll
-        for (int kk = 0; kk < kSub / 16; ++kk)
-          umma_f16(tmem_dk, desc_advance(a_ds, kk * 32), desc_advance(b_q, kk * 2048), idesc_a, (it > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < kSub / 16; ++kk) {
+          umma_f16_ta(tmem_dv, a_p + kk * kCG, desc_advance(b_do, kk * 2048), idesc_a, (it > 0 || kk > 0) ? 1u : 0u);
+          umma_f16_ta(tmem_dk, a_ds + kk * kCG, desc_advance(b_q, kk * 2048), idesc_a, (it > 0 || kk > 0) ? 1u : 0u);
+        }
         umma_commit(&ring_empty[st]);
-        umma_commit(&pds_free[buf]);
+        if (trace != nullptr) umma_commit(&acc_step[buf]);
       }
       if (ok) umma_commit(acc_done);
     }
   } else {
     const int quarter = warp & 3;
-    const int grp = (warp - 2) >> 2;    // column half of the 64-query sub-tile this group converts
+    const int grp = (warp - 2) >> 2;    // which kCG columns of the 64-query sub-tile this group converts
     const int r = quarter * 32 + lane;  // key row within the tile
     const int key = key0 + r;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
@@ -533,25 +563,26 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gri
     bool ok = true;
     for (int it = 0; it < n_it && ok; ++it) {
       const int buf = it & 1;
-      const int q0 = (i0 + it) * kSub + grp * 32;  // first query of this group's columns
-      // Lane l holds the log2-scaled LSE and delta of query q0 + l; queries past the end get +inf
-      // (P = 0).  Column values are fetched with shuffles below.
-      const int q_lane = q0 + lane;
+      const int q0 = (i0 + it) * kSub + grp * kCG;  // first query of this group's columns
+      // Lane l holds the log2-scaled LSE and delta of query q0 + (l mod kCG); queries past the end
+      // get +inf (P = 0).  Column values are fetched with shuffles below.
+      const int q_lane = q0 + (lane % kCG);
       const float lse_lane = q_lane < p.T ? lse_row[q_lane] * 1.4426950408889634f : INFINITY;
       const float delta_lane = q_lane < p.T ? delta_row[q_lane] : 0.f;
       if (!warp_wait(&sdp_full[buf], (it >> 1) & 1, p.err, kErrAttnSoftmax)) { ok = false; break; }
       tc_fence_after();
-      float s[32], dp[32];
-      tmem_ld32_nowait(tmem_base + buf * 128 + lane_off + grp * 32, s);
-      tmem_ld32_nowait(tmem_base + buf * 128 + lane_off + 64 + grp * 32, dp);
+      if (warp == 2 && lane == 0) stamp(it, 3);  // softmax warp: scores of step it complete
+      float s[kCG], dp[kCG];
+      tmem_ld16_nowait(tmem_base + buf * 128 + lane_off + grp * kCG, s);
+      tmem_ld16_nowait(tmem_base + buf * 128 + lane_off + 64 + grp * kCG, dp);
       tmem_ld_wait();
-      if (!warp_wait(&pds_free[buf], ((it >> 1) & 1) ^ 1, p.err, kErrAttnSoftmax)) { ok = false; break; }
-      uint8_t* sp = smem + L::kOpOff + buf * 2 * L::kOpBytes;
-      uint8_t* sds = sp + L::kOpBytes;
+      if (warp == 2 && lane == 0) stamp(it, 4);  // scores in registers
+      __align__(16) uint32_t p_regs[kCG / 2];
+      __align__(16) uint32_t ds_regs[kCG / 2];
       // Masking is needed only on tiles that touch the diagonal or the end of the sequence.
       const bool need_mask = (p.causal && (q0 < key0 + kTile)) || (key0 + kTile > p.T);
 #pragma unroll
-      for (int c8 = 0; c8 < 4; ++c8) {
+      for (int c8 = 0; c8 < kCG / 8; ++c8) {
         float l8[8], d8[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
@@ -571,35 +602,39 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gri
         }
 #pragma unroll
         for (int e = 0; e < 8; ++e) dsv[e] = (pv[e] * p.scale) * (dp[c8 * 8 + e] - d8[e]);
-        *reinterpret_cast<uint4*>(sp + sw128_offset(r, grp * 4 + c8)) = pack8<T>(pv);
-        *reinterpret_cast<uint4*>(sds + sw128_offset(r, grp * 4 + c8)) = pack8<T>(dsv);
+        *reinterpret_cast<uint4*>(&p_regs[c8 * 4]) = pack8<T>(pv);
+        *reinterpret_cast<uint4*>(&ds_regs[c8 * 4]) = pack8<T>(dsv);
       }
-      fence_async_smem();
+      tmem_st8(tmem_base + buf * 128 + lane_off + grp * kCG, p_regs);
+      tmem_st8(tmem_base + buf * 128 + lane_off + 64 + grp * kCG, ds_regs);
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&pds_full[buf]);
+      if (warp == 2 && lane == 0) stamp(it, 5);  // P / dS stored, hand-off signalled
     }
     if (ok && n_it > 0 && warp_wait(acc_done, 0, p.err, kErrAttnSoftmax)) {
       tc_fence_after();
-      // Group 0 writes dV, group 1 dK: stage this warp's 32 rows in the (now idle) V / K tile and
-      // store them.
-      uint8_t* dst = grp ? sk : sv;
-      const uint32_t src = grp ? tmem_dk : tmem_dv;
+      // Groups 0 and 1 write dV, groups 2 and 3 dK, each one 64-column block (D = 64: groups 0 and
+      // 2 alone): stage this warp's 32 rows in the now idle V / K tile and store them.
+      const int which = grp >> 1, block = grp & 1;
+      if (block < D / 64) {
+        uint8_t* dst = (which ? sk : sv) + block * (kTile * 128);
+        const uint32_t src = (which ? tmem_dk : tmem_dv) + block * 64;
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        float o[32];
-        tmem_ld32(src + lane_off + c * 32, o);
+        for (int c = 0; c < 2; ++c) {
+          float o[32];
+          tmem_ld32(src + lane_off + c * 32, o);
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
-          *reinterpret_cast<uint4*>(dst + (c / 2) * (kTile * 128) + sw128_offset(r, (c % 2) * 4 + q)) = pack8<T>(o + q * 8);
-      }
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0 && key0 + quarter * 32 < p.T) {
-#pragma unroll
-        for (int c = 0; c < D / 64; ++c)
-          tma_store_3d(&map_dqkv, dst + c * (kTile * 128) + quarter * 32 * 128, (grp ? col_k : col_v) + c * 64, key0 + quarter * 32, b);
-        tma_store_wait_all();
+          for (int q = 0; q < 4; ++q)
+            *reinterpret_cast<uint4*>(dst + sw128_offset(r, c * 4 + q)) = pack8<T>(o + q * 8);
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0 && key0 + quarter * 32 < p.T) {
+          tma_store_3d(&map_dqkv, dst + quarter * 32 * 128, (which ? col_k : col_v) + block * 64, key0 + quarter * 32, b);
+          tma_store_wait_all();
+        }
       }
     }
   }
@@ -611,7 +646,8 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gri
 
 // dQ: one CTA per (batch, head, 128-query tile); streams 64-key sub-tiles of K and V.
 //   S = Q K^T, dP = dO V^T (TMEM, 64 columns each, double buffered); one thread per query row
-//   writes dS = P (dP - delta) * scale to shared memory; dQ += dS K (TMEM).
+//   writes dS = P (dP - delta) * scale, packed to 16 bits, over its own score columns (TMEM), the A
+//   operand of dQ += dS K (TMEM).
 template <class T, int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_constant__ CUtensorMap map_qkv64,
@@ -640,7 +676,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < L::kStages; ++s) { mbar_init(&ring_full[s], 1); mbar_init(&ring_empty[s], 1); }
-    for (int w = 0; w < 2; ++w) { mbar_init(&sdp_full[w], 1); mbar_init(&ds_full[w], 8); mbar_init(&ds_free[w], 1); }
+    for (int w = 0; w < 2; ++w) { mbar_init(&sdp_full[w], 1); mbar_init(&ds_full[w], 4 * kBwdGroups); mbar_init(&ds_free[w], 1); }
     mbar_init(acc_done, 1);
     mbar_init_fence();
   }
@@ -684,19 +720,17 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid
       const uint64_t dq_base = make_desc(smem_u32(sq), 16, 1024), ddo_base = make_desc(smem_u32(sdo), 16, 1024);
       const uint64_t ring_k = make_desc(smem_u32(smem + L::kRingOff), 16, 1024);            // streamed tiles as K-major B
       const uint64_t ring_mn = make_desc(smem_u32(smem + L::kRingOff), kSub * 128, 1024);   // the same tiles as MN-major B
-      const uint64_t op_base = make_desc(smem_u32(smem + L::kOpOff), 16, 1024);
       auto issue_scores = [&](int buf, int st) {
         const uint64_t b_k = desc_advance(ring_k, st * 2 * L::kSubBytes), b_v = desc_advance(b_k, L::kSubBytes);
         const uint32_t d_s = tmem_base + buf * 128, d_dp = d_s + 64;
         constexpr int kBlockA = kTile * 128, kBlockB = kSub * 128;
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
+        for (int kk = 0; kk < D / 16; ++kk) {  // alternating accumulators, see the dK/dV kernel
           umma_f16(d_s, desc_advance(dq_base, (kk / 4) * kBlockA + (kk % 4) * 32), desc_advance(b_k, (kk / 4) * kBlockB + (kk % 4) * 32),
                    idesc_s, kk > 0 ? 1u : 0u);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
           umma_f16(d_dp, desc_advance(ddo_base, (kk / 4) * kBlockA + (kk % 4) * 32), desc_advance(b_v, (kk / 4) * kBlockB + (kk % 4) * 32),
                    idesc_s, kk > 0 ? 1u : 0u);
+        }
         umma_commit(&sdp_full[buf]);
       };
       bool ok = mbar_wait(q_full, 0, p.err, kErrAttnMma) && mbar_wait(&ring_full[0], 0, p.err, kErrAttnMma);
@@ -714,19 +748,18 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid
         }
         if (!mbar_wait(&ds_full[buf], (it >> 1) & 1, p.err, kErrAttnMma)) { ok = false; break; }
         tc_fence_after();
-        const uint64_t a_ds = desc_advance(op_base, buf * L::kOpBytes);
+        const uint32_t a_ds = tmem_base + buf * 128;  // dS of group kk in the first 8 columns of its score range
         const uint64_t b_k = desc_advance(ring_mn, st * 2 * L::kSubBytes);
 #pragma unroll
         for (int kk = 0; kk < kSub / 16; ++kk)
-          umma_f16(tmem_dq, desc_advance(a_ds, kk * 32), desc_advance(b_k, kk * 2048), idesc_a, (it > 0 || kk > 0) ? 1u : 0u);
+          umma_f16_ta(tmem_dq, a_ds + kk * kCG, desc_advance(b_k, kk * 2048), idesc_a, (it > 0 || kk > 0) ? 1u : 0u);
         umma_commit(&ring_empty[st]);
-        umma_commit(&ds_free[buf]);
       }
       if (ok) umma_commit(acc_done);
     }
   } else {
     const int quarter = warp & 3;
-    const int grp = (warp - 2) >> 2;  // column half of the 64-key sub-tile this group converts
+    const int grp = (warp - 2) >> 2;  // which kCG columns of the 64-key sub-tile this group converts
     const int r = quarter * 32 + lane;
     const int q = row0 + r;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
@@ -737,18 +770,17 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid
     bool ok = true;
     for (int it = 0; it < n_it && ok; ++it) {
       const int buf = it & 1;
-      const int k0 = it * kSub + grp * 32;
+      const int k0 = it * kSub + grp * kCG;
       if (!warp_wait(&sdp_full[buf], (it >> 1) & 1, p.err, kErrAttnSoftmax)) { ok = false; break; }
       tc_fence_after();
-      float s[32], dp[32];
-      tmem_ld32_nowait(tmem_base + buf * 128 + lane_off + grp * 32, s);
-      tmem_ld32_nowait(tmem_base + buf * 128 + lane_off + 64 + grp * 32, dp);
+      float s[kCG], dp[kCG];
+      tmem_ld16_nowait(tmem_base + buf * 128 + lane_off + grp * kCG, s);
+      tmem_ld16_nowait(tmem_base + buf * 128 + lane_off + 64 + grp * kCG, dp);
       tmem_ld_wait();
-      if (!warp_wait(&ds_free[buf], ((it >> 1) & 1) ^ 1, p.err, kErrAttnSoftmax)) { ok = false; break; }
-      uint8_t* sds = smem + L::kOpOff + buf * L::kOpBytes;
-      const bool need_mask = (p.causal && (k0 + 31 > row0)) || (k0 + 32 > p.T);
+      __align__(16) uint32_t ds_regs[kCG / 2];
+      const bool need_mask = (p.causal && (k0 + kCG - 1 > row0)) || (k0 + kCG > p.T);
 #pragma unroll
-      for (int c8 = 0; c8 < 4; ++c8) {
+      for (int c8 = 0; c8 < kCG / 8; ++c8) {
         float pv[8], dsv[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) pv[e] = fast_exp2(fmaf(s[c8 * 8 + e], p.scale_log2, -lse2));
@@ -759,16 +791,17 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid
         }
 #pragma unroll
         for (int e = 0; e < 8; ++e) dsv[e] = (pv[e] * p.scale) * (dp[c8 * 8 + e] - delta);
-        *reinterpret_cast<uint4*>(sds + sw128_offset(r, grp * 4 + c8)) = pack8<T>(dsv);
+        *reinterpret_cast<uint4*>(&ds_regs[c8 * 4]) = pack8<T>(dsv);
       }
-      fence_async_smem();
+      tmem_st8(tmem_base + buf * 128 + lane_off + grp * kCG, ds_regs);
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ds_full[buf]);
     }
     if (ok && warp_wait(acc_done, 0, p.err, kErrAttnSoftmax)) {
       tc_fence_after();
-      // Each group drains and stores one 64-column block of dQ (group 0 alone when D = 64).
+      // Groups 0 and 1 each drain and store one 64-column block of dQ (group 0 alone when D = 64).
       if (grp < D / 64) {
 #pragma unroll 1
         for (int c = grp * 2; c < grp * 2 + 2; ++c) {
@@ -858,8 +891,33 @@ void launch_bwd(const Tensor& qkv, const Tensor& out, const Tensor& lse, const T
   check_launch("attention_delta");
   const int n_tiles = (Tn + kTile - 1) / kTile;
   dim3 grid(B * H, n_tiles);
+  static const bool want_trace = [] { const char* e = std::getenv("ORTHON_ATTENTION_TRACE"); return e != nullptr && e[0] == '1'; }();
+  long long* trace_dev = nullptr;
+  if (want_trace) {
+    OB_CUDA(cudaMalloc(&trace_dev, 32 * 8 * sizeof(long long)));
+    OB_CUDA(cudaMemsetAsync(trace_dev, 0, 32 * 8 * sizeof(long long), st));
+    p.trace = trace_dev;
+  }
   flash_bwd_dkv_kernel<T, D><<<grid, kBwdThreads, LA::kTotal, st>>>(m128, m64, mdo, mdq, p);
   check_launch("flash_attention_backward_dkv");
+  if (want_trace) {
+    long long host[32 * 8];
+    OB_CUDA(cudaStreamSynchronize(st));
+    OB_CUDA(cudaMemcpy(host, trace_dev, sizeof(host), cudaMemcpyDeviceToHost));
+    OB_CUDA(cudaFree(trace_dev));
+    p.trace = nullptr;
+    long long t0 = 0;
+    for (int k = 0; k < 32 * 8 && t0 == 0; ++k) t0 = host[k];
+    for (int k = 0; k < 32 * 8; ++k) if (host[k] != 0 && host[k] < t0) t0 = host[k];
+    std::fprintf(stderr, "attention dK/dV timeline of CTA (0,0), cycles since its first stamp\n"
+                         "step  loads_issued  scores_issued  acc_issued  scores_seen  scores_in_regs  handoff\n");
+    for (int it = 0; it < 32; ++it) {
+      if (host[it * 8 + 3] == 0) continue;
+      std::fprintf(stderr, "%4d", it);
+      for (int slot = 0; slot < 7; ++slot) std::fprintf(stderr, " %13lld", host[it * 8 + slot] ? host[it * 8 + slot] - t0 : -1LL);
+      std::fprintf(stderr, "\n");
+    }
+  }
   flash_bwd_dq_kernel<T, D><<<grid, kBwdThreads, LB::kTotal, st>>>(m128, m64, mdo, mdq, p);
   check_launch("flash_attention_backward_dq");
 }
