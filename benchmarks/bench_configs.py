@@ -154,14 +154,20 @@ def run_cnn(args):
     scaler = fw.amp.GradScaler(enabled=False)
     rng = np.random.default_rng(rank)
 
-    def make_batch():
+    def make_arrays():
         px = rng.uniform(0, 1, size=(batch, 3, 32, 32)).astype(np.float32)
         px = (px - px.mean()) / px.std()
-        labels = rng.integers(0, 10, batch)
-        x = from_numpy(px, "bfloat16") if args.impl == "ours" else fw.cast(from_numpy(px), "bfloat16")
+        return px, rng.integers(0, 10, batch)
+
+    def upload(px, labels):
+        """Host arrays -> device tensors through the public API (what a data loader hands over)."""
         if args.impl == "ours":
-            return x.to(device), from_numpy(labels.astype(np.int64)).to(device)
-        return x.to(device), [int(v) for v in labels]
+            x = fw.cast(from_numpy(px).to(device), "bfloat16")
+            return x, from_numpy(labels.astype(np.int64)).to(device)
+        return fw.cast(from_numpy(px), "bfloat16").to(device), [int(v) for v in labels]
+
+    def make_batch():
+        return upload(*make_arrays())
 
     def loss_of(x, y):
         logits = wrapped(x)
@@ -191,10 +197,14 @@ def run_cnn(args):
         step(x, y)
     sync()
     dev_s = time.perf_counter() - t0
+    # End to end: the batches exist as host arrays (a loader's output); every step uploads its own
+    # batch and reads the loss back.
+    host_batches = [make_arrays() for _ in range(args.steps)]
+    sync()
     t0 = time.perf_counter()
     last = None
-    for _ in range(args.steps):
-        x, y = make_batch()
+    for px, labels in host_batches:
+        x, y = upload(px, labels)
         last = float(step(x, y).item())
     sync()
     e2e_s = time.perf_counter() - t0

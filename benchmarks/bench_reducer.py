@@ -24,7 +24,6 @@ ESZ = {"float32": 4, "bfloat16": 2, "float16": 2}
 
 
 def worker(rank, dtypes, max_mb, iters):
-    import orthon_b200 as ob
     import orthon_b200.distributed as dist
     from orthon_b200 import _C
     from orthon_b200.distributed import _state

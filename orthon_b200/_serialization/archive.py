@@ -6,7 +6,6 @@ directory + fsync + ``os.replace``.  Reader: identifies files by content, refuse
 streams by header, rejects duplicate member names, duplicate JSON fields at any depth, bare
 NaN/Infinity literals, compressed or mis-sized payloads.
 (reference project: python/orthon/_serialization/archive.py:74-232)"""
-import io
 import json
 import os
 import tempfile

@@ -9,7 +9,7 @@ import os
 from .. import _C
 from ._backend import Backend, _TransportFailure
 from .store import ManagerStore, Store, store_from_env
-from .work import Work, _CompletedWork
+from .work import Work
 
 RENDEZVOUS_TIMEOUT_SECONDS = 60.0
 _SUPPORTED = ("float32", "float16", "bfloat16")

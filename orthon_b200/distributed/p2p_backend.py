@@ -13,7 +13,6 @@ import json
 import os
 import time
 import socket
-import struct
 
 from .. import _C
 from ._backend import Backend, _TransportFailure

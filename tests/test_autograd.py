@@ -5,7 +5,6 @@ import pytest
 import torch
 
 import orthon_b200 as ob
-from orthon_b200 import _C
 
 
 def t(a, grad=True, dtype=None):

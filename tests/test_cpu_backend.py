@@ -1,6 +1,5 @@
 """CPU backend: results do not depend on the worker count, strided operands need no packing,
 and forked children get their own worker pool."""
-import hashlib
 import os
 import subprocess
 import sys
@@ -8,7 +7,6 @@ import sys
 import numpy as np
 
 import orthon_b200 as ob
-from orthon_b200 import _C
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 

@@ -1,6 +1,5 @@
 """Dispatcher / registry, fake-CUDA runtime seams and native process-group ordering (host only).
 (reference project: tests/cpp/test_dispatcher.cpp, test_async_runtime.cpp, test_distributed_runtime.cpp)"""
-import numpy as np
 import pytest
 
 import orthon_b200 as ob

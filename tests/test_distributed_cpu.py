@@ -2,7 +2,6 @@
 import numpy as np
 import pytest
 
-import orthon_b200 as ob
 import orthon_b200.distributed as dist
 
 import dist_workloads as W

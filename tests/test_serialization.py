@@ -1,8 +1,6 @@
 """ml-runtime-checkpoint v1: determinism, bit exactness, validation, atomicity, transactions.
 (reference project: tests/spec/serialization/*, tests/python/test_checkpoint_format.py)"""
-import io
 import json
-import os
 import pickle
 import zipfile
 

@@ -16,7 +16,6 @@ import ctypes
 import numpy as np
 import pytest
 
-import orthon_b200 as ob
 from orthon_b200 import _C
 
 pytestmark = pytest.mark.gpu
