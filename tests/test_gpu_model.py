@@ -58,3 +58,61 @@ def test_causal_lm_matches_torch(dtype, tol):
 def test_smoke_entry():
     import __graft_entry__ as entry
     entry.smoke()
+
+
+def _example(name):
+    import importlib.util
+    import os
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location(f"example_{name}", os.path.join(root, "examples", f"{name}.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_examples_train_on_the_gpu_in_float32():
+    """The float32 examples on CUDA: MLP on synthetic digits and both CNNs (convolutions through
+    the GEMM lowering, max pooling, Adam) learn and agree with the CPU run of the same script."""
+    mlp = _example("mnist_mlp")
+    gpu = mlp.main(["--synthetic", "--train-limit", "512", "--test-limit", "128", "--epochs", "2", "--device", "cuda"])
+    cpu = mlp.main(["--synthetic", "--train-limit", "512", "--test-limit", "128", "--epochs", "2", "--device", "cpu"])
+    assert gpu["history"][-1]["test"]["accuracy"] > 0.9
+    assert abs(gpu["history"][0]["train"]["loss"] - cpu["history"][0]["train"]["loss"]) < 1e-3
+    cnn = _example("cifar10_cnn")
+    args = ["--synthetic", "--train-limit", "64", "--test-limit", "32", "--batch-size", "16", "--epochs", "2", "--channels", "8"]
+    g = cnn.main(args + ["--device", "cuda"])
+    c = cnn.main(args + ["--device", "cpu"])
+    assert abs(g["history"][0]["train"]["loss"] - c["history"][0]["train"]["loss"]) < 2e-3
+    assert g["history"][1]["train"]["loss"] < g["history"][0]["train"]["loss"]
+    vgg = cnn.main(["--synthetic", "--model", "minivgg", "--vgg-base-channels", "8", "--hidden", "32", "--train-limit", "64",
+                    "--test-limit", "32", "--batch-size", "32", "--epochs", "2", "--device", "cuda"])
+    assert vgg["history"][1]["train"]["loss"] < vgg["history"][0]["train"]["loss"] + 0.05
+
+
+def test_float32_training_step_is_the_same_under_both_matmul_precisions():
+    """`high` precision changes rounding, not results beyond float32 noise: one MLP step."""
+    from orthon_b200.models import MLP
+
+    def one_step(level):
+        ob.set_float32_matmul_precision(level)
+        try:
+            ob.manual_seed(3)
+            model = MLP((512, 1024, 256, 10))
+            model.to("cuda:0")
+            opt = ob.optim.SGD(model.parameters(), lr=0.05)
+            rng = np.random.default_rng(0)
+            x = ob.from_numpy(rng.standard_normal((512, 512)).astype(np.float32)).to("cuda:0")
+            y = _C.from_numpy(rng.integers(0, 10, 512).astype(np.int64)).to("cuda:0")
+            opt.zero_grad()
+            loss = ob.cross_entropy(model(x), y)
+            loss.backward()
+            opt.step()
+            return float(loss.item()), np.asarray(next(iter(model.parameters())).to("cpu").tolist())
+        finally:
+            ob.set_float32_matmul_precision("highest")
+
+    loss_a, w_a = one_step("highest")
+    loss_b, w_b = one_step("high")
+    assert abs(loss_a - loss_b) < 1e-4 * max(1.0, abs(loss_a))
+    assert np.abs(w_a - w_b).max() < 1e-5
