@@ -639,6 +639,23 @@ __global__ void split3_kernel(const float* __restrict__ src, __nv_bfloat16* __re
   }
 }
 
+// Split-K second pass: C[m, n] = sum over s of partial[s, m, n] (float32 partials, fixed order).
+template <class T>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, T* __restrict__ C, int splits, long long MN, int N, long long ldc) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < MN; i += stride * 4) {
+    float4 acc = *reinterpret_cast<const float4*>(partial + i);
+    for (int sidx = 1; sidx < splits; ++sidx) {
+      const float4 v = *reinterpret_cast<const float4*>(partial + sidx * MN + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    const long long m = i / N;
+    const int n = static_cast<int>(i - m * N);  // N is a multiple of 4: the four values share a row
+    T* dst = C + m * ldc + n;
+    dst[0] = from_f<T>(acc.x); dst[1] = from_f<T>(acc.y); dst[2] = from_f<T>(acc.z); dst[3] = from_f<T>(acc.w);
+  }
+}
+
 // ---------------------------------------------------------------- host side
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -747,9 +764,9 @@ void launch_simt(const OperandView& a, const OperandView& b, Tensor& C, int M, i
 template <class T, int BN, int TM>
 void launch_tc05(const OperandView& a, const OperandView& b, bool a_mn, bool b_mn, Tensor& C, int M, int N, int K,
                  int nb0, int nb1, long long ldc, long long c_bs0, long long c_bs1, const Epilogue& ep, cudaStream_t st,
-                 bool out_f32 = false) {
+                 bool out_f32 = false, DType out_f32_operands = DType::BF16) {
   using L = SmemLayout<BN, TM>;
-  const DType dt = out_f32 ? DType::BF16 : C.dtype();  // operand type of the tensor maps
+  const DType dt = out_f32 ? out_f32_operands : C.dtype();  // operand type of the tensor maps
   const CUtensorMap ma = make_map(a, a_mn, TM, nb0, nb1, dt);
   const CUtensorMap mb = make_map(b, b_mn, BN, nb0, nb1, dt);
   GemmParams p{};
@@ -897,6 +914,47 @@ void gemm_dispatch(const Tensor& A_in, bool ta, const Tensor& B_in, bool tb, Ten
   }
   const bool a_mn = !(a.s_k == 1 || (a.k == 1 && a.s_mn != 1));
   const bool b_mn = !(b.s_k == 1 || (b.k == 1 && b.s_mn != 1));
+  // Split-K: a small output with a long reduction (weight gradients of a narrow model: 512 x 512
+  // over 16384 tokens) gives the persistent grid a handful of tiles.  The reduction is then cut
+  // into S slices that run as S batch entries of the same kernel (the slice index is a batch
+  // stride along K), float32 partials go to scratch and a second pass adds them in a fixed order.
+  {
+    static const int splitk_off = [] { const char* e = std::getenv("ORTHON_GEMM_SPLITK"); return (e != nullptr && e[0] == '0') ? 1 : 0; }();
+    const long long sms = sm_count_for(C);
+    const long long tiles_wide = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256);
+    const bool plain = !ep.bias.defined() && !ep.residual.defined() && !ep.preact.defined() && ep.act == 0;
+    int splits = 1;
+    if (!splitk_off && plain && nb0 * nb1 == 1 && N % 4 == 0 && tiles_wide * 4 <= sms && K >= 4096) {
+      while (splits < 32 && tiles_wide * splits * 2 <= sms && K % (splits * 2 * 64) == 0 && K / (splits * 2) >= 512) splits *= 2;
+    }
+    if (splits > 1) {
+      const long long Ks = K / splits;
+      OperandView as = a, bs = b;
+      as.k = Ks; bs.k = Ks;
+      as.bs1 = Ks * a.s_k; bs.bs1 = Ks * b.s_k;
+      as.bs0 = 0; bs.bs0 = 0;
+      as.bcast = false; bs.bcast = false;
+      if (tma_compatible(as, 1, splits) && tma_compatible(bs, 1, splits)) {
+        Tensor partial = Tensor::empty({static_cast<int64_t>(splits), static_cast<int64_t>(M), static_cast<int64_t>(N)}, DType::F32, C.device());
+        Epilogue none;
+        const long long mn = static_cast<long long>(M) * N;
+        const bool wide_s = N > 128 && tiles_wide * splits * 2 > sms;
+        g_last_route.store(wide_s ? 3 : 2, std::memory_order_relaxed);
+#define OB_SPLITK_LAUNCH(TT)                                                                                                   \
+  do {                                                                                                                         \
+    if (wide_s) launch_tc05<TT, 256, 128>(as, bs, a_mn, b_mn, partial, M, N, static_cast<int>(Ks), 1, splits, N, 0, mn, none, st, true, dt); \
+    else launch_tc05<TT, 128, 128>(as, bs, a_mn, b_mn, partial, M, N, static_cast<int>(Ks), 1, splits, N, 0, mn, none, st, true, dt);        \
+    splitk_reduce_kernel<TT><<<ew_grid(mn / 4 + 1, 256, static_cast<int>(sms)), 256, 0, st>>>(                                \
+        partial.data_as<float>(), C.data_as<TT>(), splits, mn, N, ldc);                                                        \
+  } while (0)
+        if (dt == DType::BF16) OB_SPLITK_LAUNCH(__nv_bfloat16);
+        else OB_SPLITK_LAUNCH(__half);
+#undef OB_SPLITK_LAUNCH
+        check_launch("gemm_tc05 (split-K)");
+        return;
+      }
+    }
+  }
   // Tile width: 256 columns whenever the problem is wider than one 128-column tile.  Narrow tiles
   // fill the last wave of the persistent grid better but run at about two thirds of the wide
   // tile's rate (measured on 8192 x 2048 x 8192: 900 against 1330 TFLOP/s), so they pay only when

@@ -392,3 +392,33 @@ def _piece_product_api_checks(rng, f64):
     close(y, torch.relu(f64(x) @ f64(wgt) + f64(bias)), "float32")
     y2 = ob.linear(dev_tensor(x, "float32"), dev_tensor(wgt, "float32"), dev_tensor(bias, "float32"))
     close(y2, f64(x) @ f64(wgt) + f64(bias), "float32")
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+def test_split_k_gemm_small_output_long_reduction(dtype):
+    """Weight-gradient shapes of a narrow model: the reduction is split over batch entries of the
+    tcgen05 kernel and the float32 partials are added in a fixed order."""
+    rng = np.random.default_rng(44)
+    for (m, k, n) in [(512, 16384, 512), (512, 8192, 2048), (256, 4096, 384)]:
+        x = rng.standard_normal((k, m)) * 0.1   # stored [K, M]: the transposed (weight-gradient) form
+        g = rng.standard_normal((k, n)) * 0.1
+        tx, tg = dev_tensor(x, dtype), dev_tensor(g, dtype)
+        ref = ref_round(x, dtype).double().T @ ref_round(g, dtype).double()
+        out = ob.matmul(ob.transpose(tx, 0, 1), tg)
+        assert _C._matmul_last_route().startswith("tcgen05")
+        close(out, ref.float(), dtype, scale=0.5)
+        again = ob.matmul(ob.transpose(tx, 0, 1), tg)
+        assert out.numpy().tobytes() == again.numpy().tobytes()   # fixed summation order
+        # K-major operands as well
+        a = rng.standard_normal((m, k)) * 0.1
+        b = rng.standard_normal((n, k)) * 0.1
+        ta, tb = dev_tensor(a, dtype), dev_tensor(b, dtype)
+        ref2 = ref_round(a, dtype).double() @ ref_round(b, dtype).double().T
+        close(ob.matmul(ta, ob.transpose(tb, 0, 1)), ref2.float(), dtype, scale=0.5)
+    # gradients of a Linear over many tokens take the same route
+    w = rng.standard_normal((512, 512)) * 0.05
+    xs = rng.standard_normal((16384, 512)) * 0.5
+    tw, txs = dev_tensor(w, dtype, True), dev_tensor(xs, dtype)
+    ob.matmul(txs, tw).sum().backward()
+    expect = ref_round(xs, dtype).double().T @ torch.ones(16384, 512, dtype=torch.float64)
+    close(tw.grad, expect.float(), dtype, scale=2.0)
