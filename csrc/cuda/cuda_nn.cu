@@ -791,7 +791,13 @@ void k_layernorm_bwd(OpCall& c) {
   const int sms = sm_count_for(x);
   const int threads = 256;
   if (D > 256 * 32) throw std::invalid_argument("layer_norm backward: normalized size above 8192 is not supported on CUDA");
-  const int nblocks = static_cast<int>(std::min<int64_t>(R, static_cast<int64_t>(sms) * 4));
+  int fth = 0, fch = 0;
+  const bool fast = ln_fast_ok<T>(c, D, &fth, &fch);
+  // Rows are walked by persistent blocks.  Narrow rows give small blocks (64 threads for 512
+  // columns), so more of them are needed per SM to keep enough loads in flight: up to 1024
+  // resident threads per SM (64 registers each), at most 16 blocks.
+  const int per_sm = fast ? std::max(4, std::min(16, 1024 / std::max(fth, 1))) : 4;
+  const int nblocks = static_cast<int>(std::min<int64_t>(R, static_cast<int64_t>(sms) * per_sm));
   const bool need_params = c.out[1].defined() || c.out[2].defined();
   ScratchLease lease;
   float* partial = nullptr;
@@ -800,8 +806,7 @@ void k_layernorm_bwd(OpCall& c) {
     partial = static_cast<float*>(lease.data());
   }
   const T* pw = c.in[1].defined() ? c.in[1].data_as<T>() : nullptr;
-  int fth = 0, fch = 0;
-  if (ln_fast_ok<T>(c, D, &fth, &fch)) {
+  if (fast) {
     const T* px = x.data_as<T>();
     const T* pg = c.in[2].data_as<T>();
     const float* pmn = c.in[3].data_as<float>();

@@ -65,7 +65,7 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int kEpilogueWarps = 4;
 // TMA warp, MMA warp, four epilogue warps per MMA row block of the tile.
-constexpr int gemm_threads(int tile_rows) { return 32 * (2 + kEpilogueWarps * (tile_rows / 128)); }
+constexpr int gemm_threads(int tile_rows, int epilogue_warps = kEpilogueWarps) { return 32 * (2 + epilogue_warps * (tile_rows / 128)); }
 
 enum : int { kErrProducer = 1, kErrMma = 2, kErrEpilogue = 3 };
 
@@ -110,12 +110,18 @@ __device__ __forceinline__ float gelu_grad(float z) {
   return 0.5f * (1.f + erff(z * 0.70710678118654752f)) + z * 0.3989422804014327f * __expf(-0.5f * z * z);
 }
 
-template <class T, int BN, int TM>
-__global__ void __launch_bounds__(gemm_threads(TM), 1)
+// EW = epilogue warps per MMA row block: 4, or 8 for 128-row tiles with short reductions, where
+// draining a 128 x 256 accumulator takes longer than computing the next one: two warps then share
+// each TMEM lane quarter and take half of the columns each.
+template <class T, int BN, int TM, int EW = kEpilogueWarps>
+__global__ void __launch_bounds__(gemm_threads(TM, EW), 1)
 gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_z, GemmParams p) {
   using L = SmemLayout<BN, TM>;
   constexpr int H = TM / BM;  // MMA row blocks per tile
+  static_assert(EW == 4 || (EW == 8 && H == 1 && BN == 256), "eight epilogue warps are for the 128 x 256 tile");
+  constexpr bool kSplitCols = EW == 8;        // two warps per lane quarter, half of the columns each
+  constexpr bool kOneStage = H == 2 || EW == 8;  // one 4 KB staging tile per epilogue warp
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_smem = smem + L::kStages * L::kStageBytes;
@@ -136,7 +142,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < L::kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], kEpilogueWarps); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], EW); }
     mbar_init_fence();
   }
   if (warp == 1) tmem_alloc(tmem_slot, 2 * BN);
@@ -261,8 +267,10 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const bool vec = staged || (vec_ok && (p.N % 8 == 0));
     // Staging: two 4 KB tiles per warp with one row block, one per warp with two (the row blocks
     // are then drained concurrently by their own four warps).
-    uint8_t* ebuf = epi_smem + (warp - 2) * (H == 1 ? 8192 : 4096);
-    const int my_h = (warp - 2) >> 2;
+    uint8_t* ebuf = epi_smem + (warp - 2) * (kOneStage ? 4096 : 8192);
+    const int my_h = (warp - 2) >> 2;   // row block (H == 2) or column half (EW == 8) of this warp
+    constexpr int kSubs = BN / 32;
+    const int sub_begin = kSplitCols ? my_h * (kSubs / 2) : 0, sub_end = kSplitCols ? sub_begin + kSubs / 2 : kSubs;
     int buf = 0;
     for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
       int bidx, tm, tn;
@@ -282,7 +290,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
       const float bias_row = (bias && p.bias_rows && row_ok && !p.out_f32) ? to_f(bias[row]) : 0.f;
 #pragma unroll 1
-      for (int sub = 0; sub < BN / 32; ++sub) {
+      for (int sub = sub_begin; sub < sub_end; ++sub) {
         const int col0 = tn * BN + sub * 32;
         if (col0 >= p.N) break;  // uniform across the warp
         float v[32];
@@ -321,7 +329,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (staged && half == 0) {
           // The tile about to be overwritten must have been read by its previous store.
           if (lane == 0) {
-            if (Zb || H == 2) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            if (Zb || kOneStage) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
             else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
           }
           __syncwarp();
@@ -425,8 +433,8 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             for (int j = 0; j < 32; ++j) v[j] += aux[j];
           }
         }
-        emit(Cb, H == 2 ? ebuf : (Zb ? ebuf + 4096 : ebuf + buf * 4096), false, v);
-        if (H == 1 && staged && !Zb && (half == 1 || col0 + 32 >= p.N)) buf ^= 1;
+        emit(Cb, kOneStage ? ebuf : (Zb ? ebuf + 4096 : ebuf + buf * 4096), false, v);
+        if (!kOneStage && staged && !Zb && (half == 1 || col0 + 32 >= p.N)) buf ^= 1;
       }
       tc_fence_before();
       __syncwarp();
@@ -761,7 +769,7 @@ void launch_simt(const OperandView& a, const OperandView& b, Tensor& C, int M, i
   check_launch("gemm (SIMT)");
 }
 
-template <class T, int BN, int TM>
+template <class T, int BN, int TM, int EW = kEpilogueWarps>
 void launch_tc05(const OperandView& a, const OperandView& b, bool a_mn, bool b_mn, Tensor& C, int M, int N, int K,
                  int nb0, int nb1, long long ldc, long long c_bs0, long long c_bs1, const Epilogue& ep, cudaStream_t st,
                  bool out_f32 = false, DType out_f32_operands = DType::BF16) {
@@ -805,11 +813,11 @@ void launch_tc05(const OperandView& a, const OperandView& b, bool a_mn, bool b_m
   p.tma_store = tma_store ? 1 : 0;
   static std::once_flag once;
   std::call_once(once, [] {
-    OB_CUDA(cudaFuncSetAttribute(gemm_tc05_kernel<T, BN, TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    OB_CUDA(cudaFuncSetAttribute(gemm_tc05_kernel<T, BN, TM, EW>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
   });
   const long long tiles = static_cast<long long>((M + TM - 1) / TM) * ((N + BN - 1) / BN) * nb0 * nb1;
   const int grid = static_cast<int>(std::min<long long>(tiles, sm_count_for(C)));
-  gemm_tc05_kernel<T, BN, TM><<<grid, gemm_threads(TM), L::kTotal, st>>>(ma, mb, mc, mz, p);
+  gemm_tc05_kernel<T, BN, TM, EW><<<grid, gemm_threads(TM, EW), L::kTotal, st>>>(ma, mb, mc, mz, p);
   check_launch("gemm_tc05");
 }
 
@@ -978,9 +986,13 @@ void gemm_dispatch(const Tensor& A_in, bool ta, const Tensor& B_in, bool tb, Ten
   const bool tall = wide && force_tm != 128 && !ep.preact.defined() &&
                     (force_tm == 256 || (M >= 512 && K >= tall_min_k && eff256 >= 0.8));
   if (tall) g_last_route.store(3, std::memory_order_relaxed);
+  // Short reductions: the epilogue, not the MMA loop, sets the pace of a tile; eight warps drain it.
+  static const int short_k_max = [] { const char* e = std::getenv("ORTHON_GEMM_EW8_MAX_K"); return e ? std::atoi(e) : 1024; }();
+  const bool short_k = !tall && K <= short_k_max && !ep.preact.defined();
 #define OB_GEMM_LAUNCH(TT)                                                                                           \
   do {                                                                                                               \
     if (tall) launch_tc05<TT, 256, 256>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);          \
+    else if (wide && short_k) launch_tc05<TT, 256, 128, 8>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st); \
     else if (wide) launch_tc05<TT, 256, 128>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);     \
     else launch_tc05<TT, 128, 128>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);               \
   } while (0)
