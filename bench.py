@@ -195,7 +195,14 @@ def _max_over_ranks(value, world, device):
 
 def run_reference(args):
     from baseline.reference_bench import run
-    run(args)
+    try:
+        run(args)
+    except Exception as exc:  # noqa: BLE001
+        # One rank: report the failure in the contract's form.  Several ranks: let the launcher
+        # see the error, so that it stops the ranks still waiting in a collective.
+        if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+            raise
+        print(json.dumps({"impl": "reference", "unavailable": f"{type(exc).__name__}: {exc}"[:300]}), flush=True)
 
 
 if __name__ == "__main__":
