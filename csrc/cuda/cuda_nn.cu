@@ -670,6 +670,34 @@ __global__ void layernorm_bwd_finalize_fast(const float* __restrict__ partial, T
   }
 }
 
+// First stage for many partial rows: group g adds its share of the rows (fixed order) into
+// out[g][2][D], so that the final pass above reads a few dozen rows instead of thousands.
+// grid = (ceil(D / 32), groups), block = (32, 32).
+__global__ void layernorm_bwd_group_partials(const float* __restrict__ partial, float* __restrict__ out, int nblocks, int64_t D) {
+  __shared__ float ta[32][33], tb[32][33];
+  const int64_t j = static_cast<int64_t>(blockIdx.x) * 32 + threadIdx.x;
+  const int per = (nblocks + gridDim.y - 1) / gridDim.y;
+  const int begin = blockIdx.y * per, end = min(nblocks, begin + per);
+  float a = 0.f, b = 0.f;
+  if (j < D) {
+#pragma unroll 4
+    for (int i = begin + threadIdx.y; i < end; i += 32) {
+      a += partial[static_cast<int64_t>(i) * 2 * D + j];
+      b += partial[static_cast<int64_t>(i) * 2 * D + D + j];
+    }
+  }
+  ta[threadIdx.y][threadIdx.x] = a;
+  tb[threadIdx.y][threadIdx.x] = b;
+  __syncthreads();
+  if (threadIdx.y == 0 && j < D) {
+    float sa = 0.f, sb = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) { sa += ta[i][threadIdx.x]; sb += tb[i][threadIdx.x]; }
+    out[static_cast<int64_t>(blockIdx.y) * 2 * D + j] = sa;
+    out[static_cast<int64_t>(blockIdx.y) * 2 * D + D + j] = sb;
+  }
+}
+
 template <class T>
 bool ln_fast_ok(const OpCall& c, int64_t D, int* threads, int* chunks) {
   constexpr int N = Pack<T>::N;
@@ -783,6 +811,8 @@ void k_layernorm(OpCall& c) {
   check_launch("layer_norm");
 }
 
+constexpr int kLnGroups = 32;  // row groups of the two-stage reduction of the LayerNorm parameter-gradient partials
+
 template <class T>
 void k_layernorm_bwd(OpCall& c) {
   const Tensor& x = c.in[0];
@@ -802,7 +832,7 @@ void k_layernorm_bwd(OpCall& c) {
   ScratchLease lease;
   float* partial = nullptr;
   if (need_params) {
-    lease = ScratchLease(x.device(), sizeof(float) * nblocks * 2 * D, st);
+    lease = ScratchLease(x.device(), sizeof(float) * (nblocks + kLnGroups) * 2 * D, st);
     partial = static_cast<float*>(lease.data());
   }
   const T* pw = c.in[1].defined() ? c.in[1].data_as<T>() : nullptr;
@@ -815,9 +845,18 @@ void k_layernorm_bwd(OpCall& c) {
     if (fch == 1) layernorm_bwd_fast<T, 1><<<nblocks, fth, 0, st>>>(px, pw, pg, pmn, prs, pdx, partial, R, D);
     else if (fch == 2) layernorm_bwd_fast<T, 2><<<nblocks, fth, 0, st>>>(px, pw, pg, pmn, prs, pdx, partial, R, D);
     else layernorm_bwd_fast<T, 4><<<nblocks, fth, 0, st>>>(px, pw, pg, pmn, prs, pdx, partial, R, D);
-    if (need_params)
+    if (need_params) {
+      const float* rows = partial;
+      int nrows = nblocks;
+      if (nblocks > 1024) {  // narrow rows: thousands of partial rows, reduce them in two stages
+        float* grouped = partial + static_cast<int64_t>(nblocks) * 2 * D;
+        layernorm_bwd_group_partials<<<dim3(static_cast<unsigned>((D + 31) / 32), kLnGroups), dim3(32, 32), 0, st>>>(partial, grouped, nblocks, D);
+        rows = grouped;
+        nrows = kLnGroups;
+      }
       layernorm_bwd_finalize_fast<T><<<static_cast<unsigned>((D + 31) / 32), dim3(32, 32), 0, st>>>(
-          partial, c.out[1].defined() ? c.out[1].data_as<T>() : nullptr, c.out[2].defined() ? c.out[2].data_as<T>() : nullptr, nblocks, D);
+          rows, c.out[1].defined() ? c.out[1].data_as<T>() : nullptr, c.out[2].defined() ? c.out[2].data_as<T>() : nullptr, nrows, D);
+    }
     check_launch("layer_norm backward");
     return;
   }

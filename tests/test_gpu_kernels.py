@@ -127,9 +127,10 @@ def test_softmax_family_and_losses(dtype):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_layer_norm(dtype):
     rng = np.random.default_rng(5)
-    for D in (512, 100):
-        a = rng.standard_normal((70, D)) * 2 + 0.5; w = rng.standard_normal((D,)); b = rng.standard_normal((D,))
-        g = rng.standard_normal((70, D))
+    # (4100, 512): narrow rows in thousands of persistent blocks, parameter gradients reduced in two stages
+    for R, D in ((70, 512), (70, 100), (4100, 512), (300, 2048)):
+        a = rng.standard_normal((R, D)) * 2 + 0.5; w = rng.standard_normal((D,)); b = rng.standard_normal((D,))
+        g = rng.standard_normal((R, D))
         x, ww, bb = dev_tensor(a, dtype, True), dev_tensor(w, dtype, True), dev_tensor(b, dtype, True)
         t, tw, tb = (ref_round(v, dtype).requires_grad_(True) for v in (a, w, b))
         y = _C._layer_norm(x, ww, bb, 1e-5)
@@ -138,8 +139,8 @@ def test_layer_norm(dtype):
         (y * dev_tensor(g, dtype)).sum().backward()
         (ty * ref_round(g, dtype)).sum().backward()
         close(x.grad, t.grad, dtype, 2)
-        close(ww.grad, tw.grad, dtype, 8)
-        close(bb.grad, tb.grad, dtype, 8)
+        close(ww.grad, tw.grad, dtype, 8 if R < 1000 else 32)
+        close(bb.grad, tb.grad, dtype, 8 if R < 1000 else 32)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
