@@ -142,41 +142,27 @@ CONFIGS = {
 }
 
 
-def run_reference_lm(args, cfg_override=None, dtype_override=None, device_override=None):
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    try:
-        ortho = _import_reference()
-    except Exception as exc:  # noqa: BLE001
-        if rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable": f"cannot import the reference build: {exc}"}))
-        return
-    cfg, batch, seq, name = CONFIGS[args.model]
-    if cfg_override:
-        cfg, batch, seq = cfg_override
-    fp16 = getattr(args, "amp", "bf16") == "fp16"
-    dtype = dtype_override or ("float16" if fp16 else "bfloat16")
-    device = device_override or f"cuda:{local}"
-    if device != "cpu" and not ortho.cuda_enabled():
-        if rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable": "reference build has no CUDA support"}))
-        return
+def _measure(ortho, args, model_key, amp, micro, rank, world, local):
+    """W warm-up steps, K timed steps and K end-to-end steps of one configuration.  `micro` > 1
+    splits each step's batch into that many equal slices whose gradients accumulate in `.grad`
+    (the reference's own accumulate-until-zero_grad contract) before the single optimizer step."""
     import orthon.distributed as ddist
     from orthon.amp import GradScaler, MixedPrecisionOptimizer
     from orthon.optim import Adam
 
-    if world > 1:
-        store = f"/tmp/orthon_ref_store_{os.environ.get('MASTER_PORT', '0')}_{os.getppid()}"
-        os.makedirs(store, exist_ok=True)
-        os.environ["ORTHON_NCCL_STORE_DIR"] = store
-        ddist.init_process_group("nccl", rank=rank, world_size=world, device=local)
+    cfg, batch, seq, name = CONFIGS[model_key]
+    fp16 = amp == "fp16"
+    dtype = "float16" if fp16 else "bfloat16"
+    device = f"cuda:{local}"
+    if batch % micro:
+        raise ValueError("micro-batch count must divide the batch")
+    mb = batch // micro
 
     # The reference pool never splits blocks, so cached blocks of one size class cannot serve
     # another; on the 1.3 B config the cache alone exhausts 180 GB.  Its own runtime toggle caps
     # the cache so that the configuration fits.
-    cap_gb = os.environ.get("ORTHON_REF_POOL_CAP_GB", "16" if args.model == "1p3b" else "")
-    if cap_gb and device != "cpu":
+    cap_gb = os.environ.get("ORTHON_REF_POOL_CAP_GB", "16" if model_key == "1p3b" else "")
+    if cap_gb:
         ortho._C._memory_pool_set_max_cached_bytes(int(float(cap_gb) * (1 << 30)))
 
     model = build_model(ortho, cfg, dtype, device, seed=1234)
@@ -188,81 +174,144 @@ def run_reference_lm(args, cfg_override=None, dtype_override=None, device_overri
 
     rng = np.random.default_rng(100 + rank)
     mask_np = np.triu(np.full((seq, seq), -1e9, dtype=np.float32), k=1).reshape(1, seq, seq)
-    mask = ortho.from_numpy(mask_np)
-    pos = ortho.from_numpy(np.tile(np.arange(seq, dtype=np.int64), (batch, 1)))
-    if device != "cpu":
-        mask, pos = mask.to(device), pos.to(device)
+    mask = ortho.from_numpy(mask_np).to(device)
+    pos = ortho.from_numpy(np.tile(np.arange(seq, dtype=np.int64), (mb, 1))).to(device)
 
     def make_batch():
         tok = rng.integers(0, cfg["vocab_size"], size=(batch, seq + 1), dtype=np.int64)
-        x = ortho.from_numpy(np.ascontiguousarray(tok[:, :-1]))
-        y = ortho.from_numpy(np.ascontiguousarray(tok[:, 1:]).reshape(-1))
-        return (x, y) if device == "cpu" else (x.to(device), y.to(device))
+        out = []
+        for i in range(micro):
+            rows = tok[i * mb:(i + 1) * mb]
+            x = ortho.from_numpy(np.ascontiguousarray(rows[:, :-1])).to(device)
+            y = ortho.from_numpy(np.ascontiguousarray(rows[:, 1:]).reshape(-1)).to(device)
+            out.append((x, y))
+        return out
 
-    def step(x, y):
+    def step(slices):
         opt.zero_grad()
-        log_probs = wrapped(x, pos, mask)
-        loss = ortho.nll_loss(log_probs, y, reduction="mean")
-        scaler.scale(loss).backward()
+        total = None
+        for x, y in slices:
+            log_probs = wrapped(x, pos, mask)
+            loss = ortho.nll_loss(log_probs, y, reduction="mean")
+            if micro > 1:
+                loss = loss * (1.0 / micro)
+            scaler.scale(loss).backward()
+            total = loss if total is None else total + loss
         scaler.step(opt)
         scaler.update()
-        return loss
+        return total
 
     def sync():
-        if device != "cpu":
-            ortho.cuda_synchronize()
+        ortho.cuda_synchronize()
         if world > 1:
             ddist.barrier()
 
-    x, y = make_batch()
-    try:
-        for _ in range(args.warmup):
-            step(x, y)
-    except RuntimeError as exc:
-        if "out of memory" not in str(exc):
-            raise
-        stats = ortho._C._memory_pool_stats() if hasattr(ortho._C, "_memory_pool_stats") else None
-        if rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable": "the reference runs out of device memory on this config "
-                              f"(pool cache capped at {cap_gb or 'unlimited'} GB): {exc}", "pool_stats": str(stats)}), flush=True)
-        return
+    slices = make_batch()
+    for _ in range(args.warmup):
+        step(slices)
     sync()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        step(x, y)
+        step(slices)
     sync()
     device_s = time.perf_counter() - t0
 
     t0 = time.perf_counter()
     last = None
     for _ in range(args.steps):
-        x, y = make_batch()            # host -> device copy of this step's inputs
-        last = float(step(x, y).item())  # device -> host read of the loss
+        slices = make_batch()                 # host -> device copy of this step's inputs
+        last = float(step(slices).item())     # device -> host read of the loss
     sync()
     e2e_s = time.perf_counter() - t0
 
     if world > 1:
-        t = ortho.from_numpy(np.asarray([device_s, e2e_s], dtype=np.float32)).to(device)
-        # max over ranks via sum of per-rank one-hot rows
-        rows = np.zeros((world, 2), dtype=np.float32)
+        rows = np.zeros((world, 2), dtype=np.float32)  # max over ranks via a sum of one-hot rows
         rows[rank] = [device_s, e2e_s]
         t = ortho.from_numpy(rows).to(device)
         ddist.all_reduce(t)
         vals = np.asarray(t.to("cpu").tolist()).reshape(world, 2)
         device_s, e2e_s = float(vals[:, 0].max()), float(vals[:, 1].max())
     tokens = batch * seq * world * args.steps
-    if rank == 0:
-        print(json.dumps({
-            "metric": "ddp_train_tokens_per_s", "value": tokens / device_s, "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": device_s / args.steps * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": {"bfloat16": "bf16", "float16": "fp16"}.get(dtype, dtype),
-            "data": "synthetic token ids, random-init weights", "impl": "reference",
-            "config": {"model": name, "global_batch": batch * world, "seq_len": seq, "parallelism": f"dp{world}",
-                       "optimizer": "FP32-master Adam (reference MixedPrecisionOptimizer, " + ("GradScaler init 128)" if fp16 else "scaler disabled)"),
-                       "timing": "wall clock between cuda_synchronize() calls (no event API in the reference)"},
+    config = {"model": name, "global_batch": batch * world, "seq_len": seq, "parallelism": f"dp{world}",
+              "optimizer": "FP32-master Adam (reference MixedPrecisionOptimizer, " + ("GradScaler init 128)" if fp16 else "scaler disabled)"),
+              "timing": "wall clock between cuda_synchronize() calls (no event API in the reference)"}
+    if micro > 1:
+        config["micro_batches"] = micro
+        config["note"] = (f"the full batch does not fit in device memory with the reference's kernels; each step runs {micro} "
+                          f"slices of {mb} sequences whose gradients accumulate before the one optimizer step")
+    return {"value": tokens / device_s, "ms_per_step": device_s / args.steps * 1e3,
+            "dtype": "fp16" if fp16 else "bf16", "config": config,
             "e2e": {"value": tokens / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 2 * batch * seq * 8,
-                    "d2h_bytes_per_step": 4, "last_loss": last},
-        }), flush=True)
-    if world > 1:
-        ddist.destroy_process_group()
+                    "d2h_bytes_per_step": 4, "last_loss": last}}
+
+
+def _measure_with_fallback(ortho, args, model_key, amp, rank, world, local):
+    """Tries the full batch first; if the reference runs out of device memory, halves the slice
+    until the step fits.  Returns (result or None, list of out-of-memory notes)."""
+    import gc
+
+    import orthon.distributed as ddist
+    batch = CONFIGS[model_key][1]
+    notes, micro = [], 1
+    while micro <= batch:
+        if world > 1:
+            store = f"/tmp/orthon_ref_store_{os.environ.get('MASTER_PORT', '0')}_{os.getppid()}_{model_key}_{micro}"
+            os.makedirs(store, exist_ok=True)
+            os.environ["ORTHON_NCCL_STORE_DIR"] = store
+            ddist.init_process_group("nccl", rank=rank, world_size=world, device=local)
+        try:
+            return _measure(ortho, args, model_key, amp, micro, rank, world, local), notes
+        except RuntimeError as exc:
+            if "out of memory" not in str(exc):
+                raise
+            stats = ortho._C._memory_pool_stats() if hasattr(ortho._C, "_memory_pool_stats") else None
+            peak = getattr(stats, "get", lambda *_: None)("peak_bytes") if stats is not None else None
+            notes.append(f"{micro} slice(s) per step: out of device memory" + (f" (pool peak {peak} bytes)" if peak else ""))
+        finally:
+            if world > 1:
+                ddist.destroy_process_group()
+            gc.collect()
+            ortho.cuda_synchronize()
+            for name in ("_memory_pool_clear_cache", "_memory_pool_reset_stats"):  # the reference's own toggles
+                if hasattr(ortho._C, name):
+                    getattr(ortho._C, name)()
+        micro *= 2
+    return None, notes
+
+
+ANCHOR = ("tiny", "fp16")
+
+
+def run_reference_lm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    try:
+        ortho = _import_reference()
+    except Exception as exc:  # noqa: BLE001
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": f"cannot import the reference build: {exc}"}))
+        return
+    if not ortho.cuda_enabled():
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "reference build has no CUDA support"}))
+        return
+    amp = getattr(args, "amp", "bf16")
+    main, notes = _measure_with_fallback(ortho, args, args.model, amp, rank, world, local)
+    if main is None:
+        line = {"impl": "reference", "unavailable": "the reference runs out of device memory on this config at every slice size: " + "; ".join(notes)}
+    else:
+        line = {"metric": "ddp_train_tokens_per_s", "value": main["value"], "unit": "tokens/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": main["ms_per_step"], "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": main["dtype"],
+                "data": "synthetic token ids, random-init weights", "impl": "reference", "config": main["config"],
+                "e2e": main["e2e"]}
+        if notes:
+            line["config"]["out_of_memory"] = notes
+    if getattr(args, "anchor", True) and (args.model, amp) != ANCHOR:
+        a, a_notes = _measure_with_fallback(ortho, args, ANCHOR[0], ANCHOR[1], rank, world, local)
+        line["anchor"] = {"unavailable": "; ".join(a_notes)} if a is None else {
+            "config": a["config"], "dtype": a["dtype"], "value": a["value"], "unit": "tokens/s",
+            "ms_per_step": a["ms_per_step"], "e2e": a["e2e"]}
+    if rank == 0:
+        print(json.dumps(line), flush=True)

@@ -7,6 +7,13 @@ GELU, pre-LayerNorm, learned positions, seq 1024, batch 8 per GPU, bf16 compute 
 Adam, DDP with 25 MB gradient buckets.  Token ids are uniform in [0, vocab); weights N(0, 0.02).
 Synthetic data, random-init weights.
 
+Both arms also measure a second configuration that the reference can hold in memory at full
+batch, with the same steps / warm-up and timing rules, and print it under the `anchor` key of the
+same line: the tiny causal LM (vocab 8192, d 512, 8 layers, seq 512, batch 32 per GPU) in fp16
+with GradScaler(init_scale=128).  On the 1.3 B configuration the reference arm falls back to
+slices of the batch with gradient accumulation when the full batch runs out of device memory
+(recorded in its `config`).
+
 Printed line (rank 0): tokens/s summed over all GPUs.  `value` is device-timed (CUDA events
 around exactly K steps, barrier + synchronize on both sides, max over ranks) with the step's
 inputs already resident; `e2e.value` times K more steps through the public API including the
@@ -25,6 +32,7 @@ sys.path.insert(0, ROOT)
 
 METRIC = "ddp_train_tokens_per_s"
 BASELINE_PUBLISHED = None  # the reference publishes no throughput number
+ANCHOR = ("tiny", "fp16")   # tiny causal LM, fp16 compute, GradScaler(init_scale=128)
 
 
 def parse_args():
@@ -37,6 +45,8 @@ def parse_args():
     ap.add_argument("--backend", default=None, help="distributed transport for --gpus > 1 (default: p2p)")
     ap.add_argument("--amp", default="bf16", choices=["bf16", "fp16"],
                     help="bf16: bf16 compute, scaler disabled; fp16: fp16 compute with GradScaler(init_scale=128)")
+    ap.add_argument("--no-anchor", dest="anchor", action="store_false",
+                    help="skip the second measurement (tiny causal LM, fp16, GradScaler 128) printed under 'anchor'")
     return ap.parse_args()
 
 
@@ -47,7 +57,9 @@ def model_config(name):
     return TINY_LM, 32, 512, "bfloat16", "tiny-causal-lm (vocab 8192, d512, L8, H8, ffn 2048)"
 
 
-def run_ours(args):
+def measure_ours(args, model_key, amp, rank, world, local):
+    """One measurement of one configuration: W warm-up steps, K device-timed steps, K end-to-end
+    steps.  Returns the fields of the printed line that belong to this configuration."""
     import numpy as np
     import orthon_b200 as ob
     import orthon_b200.distributed as dist
@@ -55,19 +67,11 @@ def run_ours(args):
     from orthon_b200.models import CausalLM
     from orthon_b200.utils import ClockSampler
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} does not match WORLD_SIZE {world}")
     device = f"cuda:{local}"
-    cfg, batch, seq, dtype, model_name = model_config(args.model)
-    fp16 = args.amp == "fp16"
+    cfg, batch, seq, dtype, model_name = model_config(model_key)
+    fp16 = amp == "fp16"
     if fp16:
         dtype = "float16"
-
-    if world > 1:
-        dist.init_process_group(args.backend or "p2p", rank=rank, world_size=world, device=local)
     ob.manual_seed(1234)  # identical initial weights on every rank
     model = CausalLM(cfg)
     model.cast(dtype).to(device)
@@ -75,8 +79,8 @@ def run_ours(args):
     if world > 1:
         wrapped = dist.DDP(model, sync_grads=False, bucket_size_mb=25)
     # With a live GradScaler the update must wait for the found-inf verdict, so buckets are only
-    # reduced during backward ("reduce"); otherwise the optimizer update is fused into them.
-    opt = ob.amp.MixedPrecisionOptimizer(wrapped, ob.optim.Adam, fused="reduce" if fp16 else "update", lr=3e-4)
+    # averaged during backward ("overlap"); otherwise the optimizer update is fused into them.
+    opt = ob.amp.MixedPrecisionOptimizer(wrapped, ob.optim.Adam, fused="overlap" if fp16 else "update", lr=3e-4)
     scaler = ob.amp.GradScaler(init_scale=128.0, enabled=fp16)
 
     rng = np.random.default_rng(100 + rank)
@@ -141,27 +145,60 @@ def run_ours(args):
     device_ms = _max_over_ranks(device_ms, world, device)
     e2e_s = _max_over_ranks(e2e_s, world, device)
     tokens = batch * seq * world * args.steps
-    value = tokens / (device_ms * 1e-3)
+    return {
+        "value": tokens / (device_ms * 1e-3), "ms_per_step": device_ms / args.steps,
+        "dtype": "fp16" if fp16 else "bf16",
+        "config": {"model": model_name, "global_batch": batch * world, "seq_len": seq,
+                   "parallelism": f"dp{world}",
+                   "optimizer": "FP32-master Adam (AMP, GradScaler init 128)" if fp16 else "FP32-master Adam (AMP, scaler disabled)",
+                   "l2": "per-step working set (weights, activations and optimizer state) exceeds the 126 MB L2; no flush needed",
+                   "params": model.parameter_count()},
+        "clocks": {"sm_mhz": clocks.result["sm_mhz"], "sm_max_mhz": clocks.result["sm_max_mhz"],
+                   "reasons": clocks.result["reasons"]},
+        "e2e": {"value": tokens / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 2 * batch * seq * 8,
+                "d2h_bytes_per_step": 4, "last_loss": last},
+        "gpu_launches": int(launches),
+    }
+
+
+def run_ours(args):
+    import gc
+
+    import orthon_b200.distributed as dist
+    from orthon_b200 import _C
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} does not match WORLD_SIZE {world}")
+
+    def one(model_key, amp):
+        if world > 1:
+            dist.init_process_group(args.backend or "p2p", rank=rank, world_size=world, device=local)
+        try:
+            return measure_ours(args, model_key, amp, rank, world, local)
+        finally:
+            if world > 1:
+                dist.destroy_process_group()
+            gc.collect()
+            _C.cuda_synchronize()
+
+    main = one(args.model, args.amp)
+    line = {"metric": METRIC, "value": main["value"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": main["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None if BASELINE_PUBLISHED is None else main["value"] / BASELINE_PUBLISHED,
+            "dtype": main["dtype"], "data": "synthetic token ids, random-init weights", "impl": "ours",
+            "config": main["config"], "clocks": main["clocks"], "e2e": main["e2e"], "gpu_launches": main["gpu_launches"]}
+    if args.anchor and (args.model, args.amp) != ANCHOR:
+        # The second configuration both arms can run (the reference cannot hold the 1.3 B one
+        # in 180 GB at full batch): same steps / warm-up, same timing rules.
+        a = one(*ANCHOR)
+        line["anchor"] = {"config": a["config"], "dtype": a["dtype"], "value": a["value"], "unit": "tokens/s",
+                          "ms_per_step": a["ms_per_step"], "e2e": a["e2e"], "clocks": a["clocks"],
+                          "gpu_launches": a["gpu_launches"]}
     if rank == 0:
-        line = {
-            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": device_ms / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None if BASELINE_PUBLISHED is None else value / BASELINE_PUBLISHED,
-            "dtype": "fp16" if fp16 else "bf16", "data": "synthetic token ids, random-init weights", "impl": "ours",
-            "config": {"model": model_name, "global_batch": batch * world, "seq_len": seq,
-                       "parallelism": f"dp{world}",
-                       "optimizer": "FP32-master Adam (AMP, GradScaler init 128)" if fp16 else "FP32-master Adam (AMP, scaler disabled)",
-                       "l2": "per-step working set (>= 2.7 GB of weights) exceeds the 126 MB L2; no flush needed",
-                       "params": model.parameter_count()},
-            "clocks": {"sm_mhz": clocks.result["sm_mhz"], "sm_max_mhz": clocks.result["sm_max_mhz"],
-                       "reasons": clocks.result["reasons"]},
-            "e2e": {"value": tokens / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 2 * batch * seq * 8,
-                    "d2h_bytes_per_step": 4, "last_loss": last},
-            "gpu_launches": int(launches),
-        }
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
 
 
 def _ddp_loss(wrapped, model, ids, tgt):
@@ -194,9 +231,9 @@ def _max_over_ranks(value, world, device):
 
 
 def run_reference(args):
-    from baseline.reference_bench import run
+    from baseline.reference_lm import run_reference_lm
     try:
-        run(args)
+        run_reference_lm(args)
     except Exception as exc:  # noqa: BLE001
         # One rank: report the failure in the contract's form.  Several ranks: let the launcher
         # see the error, so that it stops the ranks still waiting in a collective.

@@ -83,6 +83,34 @@ def _compile_one(src: Path, flags_cxx, flags_cu, hdr: str, verbose: bool, ptxas:
     return obj, True, res.stderr if ptxas else ""
 
 
+def source_digest() -> str:
+    """Digest of everything under csrc/ (relative path and bytes of each file, in sorted order).
+    The extension carries the digest it was built from and the package compares it with the tree
+    at import, so Python code can never run against an extension built from older sources."""
+    h = hashlib.sha256()
+    for p in sorted(CSRC.rglob("*")):
+        if p.is_file() and p.suffix in (".cpp", ".cu", ".h", ".hpp", ".cuh"):
+            h.update(p.relative_to(CSRC).as_posix().encode())
+            h.update(b"\0")
+            h.update(p.read_bytes())
+    return h.hexdigest()
+
+
+def _compile_stamp(digest: str) -> Path:
+    """One tiny object that holds the source digest (rebuilt whenever any source changes)."""
+    src = OBJ / "source_stamp.cpp"
+    obj = OBJ / f"source_stamp.{digest[:16]}.o"
+    if obj.exists():
+        return obj
+    for stale in OBJ.glob("source_stamp.*.o"):
+        stale.unlink()
+    src.write_text(f'extern "C" __attribute__((visibility("default"))) const char* ob_source_digest() {{ return "{digest}"; }}\n')
+    res = subprocess.run(["g++", "-O1", "-fPIC", "-c", str(src), "-o", str(obj)], capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"compile failed: {src}\n{res.stderr}")
+    return obj
+
+
 def target_path() -> Path:
     return ROOT / "orthon_b200" / f"_C{sysconfig.get_config_var('EXT_SUFFIX')}"
 
@@ -98,7 +126,7 @@ def build_native_tests(jobs: int | None = None, verbose: bool = False) -> Path:
     key = hashlib.sha256(_header_digest().encode())
     for p in sorted(tests_dir.iterdir()):
         key.update(p.read_bytes())
-    objs = sorted(o for o in OBJ.glob("*.o") if not o.name.startswith("bindings__module"))
+    objs = sorted(o for o in OBJ.glob("*.o") if not o.name.startswith("bindings__module") and not o.name.startswith("tests_cpp__"))
     key.update(" ".join(str(o) for o in objs).encode())
     out = ROOT / "build" / "ob_native_tests"
     stamp = OBJ / "native_tests.stamp"
@@ -133,6 +161,7 @@ def build(jobs: int | None = None, verbose: bool = False, ptxas: bool = False) -
             rebuilt += int(did)
             if info:
                 print(info)
+    objs.append(_compile_stamp(source_digest()))
     out = target_path()
     stamp = OBJ / "link.stamp"
     link_key = hashlib.sha256(" ".join(str(o) for o in objs).encode()).hexdigest()

@@ -20,10 +20,22 @@
 //
 // Barriers are per-CTA flag words in peer memory written with st.release.sys and polled with
 // ld.acquire.sys; CTA b only ever depends on CTA b of the other ranks, and the grid is small
-// enough to be co-resident, so no deadlock is possible.  Every poll loop has a clock budget:
-// when it runs out the kernel records an error code in a status word and returns, it never
-// traps or spins forever.  Reduction order is rank 0..world-1 for every element and each
-// element is reduced by exactly one rank (two-shot), so all ranks end up bit-identical.
+// enough to be co-resident, so no deadlock is possible.  Every poll loop has a time budget (a
+// kernel argument, in nanoseconds of the global timer): when it runs out the kernel records an
+// error code in a status word and returns, it never traps or spins forever.  Reduction order is
+// rank 0..world-1 for every element and each element is reduced by exactly one rank (two-shot),
+// so all ranks end up bit-identical.
+//
+// The entry barrier also carries the participation consensus of the bucket: every rank
+// publishes one bit per parameter ("this rank produced a gradient") and an "invalid local
+// gradient profile" bit; after the barrier every rank holds the union of the usage bits (read
+// by the host only when it needs them) and, if any rank flagged its profile invalid, every rank
+// leaves the kernel without touching gradients or parameters and records kErrInvalidProfile.
+//
+// The block size is a launch parameter: 512 threads when the kernel has the GPU to itself, 128
+// when it runs beside the persistent tcgen05 GEMMs of a backward pass, whose CTAs leave about
+// 14 K registers per SM free (one 128-thread CTA of this kernel fits, a 512-thread one does not
+// and would wait for a GEMM to end and then hold its SM against the next one).
 //
 // Replaces (reference project paths): the NCCL all-reduce + per-parameter copy/scale path of
 // python/orthon/distributed/_reducer.py:61-163, the unscale/inf-check kernels
@@ -45,11 +57,12 @@ namespace {
 
 constexpr int kMaxRanks = 8;
 constexpr int kMaxCtas = 160;
-constexpr int kPeerThreads = 512;
-constexpr long long kPeerWaitBudget = 4000000000LL;  // about two seconds
+constexpr int kPeerThreads = 512;  // upper bound of the block size
+constexpr int kUsageWords = 64;    // one bit per parameter of a bucket: at most 2048 parameters
+constexpr uint32_t kInvalidBit = 0x80000000u;
 
 enum : int { kModeAverage = 0, kModeAdam = 1, kModeSgd = 2 };
-enum : int { kErrEntryBarrier = 11, kErrMidBarrier = 12, kErrExitBarrier = 13 };
+enum : int { kErrEntryBarrier = 11, kErrMidBarrier = 12, kErrInvalidProfile = 20 };
 
 struct PeerArgs {
   int rank, world, mode, oneshot;
@@ -70,14 +83,25 @@ struct PeerArgs {
   void* mc_grads;  // multicast mapping of every rank's bucket (NVLS path), or null
   int* status;     // local: first error code
   int* found_inf;  // local: set to 1 when any rank saw a non-finite reduced gradient
+  long long wait_ns;  // budget of every flag wait
+  int invalid;        // this rank's gradient profile is invalid: nobody reduces, everybody reports
+  int usage_words;    // number of valid words in `usage`
+  uint32_t usage[kUsageWords];  // bit i of word w: parameter 32 w + i of the bucket has a local gradient
 };
 
-// Flag block layout (uint32 words): [phase 0..2][cta][src rank], then one found-inf word.
-__host__ __device__ inline size_t flag_words() { return 3 * kMaxCtas * kMaxRanks + 8; }
+// Flag block layout (uint32 words): [phase 0..2][cta][src rank], one found-inf word (padded to
+// 8), the usage words of every source rank, and the union of them (local result).
+__host__ __device__ inline size_t flag_words() { return 3 * kMaxCtas * kMaxRanks + 8 + (kMaxRanks + 1) * kUsageWords; }
 __device__ __forceinline__ uint32_t* flag_at(uint32_t* base, int phase, int cta, int src) {
   return base + (static_cast<size_t>(phase) * kMaxCtas + cta) * kMaxRanks + src;
 }
 __device__ __forceinline__ uint32_t* inf_word(uint32_t* base) { return base + 3 * kMaxCtas * kMaxRanks; }
+__host__ __device__ inline size_t usage_offset(int src) { return 3 * kMaxCtas * kMaxRanks + 8 + static_cast<size_t>(src) * kUsageWords; }
+__device__ __forceinline__ long long global_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -88,24 +112,65 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   return v;
 }
 
-// All CTAs with the same index on all ranks meet here.  Returns false after a timeout.
-__device__ bool peer_barrier(const PeerArgs& a, int phase, int err_code) {
+// All CTAs with the same index on all ranks meet here.  Returns 0 after a timeout, 2 when a
+// rank tagged its arrival with the invalid-profile bit, 1 otherwise.  The low 31 bits of a flag
+// word are the epoch of the launch it belongs to.
+__device__ int peer_barrier(const PeerArgs& a, int phase, int err_code, uint32_t tag = 0) {
   __syncthreads();
-  int ok = 1;
+  int ok = 1, tagged = 0;
   if (threadIdx.x < a.world) {
     __threadfence_system();
-    st_release_sys(flag_at(a.flags[threadIdx.x], phase, blockIdx.x, a.rank), a.epoch);
+    st_release_sys(flag_at(a.flags[threadIdx.x], phase, blockIdx.x, a.rank), a.epoch | tag);
     const uint32_t* mine = flag_at(a.flags[a.rank], phase, blockIdx.x, threadIdx.x);
-    const long long t0 = clock64();
-    while (ld_acquire_sys(mine) != a.epoch) {
-      if (clock64() - t0 > kPeerWaitBudget) {
+    const long long t0 = global_ns();
+    uint32_t seen;
+    while (((seen = ld_acquire_sys(mine)) & ~kInvalidBit) != a.epoch) {
+      if (global_ns() - t0 > a.wait_ns) {
         atomicCAS(a.status, 0, err_code);
         ok = 0;
         break;
       }
     }
+    tagged = ok && (seen & kInvalidBit) != 0;
   }
-  return __syncthreads_and(ok) != 0;
+  const int any_tag = __syncthreads_or(tagged);
+  if (!__syncthreads_and(ok)) return 0;
+  return any_tag ? 2 : 1;
+}
+
+// Entry of every variant: publish this rank's usage bits (CTA 0), meet the peers, collect the
+// union of the usage bits, and agree on the validity of the step.  Returns false when the kernel
+// has to leave (timeout, or some rank's gradient profile is invalid).
+__device__ bool peer_entry(const PeerArgs& a) {
+  if (blockIdx.x == 0 && static_cast<int>(threadIdx.x) < a.usage_words) {
+    for (int s = 0; s < a.world; ++s) a.flags[s][usage_offset(a.rank) + threadIdx.x] = a.usage[threadIdx.x];
+  }
+  const int r = peer_barrier(a, 0, kErrEntryBarrier, a.invalid ? kInvalidBit : 0u);
+  if (r == 0) return false;
+  if (r == 2) {
+    if (threadIdx.x == 0) atomicCAS(a.status, 0, kErrInvalidProfile);
+    return false;
+  }
+  if (blockIdx.x == 0 && static_cast<int>(threadIdx.x) < a.usage_words) {
+    uint32_t u = 0;
+    for (int s = 0; s < a.world; ++s) u |= a.flags[a.rank][usage_offset(s) + threadIdx.x];
+    a.flags[a.rank][usage_offset(kMaxRanks) + threadIdx.x] = u;
+  }
+  return true;
+}
+
+// Publishes "this CTA saw a non-finite reduced gradient" to every rank, meets the peers and
+// returns whether CTA `blockIdx.x` of any rank did (-1 after a timeout).  Every CTA that learns
+// of a non-finite value raises the host-visible flag itself: CTA b only sees the words written by
+// CTA b of the other ranks before its barrier, so the union over a rank's CTAs is what makes the
+// host flag complete and identical on every rank.
+__device__ int exchange_found_inf(const PeerArgs& a, bool bad) {
+  const int cta_bad = __syncthreads_or(bad ? 1 : 0);
+  if (cta_bad && threadIdx.x < a.world) *inf_word(a.flags[threadIdx.x]) = a.epoch;  // tell every rank
+  if (!peer_barrier(a, 1, kErrMidBarrier)) return -1;
+  const bool any_inf = ld_acquire_sys(inf_word(a.flags[a.rank])) == a.epoch;
+  if (any_inf && threadIdx.x == 0) atomicExch(a.found_inf, 1);
+  return any_inf ? 1 : 0;
 }
 
 __device__ __forceinline__ float decay_for(const PeerArgs& a, long long e) {
@@ -195,9 +260,9 @@ __device__ __forceinline__ bool reduce_range(const PeerArgs& a, long long lo, lo
   constexpr int VEC = Pack<GT>::N;
   constexpr int R = Unroll<W>::kRanks, U = Unroll<W>::kVectors;
   const int world = W ? W : a.world;
-  const long long stride = static_cast<long long>(gridDim.x) * kPeerThreads;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   bool bad = false;
-  for (long long v0 = static_cast<long long>(blockIdx.x) * kPeerThreads + threadIdx.x; v0 < nvec; v0 += stride * U) {
+  for (long long v0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v0 < nvec; v0 += stride * U) {
     Pack<GT> in[U][R];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -236,11 +301,11 @@ template <class GT>
 __device__ __forceinline__ void update_from_bucket(const PeerArgs& a) {
   constexpr int VEC = Pack<GT>::N;
   const GT* red = static_cast<const GT*>(a.grads[a.rank]);
-  const long long stride = static_cast<long long>(gridDim.x) * kPeerThreads;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (int s = 0; s < a.world; ++s) {
     const long long lo = min(a.n, static_cast<long long>(s) * a.per), hi = min(a.n, lo + a.per);
     const long long nvec = (hi - lo) / VEC;
-    for (long long vi = static_cast<long long>(blockIdx.x) * kPeerThreads + threadIdx.x; vi < nvec; vi += stride) {
+    for (long long vi = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; vi < nvec; vi += stride) {
       const long long e = lo + vi * VEC;
       const Pack<GT> in = load_pack(red + e);
       float g[VEC];
@@ -256,10 +321,9 @@ __global__ void __launch_bounds__(kPeerThreads) peer_reduce_kernel(PeerArgs a) {
   constexpr int VEC = Pack<GT>::N;  // 16 bytes of gradients per access
   constexpr int R = Unroll<W>::kRanks;
   const int world = W ? W : a.world;
-  __shared__ int s_bad;
-  if (threadIdx.x == 0) s_bad = 0;
-  const int G = gridDim.x;
-  if (!peer_barrier(a, 0, kErrEntryBarrier)) return;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long first = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (!peer_entry(a)) return;
 
   bool bad = false;
   if (a.oneshot) {
@@ -282,21 +346,14 @@ __global__ void __launch_bounds__(kPeerThreads) peer_reduce_kernel(PeerArgs a) {
         if (s < world) store_pack(const_cast<GT*>(static_cast<const GT*>(a.grads[s])) + e, out);
     });
   }
-  if (bad) atomicExch(&s_bad, 1);
-  __syncthreads();
-  if (s_bad && threadIdx.x < a.world) *inf_word(a.flags[threadIdx.x]) = a.epoch;  // tell every rank
-
-  if (!peer_barrier(a, 1, kErrMidBarrier)) return;
-  const bool any_inf = ld_acquire_sys(inf_word(a.flags[a.rank])) == a.epoch;
-  if (any_inf && threadIdx.x == 0 && blockIdx.x == 0) atomicExch(a.found_inf, 1);
+  if (exchange_found_inf(a, bad) < 0) return;
 
   if (a.oneshot && a.mode == kModeAverage) {
     // The barrier above doubles as "every peer has finished reading this rank's bucket", so
     // the locally staged averages can now overwrite it.
     const long long nvec = a.n / VEC;
     GT* mine = const_cast<GT*>(static_cast<const GT*>(a.grads[a.rank]));
-    for (long long vi = static_cast<long long>(blockIdx.x) * kPeerThreads + threadIdx.x; vi < nvec;
-         vi += static_cast<long long>(G) * kPeerThreads) {
+    for (long long vi = first; vi < nvec; vi += stride) {
       Pack<GT> out;
 #pragma unroll
       for (int k = 0; k < VEC; ++k) out.v[k] = from_f<GT>(a.staging[a.rank][vi * VEC + k]);
@@ -305,12 +362,14 @@ __global__ void __launch_bounds__(kPeerThreads) peer_reduce_kernel(PeerArgs a) {
     return;
   }
 
-  if (a.mode != kModeAverage && !any_inf) {
+  // Fused optimizer: applied to whatever was reduced, like an optimizer step that follows an
+  // all-reduce without a loss scaler.  A step that must be skipped on overflow (GradScaler) runs
+  // in average mode and applies the update after the host has read the verdict.
+  if (a.mode != kModeAverage) {
     const float* red = a.staging[a.rank];
     if (a.oneshot) {
       const long long nvec = a.n / VEC;
-      for (long long vi = static_cast<long long>(blockIdx.x) * kPeerThreads + threadIdx.x; vi < nvec;
-           vi += static_cast<long long>(G) * kPeerThreads) {
+      for (long long vi = first; vi < nvec; vi += stride) {
         float g[VEC];
 #pragma unroll
         for (int k = 0; k < VEC; k += 4) *reinterpret_cast<float4*>(g + k) = *reinterpret_cast<const float4*>(red + vi * VEC + k);
@@ -356,16 +415,14 @@ template <class GT>
 __global__ void __launch_bounds__(kPeerThreads) nvls_reduce_kernel(PeerArgs a) {
   constexpr int VEC = Pack<GT>::N;
   constexpr int U = 4;  // vectors in flight per thread
-  __shared__ int s_bad;
-  if (threadIdx.x == 0) s_bad = 0;
-  if (!peer_barrier(a, 0, kErrEntryBarrier)) return;
+  if (!peer_entry(a)) return;
 
   const long long lo = min(a.n, static_cast<long long>(a.rank) * a.per), hi = min(a.n, lo + a.per);
   const long long nvec = (hi - lo) / VEC;
-  const long long stride = static_cast<long long>(gridDim.x) * kPeerThreads;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   GT* mc = static_cast<GT*>(a.mc_grads);
   bool bad = false;
-  for (long long v0 = static_cast<long long>(blockIdx.x) * kPeerThreads + threadIdx.x; v0 < nvec; v0 += stride * U) {
+  for (long long v0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v0 < nvec; v0 += stride * U) {
     uint32_t raw[U][4];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -388,15 +445,8 @@ __global__ void __launch_bounds__(kPeerThreads) nvls_reduce_kernel(PeerArgs a) {
       }
     }
   }
-  if (bad) atomicExch(&s_bad, 1);
-  __syncthreads();
-  if (s_bad && threadIdx.x < a.world) *inf_word(a.flags[threadIdx.x]) = a.epoch;  // tell every rank
-
-  if (!peer_barrier(a, 1, kErrMidBarrier)) return;
-  const bool any_inf = ld_acquire_sys(inf_word(a.flags[a.rank])) == a.epoch;
-  if (any_inf && threadIdx.x == 0 && blockIdx.x == 0) atomicExch(a.found_inf, 1);
-
-  if (a.mode != kModeAverage && !any_inf) update_from_bucket<GT>(a);
+  if (exchange_found_inf(a, bad) < 0) return;
+  if (a.mode != kModeAverage) update_from_bucket<GT>(a);
 }
 
 __global__ void peer_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long n16) {
@@ -501,12 +551,19 @@ void bind_peer(py::module_& m) {
                            const std::vector<uintptr_t>& flags, long long n, const std::string& dtype, uint32_t epoch, double scale,
                            const std::string& mode, bool oneshot, const py::object& master, const py::object& mom, const py::object& var,
                            const py::object& model, const py::dict& hyper, Tensor& status, Tensor& found_inf, int ctas, int stream_kind,
-                           uintptr_t mc_grads) {
+                           uintptr_t mc_grads, int threads, double wait_ms, bool invalid, const std::vector<uint32_t>& usage) {
     if (world < 1 || world > kMaxRanks) throw std::invalid_argument("peer reduce supports 1..8 ranks");
     if (static_cast<int>(grads.size()) != world || static_cast<int>(staging.size()) != world || static_cast<int>(flags.size()) != world)
       throw std::invalid_argument("peer reduce: one gradient, staging and flag pointer per rank is required");
     if (n % 8 != 0) throw std::invalid_argument("peer reduce: bucket length must be a multiple of 8 elements");
+    if (threads < 32 || threads > kPeerThreads || threads % 32 != 0) throw std::invalid_argument("peer reduce: block size must be a multiple of 32 in [32, 512]");
+    if (usage.size() > static_cast<size_t>(kUsageWords)) throw std::invalid_argument("peer reduce: at most 2048 parameters per bucket");
+    if (!(wait_ms > 0.0)) throw std::invalid_argument("peer reduce: the wait budget must be positive");
     PeerArgs a{};
+    a.wait_ns = static_cast<long long>(wait_ms * 1e6);
+    a.invalid = invalid ? 1 : 0;
+    a.usage_words = static_cast<int>(usage.size());
+    for (size_t i = 0; i < usage.size(); ++i) a.usage[i] = usage[i];
     a.rank = rank; a.world = world; a.oneshot = oneshot ? 1 : 0;
     a.mode = mode == "adam" ? kModeAdam : (mode == "sgd" ? kModeSgd : kModeAverage);
     if (a.mode == kModeAverage && mode != "average") throw std::invalid_argument("peer reduce: mode must be average, adam or sgd");
@@ -553,21 +610,21 @@ void bind_peer(py::module_& m) {
     // few CTAs so the flag exchange stays cheap.
     int grid = ctas > 0 ? ctas : std::max(8, std::min(kMaxCtas, (n >= (8ll << 20)) ? sms : sms / 2));
     const long long vecs = n / (gd == DType::F32 ? 4 : 8);
-    grid = static_cast<int>(std::max<long long>(1, std::min<long long>(grid, (vecs / world + kPeerThreads - 1) / kPeerThreads)));
+    grid = static_cast<int>(std::max<long long>(1, std::min<long long>(grid, (vecs / world + threads - 1) / threads)));
     if (grid > kMaxCtas) grid = kMaxCtas;
     cudaStream_t st = pick_stream(device, stream_kind);
 #define OB_PEER_LAUNCH(GT)                                                                    \
   do {                                                                                        \
-    if (world == 2) peer_reduce_kernel<GT, 2><<<grid, kPeerThreads, 0, st>>>(a);              \
-    else if (world == 4) peer_reduce_kernel<GT, 4><<<grid, kPeerThreads, 0, st>>>(a);         \
-    else if (world == 8) peer_reduce_kernel<GT, 8><<<grid, kPeerThreads, 0, st>>>(a);         \
-    else peer_reduce_kernel<GT, 0><<<grid, kPeerThreads, 0, st>>>(a);                         \
+    if (world == 2) peer_reduce_kernel<GT, 2><<<grid, threads, 0, st>>>(a);              \
+    else if (world == 4) peer_reduce_kernel<GT, 4><<<grid, threads, 0, st>>>(a);         \
+    else if (world == 8) peer_reduce_kernel<GT, 8><<<grid, threads, 0, st>>>(a);         \
+    else peer_reduce_kernel<GT, 0><<<grid, threads, 0, st>>>(a);                         \
   } while (0)
     if (mc_grads != 0) {
       // In-switch reduction and broadcast through the multicast mapping of the bucket.
-      if (gd == DType::F32) nvls_reduce_kernel<float><<<grid, kPeerThreads, 0, st>>>(a);
-      else if (gd == DType::BF16) nvls_reduce_kernel<__nv_bfloat16><<<grid, kPeerThreads, 0, st>>>(a);
-      else if (gd == DType::F16) nvls_reduce_kernel<__half><<<grid, kPeerThreads, 0, st>>>(a);
+      if (gd == DType::F32) nvls_reduce_kernel<float><<<grid, threads, 0, st>>>(a);
+      else if (gd == DType::BF16) nvls_reduce_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>(a);
+      else if (gd == DType::F16) nvls_reduce_kernel<__half><<<grid, threads, 0, st>>>(a);
       else throw std::invalid_argument("peer reduce: gradients must be float32, float16 or bfloat16");
     } else if (gd == DType::F32) OB_PEER_LAUNCH(float);
     else if (gd == DType::BF16) OB_PEER_LAUNCH(__nv_bfloat16);
@@ -579,7 +636,12 @@ void bind_peer(py::module_& m) {
   }, py::arg("rank"), py::arg("world"), py::arg("device"), py::arg("grads"), py::arg("staging"), py::arg("flags"), py::arg("n"),
      py::arg("dtype"), py::arg("epoch"), py::arg("scale"), py::arg("mode"), py::arg("oneshot"), py::arg("master") = py::none(),
      py::arg("m") = py::none(), py::arg("v") = py::none(), py::arg("model") = py::none(), py::arg("hyper") = py::dict(),
-     py::arg("status"), py::arg("found_inf"), py::arg("ctas") = 0, py::arg("stream_kind") = 1, py::arg("mc_grads") = 0);
+     py::arg("status"), py::arg("found_inf"), py::arg("ctas") = 0, py::arg("stream_kind") = 1, py::arg("mc_grads") = 0,
+     py::arg("threads") = kPeerThreads, py::arg("wait_ms") = 2000.0, py::arg("invalid") = false,
+     py::arg("usage") = std::vector<uint32_t>());
+  m.attr("_PEER_USAGE_WORD_OFFSET") = py::int_(usage_offset(kMaxRanks));
+  m.attr("_PEER_USAGE_WORDS") = py::int_(kUsageWords);
+  m.attr("_PEER_ERR_INVALID_PROFILE") = py::int_(static_cast<int>(kErrInvalidProfile));
 }
 
 }  // namespace ob

@@ -116,9 +116,10 @@ struct AdamHyper {
 };
 // Fused FP32-master Adam over one flat range.  `model` may be undefined or a low-precision
 // copy to refresh; `grad` may be F32/F16/BF16.
-void adam_step_(Tensor& master, Tensor& m, Tensor& v, const Tensor& grad, Tensor& model, const AdamHyper& h);
+void adam_step_(Tensor& master, Tensor& m, Tensor& v, const Tensor& grad, Tensor& model, const AdamHyper& h,
+                int stream_kind = 0, int threads = 0);
 void sgd_step_(Tensor& master, const Tensor& grad, Tensor& model, double lr, double weight_decay,
-               double grad_scale);
+               double grad_scale, int stream_kind = 0, int threads = 0);
 
 // ---- dispatch glue
 void run_kernel(OperatorId op, Device dev, DType dtype, OpCall& call, uint8_t layout = kContiguous);

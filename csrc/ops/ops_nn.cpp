@@ -789,7 +789,17 @@ void amp_copy_master_to_model_(Tensor& model, const Tensor& master) {
   model.bump_version();
 }
 
-void adam_step_(Tensor& master, Tensor& m, Tensor& v, const Tensor& grad, Tensor& model, const AdamHyper& h) {
+// `stream_kind` 1 queues the update on the device's second (communication) stream; `threads` > 0
+// sets the block size (small blocks share an SM with a persistent GEMM CTA of a backward pass).
+static void place_update(OpCall& c, const Tensor& master, int stream_kind, int threads) {
+  if (threads != 0 && (threads < 32 || threads > 1024 || threads % 32 != 0))
+    throw std::invalid_argument("optimizer step: block size must be a multiple of 32 in [32, 1024]");
+  c.i[0] = threads;
+  if (stream_kind == 1 && master.device().is_cuda()) c.stream = Runtime::instance().cuda(master.device().index).comm_stream();
+}
+
+void adam_step_(Tensor& master, Tensor& m, Tensor& v, const Tensor& grad, Tensor& model, const AdamHyper& h, int stream_kind,
+                int threads) {
   if (!master.is_contiguous() || !m.is_contiguous() || !v.is_contiguous() || !grad.is_contiguous())
     throw std::invalid_argument("adam_step: tensors must be contiguous");
   if (m.numel() != master.numel() || v.numel() != master.numel() || grad.numel() != master.numel())
@@ -800,12 +810,14 @@ void adam_step_(Tensor& master, Tensor& m, Tensor& v, const Tensor& grad, Tensor
   if (model.defined()) c.in[4] = model;
   c.f[0] = h.lr; c.f[1] = h.beta1; c.f[2] = h.beta2; c.f[3] = h.eps; c.f[4] = h.weight_decay;
   c.f[5] = h.bias_c1; c.f[6] = h.bias_c2; c.f[7] = h.grad_scale;
+  place_update(c, master, stream_kind, threads);
   run_kernel(OperatorId::AdamStep, master.device(), master.dtype(), c);
   master.bump_version(); m.bump_version(); v.bump_version();
   if (model.defined()) model.bump_version();
 }
 
-void sgd_step_(Tensor& master, const Tensor& grad, Tensor& model, double lr, double wd, double grad_scale) {
+void sgd_step_(Tensor& master, const Tensor& grad, Tensor& model, double lr, double wd, double grad_scale, int stream_kind,
+               int threads) {
   if (!master.is_contiguous() || !grad.is_contiguous()) throw std::invalid_argument("sgd_step: tensors must be contiguous");
   if (grad.numel() != master.numel()) throw std::invalid_argument("sgd_step: element counts differ");
   if (master.numel() == 0) return;
@@ -813,6 +825,7 @@ void sgd_step_(Tensor& master, const Tensor& grad, Tensor& model, double lr, dou
   c.in[0] = master; c.in[1] = grad;
   if (model.defined()) c.in[2] = model;
   c.f[0] = lr; c.f[1] = wd; c.f[2] = grad_scale;
+  place_update(c, master, stream_kind, threads);
   run_kernel(OperatorId::SgdStep, master.device(), master.dtype(), c);
   master.bump_version();
   if (model.defined()) model.bump_version();

@@ -15,7 +15,38 @@ except ImportError as exc:  # pragma: no cover - build problem, never a silent f
         "orthon_b200._C is not built; run `python build.py` at the repository root"
     ) from exc
 
-from ._C import (  # noqa: F401
+
+
+def _check_build_matches_sources():
+    """A checkout carries the native sources next to the package.  If they differ from the ones
+    the extension was built from, Python code may call bindings that do not exist yet (or exist
+    with another signature): refuse to import instead of failing somewhere inside a run."""
+    import hashlib
+    import os
+    csrc = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc")
+    built = getattr(_C, "_source_digest", None)
+    if built is None or not os.path.isdir(csrc) or os.environ.get("ORTHON_SKIP_BUILD_CHECK") == "1":
+        return
+    h = hashlib.sha256()
+    paths = []
+    for root, _, files in os.walk(csrc):
+        for name in files:
+            if name.endswith((".cpp", ".cu", ".h", ".hpp", ".cuh")):
+                full = os.path.join(root, name)
+                paths.append((os.path.relpath(full, csrc).replace(os.sep, "/"), full))
+    for rel, full in sorted(paths):
+        h.update(rel.encode())
+        h.update(b"\0")
+        with open(full, "rb") as f:
+            h.update(f.read())
+    if h.hexdigest() != built:
+        raise ImportError("orthon_b200._C was built from other sources than the ones under csrc/ "
+                          "(stale extension); run `python build.py` at the repository root")
+
+
+_check_build_matches_sources()
+
+from ._C import (  # noqa: F401,E402
     DType, DeviceType, Device, Tensor, UnsupportedOperation,
     isfinite_all, empty, zeros, ones, full, from_numpy, fill_,
     add, mul, sub, div, reshape, transpose, contiguous,

@@ -54,10 +54,21 @@ def _check_sync(p, master):
 
 class MixedPrecisionOptimizer:
     def __init__(self, model, optimizer_cls, fused="auto", **optimizer_kwargs):
-        """`fused` only matters when `model` is a DDP wrapper whose reducer keeps gradients in
-        peer-memory buckets: "update" applies the optimizer inside the reduction kernel while
-        backward is still running (no GradScaler), "reduce"/"auto" averages in the kernel and
-        applies one fused update per bucket in `step()`, False keeps the per-parameter path."""
+        """`fused` selects how the step is scheduled when the gradients can live in flat buckets
+        (one CUDA device, one dtype; across ranks: the peer-memory transport):
+
+        * "reduce" / "auto": gradients accumulate locally over any number of backward passes;
+          `step()` averages every bucket with one fused kernel and applies one fused update per
+          bucket.  Works with a GradScaler.
+        * "overlap": each bucket is averaged from the autograd hooks while backward is still
+          running; `step()` applies the update.  Works with a GradScaler.  Exactly one backward
+          per `zero_grad()`: a second one raises.
+        * "update": the optimizer update itself runs inside the reduction kernel during backward
+          (no GradScaler: there is no point at which a step could be skipped).  One backward per
+          `zero_grad()`, as above.
+        * False keeps the per-parameter path."""
+        if fused not in ("auto", "reduce", "overlap", "update", False):
+            raise ValueError("fused must be 'auto', 'reduce', 'overlap', 'update' or False")
         check = getattr(model, "_validate_master_gradient_sync", None)
         if check is not None:
             check()
@@ -116,6 +127,9 @@ class MixedPrecisionOptimizer:
         by_master = {id(s.parameter): s.master for s in self._states}
         reducer.set_decay_segments(lambda p: self._inner._weight_decay if self._inner._should_decay(by_master[id(p)]) else 0.0)
         self._peer = reducer
+        if fused in ("overlap", "update"):
+            reducer.overlap = True          # launch from the hooks, during backward
+            reducer.single_backward = True  # nothing synchronises at the end of backward: guard the cycle
         if fused == "update":
             reducer.mode = self._kind
             reducer.hyper = self._fused_hyper
@@ -229,7 +243,8 @@ class MixedPrecisionOptimizer:
     def _unscale_and_check(self, inv_scale):
         if self._peer is not None:
             if self._peer.mode != "average":
-                raise RuntimeError("GradScaler needs MixedPrecisionOptimizer(fused='reduce'): the update cannot run inside backward")
+                raise RuntimeError("GradScaler needs MixedPrecisionOptimizer(fused='reduce') or fused='overlap': "
+                                   "an update that runs inside backward cannot be skipped")
             self._peer.synchronize()
             self._pending_inv_scale = float(inv_scale)
             return self._peer.found_inf()  # scaled, averaged gradients: same verdict on every rank

@@ -59,13 +59,21 @@ class PeerBackend(Backend):
         self._xseq = 0
         self._closed, self._failure = False, None
         self._dev = f"cuda:{self._device}"
-        self._status = _C._zeros_on([1], "int32", self._dev)
-        self._found_inf = _C._zeros_on([1], "int32", self._dev)
+        # Device words the kernels report into: [0] first error code of a bounded wait, [1] "a
+        # reduced gradient was non-finite", [2] the same for generic collectives (kept apart so that
+        # an overflow in an unrelated all_reduce never makes a GradScaler skip a step).
+        self._words = _C._zeros_on([4], "int32", self._dev)
+        self._status = _C._view_flat(self._words, 0, [1])
+        self._found_inf = _C._view_flat(self._words, 1, [1])
+        self._coll_inf = _C._view_flat(self._words, 2, [1])
+        self._host_words = _C._pinned_empty([4], "int32")
+        self._host_words._copy_data_(_C.zeros([4], "int32"))
+        self._poll_event = None
+        self.wait_ms = float(os.environ.get("ORTHON_PEER_WAIT_MS", 2000.0))  # budget of every device-side flag wait
         self._epoch = 0
         # One symmetric region: [staging grads | float32 staging | flags].
         self._stage = self.allocate_symmetric(STAGING_BYTES * 2 + _C._PEER_FLAG_BYTES)
         self._nccl = None
-        self._vmm = None  # decided collectively on first use
         self._vmm = None  # decided collectively on first use
 
     rank = property(lambda self: self._rank)
@@ -231,12 +239,42 @@ class PeerBackend(Backend):
         self._epoch += 1
         return self._epoch
 
+    INVALID_PROFILE = ("DDP gradient synchronization rejected an invalid gradient profile "
+                       "on one or more ranks (dtype, shape, device, or backend support)")
+
+    def _judge(self, code):
+        """Turns a status code into the exception it stands for.  A wait that ran out poisons
+        the group (the ranks are no longer in step); a rejected gradient profile does not: every
+        rank left that bucket untouched, in step."""
+        if not code:
+            return
+        self._status.fill_(0.0)
+        if code == _C._PEER_ERR_INVALID_PROFILE:
+            raise RuntimeError(self.INVALID_PROFILE)
+        self._failure = f"peer kernel wait timed out (code {code})"
+        raise _TransportFailure("p2p backend failed: " + self._failure)
+
+    def read_words(self):
+        """One device read (synchronises the compute stream): (status code, gradient found-inf)."""
+        status, found, _, _ = self._words.tolist()
+        return int(status), bool(found)
+
     def check_status(self):
         """Reads the device error word (synchronises); a timeout poisons the group."""
-        code = self._status.tolist()[0]
-        if code:
-            self._failure = f"peer kernel wait timed out (code {code})"
-            raise _TransportFailure("p2p backend failed: " + self._failure)
+        self._open()
+        self._judge(self.read_words()[0])
+
+    def poll_status(self):
+        """Checks the error word without waiting for the device: looks at the copy queued by the
+        previous call if it has landed, then queues a fresh copy behind the work issued so far.
+        A failure therefore surfaces one call late, on steps that never synchronise."""
+        self._open()
+        if self._poll_event is not None and self._poll_event.ready():
+            self._poll_event = None
+            self._judge(int(self._host_words.tolist()[0]))
+        if self._poll_event is None:
+            _C._copy_d2h_async(self._host_words, self._words)
+            self._poll_event = _C.CudaEvent.record(self._device)
 
     def status_tensors(self):
         return self._status, self._found_inf
@@ -268,8 +306,8 @@ class PeerBackend(Backend):
         staging = [p + STAGING_BYTES for p in self._stage.ptrs]
         flags = [p + 2 * STAGING_BYTES for p in self._stage.ptrs]
         _C._peer_reduce(self._rank, self._world, self._device, grads, staging, flags, padded, dtype, self.next_epoch(),
-                        1.0, "average", padded * esz <= (1 << 20), status=self._status, found_inf=self._found_inf,
-                        stream_kind=0)
+                        1.0, "average", padded * esz <= (1 << 20), status=self._status, found_inf=self._coll_inf,
+                        stream_kind=0, wait_ms=self.wait_ms)
         flat._copy_flat_range_from(off, stage, 0, n)
 
     def _fallback(self):
@@ -328,6 +366,9 @@ class PeerBackend(Backend):
         self._closed = True
         try:
             _C.cuda_synchronize()
+            code = self.read_words()[0]
+            if code and self._failure is None:
+                self._failure = f"peer kernel reported code {code} before shutdown"
         except RuntimeError:
             pass
         if self._nccl is not None:

@@ -1,9 +1,21 @@
 """DistributedDataParallel: replicated parameters, averaged gradients.
 
-Construction captures the active group, takes the unique trainable parameters in sorted-name
-order, broadcasts them from `src`, and registers a post-accumulate hook per parameter (marks
-it used) plus one keyed backward finalizer (runs the reducer once per backward, after every
-leaf gradient is committed).  Buffers are not broadcast.
+The wrapper owns one gradient synchroniser for the trainable parameters of a module (unique
+owners, sorted by name so every rank agrees on the order) and wires it into autograd with two
+callbacks: a per-parameter post-accumulate hook that reports "this parameter has its gradient"
+and one keyed backward finalizer that runs the synchroniser once per backward pass.
+
+Which synchroniser is chosen follows from where the parameters live:
+
+* parameters of one dtype on one CUDA device under the peer-memory transport get the
+  PeerReducer: their gradients live inside symmetric buckets and one fused kernel per bucket
+  averages them over NVLink.  `overlap_grad_sync=True` launches a bucket from the hooks while
+  backward is still running; otherwise all buckets are launched by the finalizer (or by
+  `all_reduce_gradients()` when `sync_grads=False`), with the participation consensus carried in
+  the kernel's entry barrier;
+* everything else gets the generic Reducer (any backend, control all-reduce, packing).
+
+Parameters are broadcast from `src` at construction; buffers are not.
 (reference project: python/orthon/distributed/ddp.py:7-119)"""
 import weakref
 
@@ -11,103 +23,128 @@ from ..distributed import _state
 from .peer_reducer import PeerReducer
 from .reducer import Reducer
 
+_MODULE_API = ("named_parameters", "state_dict", "load_state_dict")
+
+
+def _check_options(sync_grads, bucket_size_mb, overlap_grad_sync):
+    if overlap_grad_sync:
+        if not sync_grads:
+            raise ValueError("overlap_grad_sync=True requires sync_grads=True")
+        if bucket_size_mb is None:
+            raise ValueError("overlap_grad_sync=True requires bucket_size_mb to be provided")
+    if bucket_size_mb is not None and int(float(bucket_size_mb) * 1024 * 1024) < 1:
+        raise ValueError("bucket_size_mb must be positive when provided")
+
+
+def _trainable_owners(module):
+    """(name, parameter) pairs: each trainable Python owner once, in sorted-name order."""
+    if hasattr(module, "named_parameters"):
+        pairs = sorted(module.named_parameters(), key=lambda pair: pair[0])
+    else:
+        pairs = [(str(index), p) for index, p in enumerate(module.parameters())]
+        pairs.sort(key=lambda pair: pair[0])
+    unique = {}
+    for name, p in pairs:
+        if p.requires_grad:
+            unique.setdefault(id(p), (name, p))
+    return list(unique.values())
+
+
+class _AutogradLink:
+    """Callbacks handed to autograd.  They hold the reducer weakly: a wrapper that was dropped
+    leaves hooks behind on the parameters, and those must turn into no-ops."""
+
+    def __init__(self, reducer):
+        self._reducer = weakref.ref(reducer)
+        self.key = id(reducer)
+
+    def finalize(self):
+        reducer = self._reducer()
+        if reducer is not None:
+            reducer.synchronize()
+
+    def marker(self, parameter):
+        owner, ref = id(parameter), self._reducer
+
+        def mark():
+            reducer = ref()
+            if reducer is not None:
+                reducer.mark(owner)
+
+        return mark
+
 
 class DistributedDataParallel:
     def __init__(self, module, src=0, sync_grads=True, bucket_size_mb=None, overlap_grad_sync=False):
+        _check_options(sync_grads, bucket_size_mb, overlap_grad_sync)
         self.module = module
         self._sync_grads = bool(sync_grads)
-        if overlap_grad_sync and not sync_grads:
-            raise ValueError("overlap_grad_sync=True requires sync_grads=True")
-        if overlap_grad_sync and bucket_size_mb is None:
-            raise ValueError("overlap_grad_sync=True requires bucket_size_mb to be provided")
-        if bucket_size_mb is not None and int(float(bucket_size_mb) * 1024 * 1024) < 1:
-            raise ValueError("bucket_size_mb must be positive when provided")
         group = _state.get_active()
-        if hasattr(module, "named_parameters"):
-            named = list(module.named_parameters())
-        else:
-            named = [(str(i), p) for i, p in enumerate(module.parameters())]
-        owners, seen = [], set()
-        for name, p in sorted(named, key=lambda item: item[0]):
-            if id(p) not in seen and p.requires_grad:
-                seen.add(id(p))
-                owners.append((name, p))
-        for _, p in owners:
-            group.broadcast(p, src=src)
+        owners = _trainable_owners(module)
+        for _, parameter in owners:
+            group.broadcast(parameter, src=src)
         if PeerReducer.eligible(owners, group):
-            # Buckets become the gradient storage; reduction starts from the leaf hooks.
-            self._reducer = PeerReducer(owners, group, bucket_size_mb, overlap=True)
+            self._reducer = PeerReducer(owners, group, bucket_size_mb, overlap=bool(overlap_grad_sync))
         else:
             self._reducer = Reducer(owners, group, bucket_size_mb, bool(overlap_grad_sync))
-        ref = weakref.ref(self._reducer)
-
-        def finalize():
-            r = ref()
-            if r is not None:
-                r.synchronize()
-
-        self._finalizer, self._finalizer_key = finalize, id(self._reducer)
-        for _, p in owners:
-
-            def used(owner=id(p), ref=ref):
-                r = ref()
-                if r is not None:
-                    r.mark(owner)
-
-            p._register_post_accumulate_grad_hook(used)
+        self._link = _AutogradLink(self._reducer)
+        for _, parameter in owners:
+            parameter._register_post_accumulate_grad_hook(self._link.marker(parameter))
             if self._sync_grads:
-                p._register_backward_finalizer(self._finalizer_key, finalize)
+                parameter._register_backward_finalizer(self._link.key, self._link.finalize)
 
+    # The finalizer is also keyed on the outputs, so a backward pass that reaches no parameter
+    # of this rank still takes part in the synchronisation.
     def _attach_outputs(self, output):
         if not self._sync_grads:
             return
-        if isinstance(output, (tuple, list)):
-            for v in output:
-                self._attach_outputs(v)
-        elif isinstance(output, dict):
-            for v in output.values():
-                self._attach_outputs(v)
-        elif hasattr(output, "_register_backward_finalizer") and output.requires_grad:
-            output._register_backward_finalizer(self._finalizer_key, self._finalizer)
+        pending = [output]
+        while pending:
+            value = pending.pop()
+            if isinstance(value, dict):
+                pending.extend(value.values())
+            elif isinstance(value, (tuple, list)):
+                pending.extend(value)
+            elif hasattr(value, "_register_backward_finalizer") and value.requires_grad:
+                value._register_backward_finalizer(self._link.key, self._link.finalize)
 
     def __call__(self, *args, **kwargs):
         self._reducer.group.ensure_open()
-        out = self.module(*args, **kwargs)
-        self._attach_outputs(out)
-        return out
+        output = self.module(*args, **kwargs)
+        self._attach_outputs(output)
+        return output
 
-    def forward(self, *args, **kwargs):
-        return self(*args, **kwargs)
+    forward = __call__
 
+    # ------------------------------------------------------------ module API
     def parameters(self):
         return self.module.parameters()
 
-    def _delegate(self, name, *args, **kwargs):
-        if not hasattr(self.module, name):
-            raise AttributeError(f"{type(self.module).__name__} has no {name}()")
-        return getattr(self.module, name)(*args, **kwargs)
-
-    def named_parameters(self, *a, **k):
-        return self._delegate("named_parameters", *a, **k)
-
-    def state_dict(self, *a, **k):
-        return self._delegate("state_dict", *a, **k)
-
-    def load_state_dict(self, *a, **k):
-        return self._delegate("load_state_dict", *a, **k)
+    def __getattr__(self, name):
+        # Only reached for names the wrapper does not define itself.
+        if name in _MODULE_API:
+            module = self.__dict__.get("module")
+            if module is None or not hasattr(module, name):
+                raise AttributeError(f"{type(module).__name__} has no {name}()")
+            return getattr(module, name)
+        raise AttributeError(f"{type(self).__name__!r} object has no attribute {name!r}")
 
     def train(self):
-        return self.module.train() if hasattr(self.module, "train") else self
+        switch = getattr(self.module, "train", None)
+        return self if switch is None else switch()
 
     def eval(self):
-        return self.module.eval() if hasattr(self.module, "eval") else self
+        switch = getattr(self.module, "eval", None)
+        return self if switch is None else switch()
 
+    # ------------------------------------------------------- gradient control
     def zero_grad(self):
-        self._reducer.reset()
-        if hasattr(self.module, "zero_grad"):
-            return self.module.zero_grad()
-        for p in self.parameters():
-            p.zero_grad()
+        self._reducer.reset()  # raises while asynchronous reductions are outstanding
+        clear = getattr(self.module, "zero_grad", None)
+        if clear is not None:
+            return clear()
+        for parameter in self.parameters():
+            parameter.zero_grad()
 
     def all_reduce_gradients(self):
         self._reducer.synchronize()

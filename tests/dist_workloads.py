@@ -166,3 +166,233 @@ def nvls_reduce(rank, backend, dtype, n):
     expect = base * sum(r + 1 for r in range(ws)) / ws
     return {"nvls": out["nvls"].tolist(), "peer": out["peer"].tolist(), "expect": expect.tolist(),
             "master": master.tolist(), "found_inf": int(found.tolist()[0])}
+
+
+# ------------------------------------------------------------------ peer-path scenarios (GPU ranks)
+def _small_model(seed, dev, dtype="float32"):
+    import orthon_b200 as ob
+    ob.manual_seed(seed)
+    m = ob.nn.Sequential(ob.nn.Linear(6, 8), ob.nn.ReLU(), ob.nn.Linear(8, 3))
+    if dtype != "float32":
+        m.cast(dtype)
+    return m.to(dev) if dev != "cpu" else m
+
+
+def _flat_params(model):
+    return np.concatenate([p.numpy().astype(np.float32).reshape(-1) for p in model.parameters()])
+
+
+def accumulation_explicit_sync(rank, backend):
+    """Two backward passes, then one explicit synchronisation: the result is the average over
+    ranks of the locally accumulated sums (the wrapper was built with sync_grads=False)."""
+    import orthon_b200 as ob
+    import orthon_b200.distributed as dist
+    dev = _device(backend, rank)
+    model = _small_model(3, dev)
+    ddp = dist.DDP(model, sync_grads=False, bucket_size_mb=1)
+    rng = np.random.default_rng(50 + rank)
+    ddp.zero_grad()
+    for _ in range(2):
+        x = ob.from_numpy(rng.standard_normal((4, 6)).astype(np.float32)).to(dev)
+        y = ob.from_numpy(rng.integers(0, 3, 4).astype(np.int64)).to(dev)
+        ob.cross_entropy(ddp(x), y).backward()
+    local = [p.grad.numpy().copy() for p in model.parameters()]
+    ddp.all_reduce_gradients()
+    ddp.wait_for_gradient_sync()
+    synced = [p.grad.numpy().copy() for p in model.parameters()]
+    return [g.tolist() for g in local], [g.tolist() for g in synced], type(ddp._reducer).__name__
+
+
+def amp_accumulation(rank, backend, fused):
+    """AMP + GradScaler with two micro-batches per step.  'reduce' accumulates locally and
+    averages in step(); 'overlap' and 'update' reduce inside backward and must refuse the
+    second backward.  Returns the final masters, or the refusal text."""
+    import orthon_b200 as ob
+    import orthon_b200.distributed as dist
+    dev = _device(backend, rank)
+    model = _small_model(21, dev)
+    ddp = dist.DDP(model, sync_grads=False, bucket_size_mb=1)
+    opt = ob.amp.MixedPrecisionOptimizer(ddp, ob.optim.Adam, fused=fused, lr=1e-2)
+    scaler = ob.amp.GradScaler(init_scale=8.0, enabled=fused != "update")
+    refused = None
+    for step in range(2):
+        opt.zero_grad()
+        for micro in range(2):
+            rng = np.random.default_rng(1000 * step + 10 * micro + rank)
+            x = ob.from_numpy(rng.standard_normal((4, 6)).astype(np.float32)).to(dev)
+            y = ob.from_numpy(rng.integers(0, 3, 4).astype(np.int64)).to(dev)
+            try:
+                scaler.scale(ob.cross_entropy(ddp(x), y) * 0.5).backward()
+            except RuntimeError as exc:
+                refused = str(exc)
+                break
+        if refused:
+            break
+        scaler.step(opt)
+        scaler.update()
+    ob.cuda_synchronize()
+    dist.barrier()
+    return refused, _flat_params(model).tolist()
+
+
+def amp_accumulation_reference(world):
+    """The same two steps of two micro-batches in one process (gradients averaged by hand)."""
+    import orthon_b200 as ob
+    model = _small_model(21, "cpu")
+    params = list(model.parameters())
+    opt = ob.optim.Adam(params, lr=1e-2)
+    for step in range(2):
+        total = [np.zeros(tuple(p.shape), dtype=np.float32) for p in params]
+        for rank in range(world):
+            for micro in range(2):
+                rng = np.random.default_rng(1000 * step + 10 * micro + rank)
+                x = ob.from_numpy(rng.standard_normal((4, 6)).astype(np.float32))
+                y = [int(v) for v in rng.integers(0, 3, 4)]
+                for p in params:
+                    p.zero_grad()
+                (ob.cross_entropy(model(x), y) * 0.5).backward()
+                total = [t + p.grad.numpy() for t, p in zip(total, params)]
+        for p, g in zip(params, total):
+            p.set_grad(ob.from_numpy((g / world).astype(np.float32)))
+        opt.step()
+    return _flat_params(model)
+
+
+def amp_inf_on_last_rank(rank, backend, fused):
+    """The last rank overflows in step 1: every rank must skip that update, halve the scale and
+    stay bit-identical."""
+    import orthon_b200 as ob
+    import orthon_b200.distributed as dist
+    dev = _device(backend, rank)
+    ws = dist.get_world_size()
+    model = _small_model(7, dev)
+    ddp = dist.DDP(model, sync_grads=False, bucket_size_mb=1)
+    opt = ob.amp.MixedPrecisionOptimizer(ddp, ob.optim.Adam, fused=fused, lr=1e-2)
+    scaler = ob.amp.GradScaler(init_scale=64.0)
+    rng = np.random.default_rng(90 + rank)
+    trace = []
+    for step in range(3):
+        x = ob.from_numpy(rng.standard_normal((4, 6)).astype(np.float32)).to(dev)
+        y = ob.from_numpy(rng.integers(0, 3, 4).astype(np.int64)).to(dev)
+        opt.zero_grad()
+        loss = ob.cross_entropy(ddp(x), y)
+        if step == 1 and rank == ws - 1:
+            loss = loss * float("inf")
+        before = _flat_params(model)
+        scaler.scale(loss).backward()
+        scaler.step(opt)
+        skipped = scaler.found_inf
+        scaler.update()
+        trace.append((bool(skipped), float(scaler.scale_factor), bool(np.array_equal(before, _flat_params(model)))))
+    return trace, _flat_params(model).tolist()
+
+
+def found_inf_in_a_late_block(rank, backend, n):
+    """Kernel level: one non-finite value near the end of the last rank's bucket (an element that
+    a high-numbered thread block reduces) must raise the found-inf word on every rank."""
+    import orthon_b200.distributed as dist
+    from orthon_b200 import _C
+    from orthon_b200.distributed import _state
+    be = _state.get_active().backend
+    ws = dist.get_world_size()
+    dev = f"cuda:{rank}"
+    flag_bytes = (_C._PEER_FLAG_BYTES + 255) & ~255
+    region = be.allocate_symmetric(n * 4 + n * 4 + flag_bytes)
+    grads, staging = list(region.ptrs), [p + n * 4 for p in region.ptrs]
+    flags = [p + 8 * n for p in region.ptrs]
+    grad_t = _C._tensor_from_ptr(region.local, [n], "float32", rank)
+    status, found = be.status_tensors()
+    out = {}
+    for name, poison in (("clean", False), ("poisoned", True)):
+        host = np.full([n], float(rank + 1), dtype=np.float32)
+        if poison and rank == ws - 1:
+            host[n - 3] = np.inf
+        grad_t._copy_flat_range_from(0, _C.from_numpy(host).to(dev), 0, n)
+        _C.cuda_synchronize()
+        dist.barrier()
+        blocks = _C._peer_reduce(rank, ws, rank, grads, staging, flags, n, "float32", be.next_epoch(), 1.0 / ws, "average", False,
+                                 status=status, found_inf=found, stream_kind=0)
+        _C.cuda_synchronize()
+        code, hit = be.read_words()
+        out[name] = (int(code), bool(hit), int(blocks), float(grad_t.tolist()[0]))
+        found.fill_(0.0)
+        dist.barrier()
+    return out
+
+
+def participation(rank, backend, case):
+    """Rank-divergent participation on the default (non-overlapped) schedule.
+    case 'partial': only rank 0 uses head b -> idle ranks contribute zeros, all get the average.
+    case 'unused' : nobody uses head b -> its gradient stays None everywhere.
+    case 'invalid': rank 0 assigns a gradient of the wrong shape -> every rank is told."""
+    import orthon_b200 as ob
+    import orthon_b200.distributed as dist
+    from orthon_b200 import nn
+    dev = _device(backend, rank)
+
+    class TwoHeads(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a = nn.Linear(4, 3)
+            self.b = nn.Linear(4, 3)
+
+        def forward(self, x, use_b):
+            y = self.a(x)
+            return y + self.b(x) if use_b else y
+
+    ob.manual_seed(9)
+    model = TwoHeads()
+    if dev != "cpu":
+        model.to(dev)
+    ddp = dist.DDP(model, sync_grads=False, bucket_size_mb=1)
+    x = ob.from_numpy(np.random.default_rng(3).standard_normal((2, 4)).astype(np.float32))
+    x = x if dev == "cpu" else x.to(dev)
+    ddp.zero_grad()
+    ddp(x, case == "partial" and rank == 0).sum().backward()
+    error = None
+    if case == "invalid" and rank == 0:
+        bad = ob.from_numpy(np.zeros((5, 3), dtype=np.float32))
+        model.a.weight.set_grad(bad if dev == "cpu" else bad.to(dev))
+    try:
+        ddp.all_reduce_gradients()
+        ddp.wait_for_gradient_sync()
+    except RuntimeError as exc:
+        error = str(exc)
+    dist.barrier()
+    gb = model.b.weight.grad
+    return {"error": error, "b": None if gb is None else gb.numpy().tolist(),
+            "a": None if error else model.a.weight.grad.numpy().tolist(), "reducer": type(ddp._reducer).__name__}
+
+
+def missing_peer(rank, backend):
+    """Rank 0 launches a bucket that no other rank ever launches, with a wait budget of 100 ms and
+    without multicast.  Its kernel must come back, the status word must name the entry barrier
+    and the group must stay failed; the other ranks, which were between steps, shut down normally."""
+    import orthon_b200.distributed as dist
+    from orthon_b200 import _C
+    from orthon_b200.distributed import _state
+    group = _state.get_active()
+    be = group.backend
+    ws = dist.get_world_size()
+    n = 1 << 16
+    flag_bytes = (_C._PEER_FLAG_BYTES + 255) & ~255
+    region = be.allocate_symmetric(n * 4 + n * 4 + flag_bytes)
+    out = {"rank": rank}
+    dist.barrier()
+    if rank == 0:
+        status, found = be.status_tensors()
+        _C._peer_reduce(rank, ws, rank, list(region.ptrs), [p + 4 * n for p in region.ptrs], [p + 8 * n for p in region.ptrs], n,
+                        "float32", be.next_epoch(), 1.0, "average", False, status=status, found_inf=found, stream_kind=0,
+                        wait_ms=100.0)
+        _C.cuda_synchronize()  # returns: the wait is bounded
+        try:
+            be.check_status()
+            out["first"] = None
+        except RuntimeError as exc:
+            out["first"] = str(exc)
+        try:
+            group.barrier()
+            out["second"] = None
+        except RuntimeError as exc:
+            out["second"] = str(exc)
+    return out
