@@ -245,36 +245,77 @@ def _measure(ortho, args, model_key, amp, micro, rank, world, local):
                     "d2h_bytes_per_step": 4, "last_loss": last}}
 
 
-def _measure_with_fallback(ortho, args, model_key, amp, rank, world, local):
-    """Tries the full batch first; if the reference runs out of device memory, halves the slice
-    until the step fits.  Returns (result or None, list of out-of-memory notes)."""
-    import gc
-
-    import orthon.distributed as ddist
-    batch = CONFIGS[model_key][1]
-    notes, micro = [], 1
-    while micro <= batch:
+def _worker_main(argv):
+    """One attempt in a process of its own (a fresh reference pool and CUDA context): prints one
+    JSON line, {"ok": result} or {"oom": note} or {"error": text}."""
+    import argparse
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", required=True)
+    ap.add_argument("--amp", required=True)
+    ap.add_argument("--micro", type=int, required=True)
+    ap.add_argument("--steps", type=int, required=True)
+    ap.add_argument("--warmup", type=int, required=True)
+    a = ap.parse_args(argv)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    try:
+        ortho = _import_reference()
+        if not ortho.cuda_enabled():
+            print(json.dumps({"error": "reference build has no CUDA support"}), flush=True)
+            return
+        import orthon.distributed as ddist
         if world > 1:
-            store = f"/tmp/orthon_ref_store_{os.environ.get('MASTER_PORT', '0')}_{os.getppid()}_{model_key}_{micro}"
+            store = f"/tmp/orthon_ref_store_{os.environ.get('MASTER_PORT', '0')}_{os.environ.get('ORTHON_REF_ATTEMPT', '0')}"
             os.makedirs(store, exist_ok=True)
             os.environ["ORTHON_NCCL_STORE_DIR"] = store
             ddist.init_process_group("nccl", rank=rank, world_size=world, device=local)
         try:
-            return _measure(ortho, args, model_key, amp, micro, rank, world, local), notes
+            out = {"ok": _measure(ortho, a, a.model, a.amp, a.micro, rank, world, local)}
         except RuntimeError as exc:
             if "out of memory" not in str(exc):
                 raise
-            stats = ortho._C._memory_pool_stats() if hasattr(ortho._C, "_memory_pool_stats") else None
-            peak = getattr(stats, "get", lambda *_: None)("peak_bytes") if stats is not None else None
-            notes.append(f"{micro} slice(s) per step: out of device memory" + (f" (pool peak {peak} bytes)" if peak else ""))
-        finally:
-            if world > 1:
-                ddist.destroy_process_group()
-            gc.collect()
-            ortho.cuda_synchronize()
-            for name in ("_memory_pool_clear_cache", "_memory_pool_reset_stats"):  # the reference's own toggles
-                if hasattr(ortho._C, name):
-                    getattr(ortho._C, name)()
+            stats = ortho._C._memory_pool_stats() if hasattr(ortho._C, "_memory_pool_stats") else {}
+            out = {"oom": f"{a.micro} slice(s) per step: out of device memory (pool peak {stats.get('peak_bytes')} bytes)"}
+        print(json.dumps(out), flush=True)
+        if world > 1 and "ok" in out:
+            ddist.destroy_process_group()
+    except Exception as exc:  # noqa: BLE001
+        print(json.dumps({"error": f"{type(exc).__name__}: {exc}"[:300]}), flush=True)
+
+
+def _attempt(args, model_key, amp, micro, tag):
+    import subprocess
+    env = dict(os.environ, ORTHON_REF_ATTEMPT=f"{tag}_{model_key}_{micro}_{os.environ.get('TORCHELASTIC_RUN_ID', '')}")
+    cmd = [sys.executable, os.path.abspath(__file__), "--worker", "--model", model_key, "--amp", amp, "--micro", str(micro),
+           "--steps", str(args.steps), "--warmup", str(args.warmup)]
+    try:
+        res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=float(os.environ.get("ORTHON_REF_ATTEMPT_TIMEOUT", 1500)))
+    except subprocess.TimeoutExpired:
+        return {"error": f"attempt with {micro} slice(s) per step did not finish in time"}
+    for line in reversed(res.stdout.strip().splitlines()):
+        try:
+            doc = json.loads(line)
+        except ValueError:
+            continue
+        if isinstance(doc, dict) and ({"ok", "oom", "error"} & set(doc)):
+            return doc
+    return {"error": f"worker exited with code {res.returncode}: {res.stderr.strip()[-300:]}"}
+
+
+def _measure_with_fallback(args, model_key, amp, tag):
+    """Tries the full batch first; while the reference runs out of device memory, halves the
+    slice.  Every attempt runs in a fresh process.  Returns (result or None, notes)."""
+    batch = CONFIGS[model_key][1]
+    notes, micro = [], 1
+    while micro <= batch:
+        doc = _attempt(args, model_key, amp, micro, tag)
+        if "ok" in doc:
+            return doc["ok"], notes
+        if "error" in doc:
+            notes.append(doc["error"])
+            return None, notes
+        notes.append(doc["oom"])
         micro *= 2
     return None, notes
 
@@ -285,21 +326,14 @@ ANCHOR = ("tiny", "fp16")
 def run_reference_lm(args):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    try:
-        ortho = _import_reference()
-    except Exception as exc:  # noqa: BLE001
+    if not os.path.isdir(os.path.join(REF, "orthon")):
         if rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable": f"cannot import the reference build: {exc}"}))
-        return
-    if not ortho.cuda_enabled():
-        if rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable": "reference build has no CUDA support"}))
+            print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/orthon is missing (reference not installed)"}))
         return
     amp = getattr(args, "amp", "bf16")
-    main, notes = _measure_with_fallback(ortho, args, args.model, amp, rank, world, local)
+    main, notes = _measure_with_fallback(args, args.model, amp, "main")
     if main is None:
-        line = {"impl": "reference", "unavailable": "the reference runs out of device memory on this config at every slice size: " + "; ".join(notes)}
+        line = {"impl": "reference", "unavailable": "the reference cannot run this config: " + "; ".join(notes)[:600]}
     else:
         line = {"metric": "ddp_train_tokens_per_s", "value": main["value"], "unit": "tokens/s", "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": main["ms_per_step"], "higher_is_better": True,
@@ -309,9 +343,14 @@ def run_reference_lm(args):
         if notes:
             line["config"]["out_of_memory"] = notes
     if getattr(args, "anchor", True) and (args.model, amp) != ANCHOR:
-        a, a_notes = _measure_with_fallback(ortho, args, ANCHOR[0], ANCHOR[1], rank, world, local)
-        line["anchor"] = {"unavailable": "; ".join(a_notes)} if a is None else {
+        a, a_notes = _measure_with_fallback(args, ANCHOR[0], ANCHOR[1], "anchor")
+        line["anchor"] = {"unavailable": "; ".join(a_notes)[:600]} if a is None else {
             "config": a["config"], "dtype": a["dtype"], "value": a["value"], "unit": "tokens/s",
             "ms_per_step": a["ms_per_step"], "e2e": a["e2e"]}
     if rank == 0:
         print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    if len(sys.argv) > 1 and sys.argv[1] == "--worker":
+        _worker_main(sys.argv[2:])

@@ -26,8 +26,8 @@ ESZ = {"float32": 4, "bfloat16": 2, "float16": 2}
 def worker(rank, dtypes, max_mb, iters):
     import orthon_b200.distributed as dist
     from orthon_b200 import _C
-    from orthon_b200.distributed import _state
-    group = _state.get_active()
+    from orthon_b200.distributed import group as _group
+    group = _group.active()
     be = group.backend
     ws, dev_i = group.world_size, be.device
     dev = f"cuda:{dev_i}"

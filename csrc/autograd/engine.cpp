@@ -101,6 +101,7 @@ struct GraphTask {
   std::vector<std::shared_ptr<TensorImpl>> leaves;  // discovery order, unique
   std::unordered_set<TensorImpl*> leaf_set;
   std::unordered_map<TensorImpl*, int> leaf_edges;  // graph edges that still owe this leaf a gradient
+  std::unordered_map<TensorImpl*, int> leaf_uses;   // graph edges that reach this leaf (fixed after discovery)
   std::vector<std::pair<uint64_t, std::function<void()>>> finalizers;
   std::unordered_set<uint64_t> finalizer_keys;
 
@@ -138,6 +139,7 @@ struct GraphTask {
       if (e.kind == GraphEdge::Leaf) {
         add_leaf(e.leaf);
         ++leaf_edges[e.leaf.get()];
+        ++leaf_uses[e.leaf.get()];
       } else if (e.kind == GraphEdge::Producer) {
         if (e.node->released()) throw std::runtime_error(kFreedGraph);
         ++deps[e.node.get()];
@@ -218,8 +220,27 @@ void AutogradEngine::backward(const Tensor& root, bool retain_graph) {
       grads.erase(node.get());
       node->validate_saved_versions();
       check_grad(g, node->out_shape, node->out_dtype, node->out_device, node->name());
-      std::vector<Tensor> in_grads = node->backward(g);
       const auto& edges = node->edges();
+      // A leaf with a preassigned gradient slot and this node as its only consumer, not
+      // accumulating onto an earlier gradient: offer the slot as the formula's destination.
+      bool offered = false;
+      for (size_t i = 0; i < edges.size(); ++i) {
+        const GraphEdge& e = edges[i];
+        if (e.kind != GraphEdge::Leaf) continue;
+        AutogradMeta& m = e.leaf->ag();
+        if (!m.grad_slot || task.leaf_uses[e.leaf.get()] != 1) continue;
+        if (m.grad && m.grad->buffer() == m.grad_slot->buffer()) continue;
+        if (!offered) { node->grad_out.assign(edges.size(), Tensor()); offered = true; }
+        node->grad_out[i] = Tensor(m.grad_slot);
+      }
+      std::vector<Tensor> in_grads;
+      try {
+        in_grads = node->backward(g);
+      } catch (...) {
+        node->grad_out.clear();
+        throw;
+      }
+      if (offered) node->grad_out.clear();
       if (in_grads.size() > edges.size())
         throw std::runtime_error(std::string("backward: ") + node->name() + " returned too many gradients");
       for (size_t i = 0; i < edges.size(); ++i) {
@@ -242,7 +263,9 @@ void AutogradEngine::backward(const Tensor& root, bool retain_graph) {
               AutogradMeta& m = e.leaf->ag();
               Tensor slot(m.grad_slot);
               const bool accumulating = m.grad && m.grad->buffer() == m.grad_slot->buffer();
+              const bool in_place = it->second.impl()->buffer() == slot.impl()->buffer() && it->second.data() == slot.data();
               if (accumulating) ops::add_(slot, it->second, 1.0);
+              else if (in_place) slot.bump_version();  // the formula wrote the slot itself
               else ops::copy_(slot, it->second);
               m.grad = m.grad_slot;
               leaf_grads.erase(it);
@@ -286,7 +309,9 @@ void AutogradEngine::backward(const Tensor& root, bool retain_graph) {
     AutogradMeta& m = c.leaf->ag();
     if (c.into_slot) {
       Tensor slot(m.grad_slot);
+      const bool in_place = c.value.impl()->buffer() == slot.impl()->buffer() && c.value.data() == slot.data();
       if (c.add_into_slot) ops::add_(slot, c.value, 1.0);
+      else if (in_place) slot.bump_version();
       else ops::copy_(slot, c.value);
       m.grad = m.grad_slot;
     } else {

@@ -828,7 +828,11 @@ void adam_with_grad(OpCall& c) {
   const int vt = c.i[0] > 0 ? static_cast<int>(c.i[0]) : kThreads;  // block size of the vector pass
   auto launch = [&](auto model_ptr) {
     using MT = std::remove_pointer_t<decltype(model_ptr)>;
-    if (n8 > 0) adam_vec_kernel<G, MT><<<ew_grid(n8, vt, sms), vt, 0, st>>>(pp, pm, pv, pg, model_ptr, n8, a);
+    if (n8 > 0) {
+      static const bool once = (prefer_max_shared_carveout(adam_vec_kernel<G, MT>), true);
+      (void)once;
+      adam_vec_kernel<G, MT><<<ew_grid(n8, vt, sms), vt, 0, st>>>(pp, pm, pv, pg, model_ptr, n8, a);
+    }
     if (rest > 0)
       adam_kernel<G, MT><<<ew_grid(rest, kThreads, sms), kThreads, 0, st>>>(pp + done, pm + done, pv + done, pg + done,
                                                                            model_ptr ? model_ptr + done : model_ptr, rest, a);
@@ -865,7 +869,11 @@ void sgd_with_grad(OpCall& c) {
   const int vt = c.i[0] > 0 ? static_cast<int>(c.i[0]) : kThreads;  // block size of the vector pass
   auto launch = [&](auto model_ptr) {
     using MT = std::remove_pointer_t<decltype(model_ptr)>;
-    if (n8 > 0) sgd_vec_kernel<G, MT><<<ew_grid(n8, vt, sms), vt, 0, st>>>(pp, pg, model_ptr, n8, lr, wd, gs);
+    if (n8 > 0) {
+      static const bool once = (prefer_max_shared_carveout(sgd_vec_kernel<G, MT>), true);
+      (void)once;
+      sgd_vec_kernel<G, MT><<<ew_grid(n8, vt, sms), vt, 0, st>>>(pp, pg, model_ptr, n8, lr, wd, gs);
+    }
     if (rest > 0)
       sgd_kernel<G, MT><<<ew_grid(rest, kThreads, sms), kThreads, 0, st>>>(pp + done, pg + done, model_ptr ? model_ptr + done : model_ptr,
                                                                           rest, lr, wd, gs);

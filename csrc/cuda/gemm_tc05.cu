@@ -29,8 +29,10 @@
 
 #include <atomic>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <string>
+#include <unordered_map>
 
 #include "ob/cuda_common.cuh"
 #include "ob/ops.h"
@@ -681,6 +683,62 @@ EncodeFn encode_fn() {
   return fn;
 }
 
+// Encoded tensor maps are cached: a training step presents the same (pointer, extents, strides,
+// box) combinations again and again (weights never move, activations come back from the pool at
+// the same addresses), and each cuTensorMapEncodeTiled call costs the host about as much as
+// the rest of a launch.  The cache is a flat hash table that is simply cleared when it fills up.
+struct MapKey {
+  const void* ptr;
+  uint64_t dims[5];
+  uint64_t strides[4];
+  uint32_t box[5];
+  uint32_t rank, dtype, promo;
+  bool operator==(const MapKey& o) const { return std::memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    const uint64_t* w = reinterpret_cast<const uint64_t*>(&k);
+    uint64_t h = 0x9E3779B97F4A7C15ull;
+    for (size_t i = 0; i < sizeof(MapKey) / 8; ++i) { h ^= w[i]; h *= 0xBF58476D1CE4E5B9ull; h ^= h >> 29; }
+    return static_cast<size_t>(h);
+  }
+};
+static_assert(sizeof(MapKey) % 8 == 0, "MapKey is hashed as 64-bit words");
+std::mutex g_map_mu;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_map_cache;
+std::atomic<long long> g_map_hits{0}, g_map_misses{0};
+
+bool encode_cached(CUtensorMap* out, DType dt, int rank, const void* base, const cuuint64_t* dims, const cuuint64_t* strides,
+                   const cuuint32_t* box, CUtensorMapL2promotion promo) {
+  MapKey key;
+  std::memset(&key, 0, sizeof(key));
+  key.ptr = base;
+  for (int i = 0; i < rank; ++i) { key.dims[i] = dims[i]; key.box[i] = box[i]; }
+  for (int i = 0; i + 1 < rank; ++i) key.strides[i] = strides[i];
+  key.rank = static_cast<uint32_t>(rank);
+  key.dtype = static_cast<uint32_t>(dt);
+  key.promo = static_cast<uint32_t>(promo);
+  {
+    std::lock_guard<std::mutex> lock(g_map_mu);
+    auto it = g_map_cache.find(key);
+    if (it != g_map_cache.end()) {
+      *out = it->second;
+      g_map_hits.fetch_add(1, std::memory_order_relaxed);
+      return true;
+    }
+  }
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  const CUresult r = encode_fn()(out, dt == DType::BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                                 static_cast<cuuint32_t>(rank), const_cast<void*>(base), dims, strides, box, estr,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  g_map_misses.fetch_add(1, std::memory_order_relaxed);
+  std::lock_guard<std::mutex> lock(g_map_mu);
+  if (g_map_cache.size() >= 8192) g_map_cache.clear();
+  g_map_cache.emplace(key, *out);
+  return true;
+}
+
 // Logical operand of the GEMM: `mn` x `k` elements with element strides, plus batch strides.
 struct OperandView {
   const void* ptr;
@@ -716,12 +774,8 @@ CUtensorMap make_map(const OperandView& o, bool mn_major, int box_rows, int nb0,
   const long long s0 = nb0 > 1 ? o.bs0 : s1 * nb1;
   cuuint64_t strides[3] = {static_cast<cuuint64_t>(rs) * 2, static_cast<cuuint64_t>(s1) * 2, static_cast<cuuint64_t>(s0) * 2};
   cuuint32_t box[4] = {64, static_cast<cuuint32_t>(mn_major ? 64 : box_rows), 1, 1};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
-  const CUresult r = encode_fn()(&m, dt == DType::BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
-                                 const_cast<void*>(o.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r)));
+  if (!encode_cached(&m, dt, 4, o.ptr, dims, strides, box, CU_TENSOR_MAP_L2_PROMOTION_L2_256B))
+    throw std::runtime_error("cuTensorMapEncodeTiled rejected a GEMM operand");
   return m;
 }
 
@@ -797,10 +851,7 @@ void launch_tc05(const OperandView& a, const OperandView& b, bool a_mn, bool b_m
     const long long s0 = nb0 > 1 ? c_bs0 : s1 * nb1;
     cuuint64_t strides[3] = {static_cast<cuuint64_t>(ldc) * 2, static_cast<cuuint64_t>(s1) * 2, static_cast<cuuint64_t>(s0) * 2};
     cuuint32_t box[4] = {64, 32, 1, 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    return encode_fn()(out, dt == DType::BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, ptr, dims,
-                       strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                       CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return encode_cached(out, dt, 4, ptr, dims, strides, box, CU_TENSOR_MAP_L2_PROMOTION_NONE);
   };
   CUtensorMap mc = ma, mz = ma;
   static const bool direct_store = [] { const char* e = std::getenv("ORTHON_GEMM_STORE"); return e != nullptr && std::string(e) == "direct"; }();
@@ -1034,12 +1085,16 @@ int* tc05_error_flag(int device) { return error_flag(device); }
 bool tc05_encode_map(CUtensorMap* out, DType dt, int rank, void* base, const uint64_t* dims, const uint64_t* strides_bytes,
                      const uint32_t* box) {
   cuuint64_t d[5], s[4];
-  cuuint32_t b[5], e[5];
-  for (int i = 0; i < rank; ++i) { d[i] = dims[i]; b[i] = box[i]; e[i] = 1; }
+  cuuint32_t b[5];
+  for (int i = 0; i < rank; ++i) { d[i] = dims[i]; b[i] = box[i]; }
   for (int i = 0; i + 1 < rank; ++i) s[i] = strides_bytes[i];
-  return encode_fn()(out, dt == DType::BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                     static_cast<cuuint32_t>(rank), base, d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return encode_cached(out, dt, rank, base, d, s, b, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+}
+
+// (hits, misses) of the tensor-map cache since the process started.
+void tensor_map_cache_stats(long long* hits, long long* misses) {
+  *hits = g_map_hits.load(std::memory_order_relaxed);
+  *misses = g_map_misses.load(std::memory_order_relaxed);
 }
 
 // Diagnostics (reference project: src/diagnostics/matmul.cpp:14-87): force a route, read the

@@ -613,15 +613,24 @@ void bind_peer(py::module_& m) {
     grid = static_cast<int>(std::max<long long>(1, std::min<long long>(grid, (vecs / world + threads - 1) / threads)));
     if (grid > kMaxCtas) grid = kMaxCtas;
     cudaStream_t st = pick_stream(device, stream_kind);
-#define OB_PEER_LAUNCH(GT)                                                                    \
-  do {                                                                                        \
-    if (world == 2) peer_reduce_kernel<GT, 2><<<grid, threads, 0, st>>>(a);              \
-    else if (world == 4) peer_reduce_kernel<GT, 4><<<grid, threads, 0, st>>>(a);         \
-    else if (world == 8) peer_reduce_kernel<GT, 8><<<grid, threads, 0, st>>>(a);         \
-    else peer_reduce_kernel<GT, 0><<<grid, threads, 0, st>>>(a);                         \
+#define OB_PEER_LAUNCH_W(GT, W)                                                                 \
+  do {                                                                                         \
+    static const bool once = (prefer_max_shared_carveout(peer_reduce_kernel<GT, W>), true);    \
+    (void)once;                                                                                \
+    peer_reduce_kernel<GT, W><<<grid, threads, 0, st>>>(a);                                    \
+  } while (0)
+#define OB_PEER_LAUNCH(GT)                        \
+  do {                                            \
+    if (world == 2) OB_PEER_LAUNCH_W(GT, 2);      \
+    else if (world == 4) OB_PEER_LAUNCH_W(GT, 4); \
+    else if (world == 8) OB_PEER_LAUNCH_W(GT, 8); \
+    else OB_PEER_LAUNCH_W(GT, 0);                 \
   } while (0)
     if (mc_grads != 0) {
       // In-switch reduction and broadcast through the multicast mapping of the bucket.
+      static const bool once = (prefer_max_shared_carveout(nvls_reduce_kernel<float>), prefer_max_shared_carveout(nvls_reduce_kernel<__nv_bfloat16>),
+                                prefer_max_shared_carveout(nvls_reduce_kernel<__half>), true);
+      (void)once;
       if (gd == DType::F32) nvls_reduce_kernel<float><<<grid, threads, 0, st>>>(a);
       else if (gd == DType::BF16) nvls_reduce_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>(a);
       else if (gd == DType::F16) nvls_reduce_kernel<__half><<<grid, threads, 0, st>>>(a);
@@ -631,6 +640,7 @@ void bind_peer(py::module_& m) {
     else if (gd == DType::F16) OB_PEER_LAUNCH(__half);
     else throw std::invalid_argument("peer reduce: gradients must be float32, float16 or bfloat16");
 #undef OB_PEER_LAUNCH
+#undef OB_PEER_LAUNCH_W
     check_launch("peer reduce");
     return grid;
   }, py::arg("rank"), py::arg("world"), py::arg("device"), py::arg("grads"), py::arg("staging"), py::arg("flags"), py::arg("n"),

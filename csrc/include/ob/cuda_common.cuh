@@ -95,6 +95,15 @@ inline int ew_grid(int64_t work_items, int threads, int sm_count) {
   return static_cast<int>(blocks);
 }
 
+// A kernel that is meant to run beside the persistent tcgen05 GEMMs has to live under the same
+// shared-memory / L1 split as they do (an SM is configured for one split at a time, and the GEMMs
+// ask for the largest shared-memory share): without this hint the driver would pick the smallest
+// share for a kernel that uses no shared memory, and its blocks would wait for the GEMM to drain.
+template <class Kernel>
+inline void prefer_max_shared_carveout(Kernel kernel) {
+  cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+
 inline cudaStream_t stream_of(const OpCall& c) { return static_cast<cudaStream_t>(c.stream); }
 int sm_count_for(const Tensor& t);
 void check_launch(const char* what);

@@ -155,6 +155,13 @@ class Node : public std::enable_shared_from_this<Node> {
   void validate_saved_versions() const;
   bool released() const { return released_; }
   void mark_released();
+  // Destination offers, set by the engine around one backward() call: grad_out[i], when defined,
+  // is storage with the shape, dtype and device of input i's gradient (a leaf's preassigned
+  // gradient slot whose only consumer is this node).  A formula that can write its result there
+  // directly does so and returns that tensor for input i; the engine then skips its copy.
+  // Formulas that ignore the offer stay correct.
+  std::vector<Tensor> grad_out;
+  Tensor grad_destination(size_t input) const { return input < grad_out.size() ? grad_out[input] : Tensor(); }
   // Output metadata recorded at attach time, used to validate incoming gradients.
   Shape out_shape;
   DType out_dtype = DType::F32;

@@ -16,7 +16,7 @@ namespace ops {
 // ------------------------------------------------------------------------ GEMM
 namespace {
 
-Tensor gemm_raw(const Tensor& a, bool ta, const Tensor& b, bool tb) {
+Tensor gemm_raw(const Tensor& a, bool ta, const Tensor& b, bool tb, const Tensor& destination = Tensor()) {
   check_same_device(a, b, "matmul");
   check_same_dtype(a, b, "matmul");
   default_dispatcher().check_dtype(OperatorId::Matmul, a.device(), a.dtype());
@@ -38,7 +38,11 @@ Tensor gemm_raw(const Tensor& a, bool ta, const Tensor& b, bool tb) {
   Shape os(a.shape().begin(), a.shape().end() - 2);
   os.push_back(M);
   os.push_back(N);
-  Tensor out = Tensor::empty(os, a.dtype(), a.device());
+  // A caller-provided destination (a contiguous tensor of the result's shape, dtype and device:
+  // a leaf's gradient slot offered by the engine) takes the product directly.
+  const bool direct = destination.defined() && destination.shape() == os && destination.dtype() == a.dtype() &&
+                      destination.device() == a.device() && destination.is_contiguous();
+  Tensor out = direct ? destination : Tensor::empty(os, a.dtype(), a.device());
   if (out.numel() == 0) return out;
   if (K == 0) {
     fill_raw(out, 0.0);
@@ -60,8 +64,8 @@ struct MatMulNode : Node {
   bool ta, tb;
   const char* name() const override { return "MatMulNode"; }
   std::vector<Tensor> backward(const Tensor& g) override {
-    Tensor da = ta ? gemm_raw(b, tb, g, true) : gemm_raw(g, false, b, !tb);
-    Tensor db = tb ? gemm_raw(g, true, a, ta) : gemm_raw(a, !ta, g, false);
+    Tensor da = ta ? gemm_raw(b, tb, g, true, grad_destination(0)) : gemm_raw(g, false, b, !tb, grad_destination(0));
+    Tensor db = tb ? gemm_raw(g, true, a, ta, grad_destination(1)) : gemm_raw(a, !ta, g, false, grad_destination(1));
     return {da, db};
   }
   void release_saved() override { a = Tensor(); b = Tensor(); }
@@ -106,7 +110,7 @@ struct LinearNode : Node {
     if (act == Act::Relu) gz = unary_backward(Unary::Relu, saved_act, g2);
     else if (act == Act::Gelu) gz = unary_backward(Unary::Gelu, saved_act, g2);
     Tensor dx = reshape(gemm_raw(gz, false, w, true), x_shape);
-    Tensor dw = gemm_raw(x2, true, gz, false);
+    Tensor dw = gemm_raw(x2, true, gz, false, grad_destination(1));
     std::vector<Tensor> out{dx, dw};
     out.push_back(has_bias ? sum(gz, 0, false) : Tensor());
     out.push_back(has_res ? g : Tensor());
@@ -204,9 +208,9 @@ struct MlpNode : Node {
     // dz = (g @ w2^T) * gelu'(z) in one GEMM (z holds the derivative saved by the forward).
     Tensor dz = Tensor::empty({g2.shape()[0], F}, g2.dtype(), g2.device());
     linear_raw(g2, transpose(w2, 0, 1), Tensor(), 3, z, dz, nullptr);
-    Tensor dw2 = gemm_raw(h, true, g2, false);
+    Tensor dw2 = gemm_raw(h, true, g2, false, grad_destination(3));
     Tensor dx = reshape(gemm_raw(dz, false, w1, true), x_shape);
-    Tensor dw1 = gemm_raw(x2, true, dz, false);
+    Tensor dw1 = gemm_raw(x2, true, dz, false, grad_destination(1));
     std::vector<Tensor> out{dx, dw1, has_b1 ? sum(dz, 0, false) : Tensor(), dw2, has_b2 ? sum(g2, 0, false) : Tensor(),
                             has_res ? g : Tensor()};
     return out;

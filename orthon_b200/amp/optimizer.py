@@ -72,8 +72,8 @@ class MixedPrecisionOptimizer:
         check = getattr(model, "_validate_master_gradient_sync", None)
         if check is not None:
             check()
-        from ..distributed import _state as dstate
-        self._group = dstate.get_active() if dstate.is_initialized() else None
+        from ..distributed import group as dstate
+        self._group = dstate.active() if dstate.is_active() else None
         self._ddp = model if hasattr(model, "_reducer") else None
         self._peer = None
         self._pending_inv_scale = None
@@ -270,16 +270,25 @@ class MixedPrecisionOptimizer:
                 if s.master is not s.parameter:
                     _C._amp_copy_master_to_model_(s.parameter, s.master)
 
-    def _amp_collective_device(self):
+    def _agree_on_overflow(self, local):
+        """The overflow verdict of this cycle, identical on every rank.  The peer-memory reducer
+        exchanges the found-inf word inside its reduction kernel, so its verdict already is;
+        otherwise the ranks add up a one-element flag."""
+        from ..distributed import group as dstate
         if self._group is not None:
             self._group.ensure_open()
-        return self._states[0].master.device if self._states else None
+        group = self._group if self._group is not None else (dstate.active() if dstate.is_active() else None)
+        if group is None or group.world_size == 1 or self._peer is not None or not self._states:
+            return bool(local)
+        flag = _C._full_on([1], 1.0 if local else 0.0, "float32", str(self._states[0].master.device))
+        group.all_reduce(flag, op="sum")
+        return float(flag.tolist()[0]) > 0.0
 
     def _all_reduce_master_grads(self):
-        from ..distributed import _state as dstate
+        from ..distributed import group as dstate
         from ..parallel.reducer import reduce_master_gradients
-        if self._group is None and dstate.is_initialized():
-            self._group = dstate.get_active()
+        if self._group is None and dstate.is_active():
+            self._group = dstate.active()
         if self._group is None:
             return
         self._group.ensure_open()

@@ -1,54 +1,55 @@
 """Distributed facade: process-group lifecycle, collectives, `spawn`, DDP.
-(reference project: python/orthon/distributed/__init__.py:14-88)"""
-from . import _state
-from ._backend import Backend, register_backend, get_backend_factory, _SingleRankBackend  # noqa: F401
-from ._env import apply_env_defaults, rank_config_from_env  # noqa: F401
-from ._process_group import _ProcessGroup
-from .work import Work  # noqa: F401
+
+One group is active per process.  `init_process_group` builds the transport named by `backend`
+(arguments the caller leaves out come from the launcher environment), wraps it in a
+`GroupHandle` and returns the transport, as the reference does
+(python/orthon/distributed/__init__.py:14-88).
+"""
+from . import group as _group
+from .group import Backend, Work, register_backend, get_backend_factory  # noqa: F401
+from .launch_env import LaunchEnvironment, apply_env_defaults, rank_config_from_env  # noqa: F401
 
 
 def init_process_group(backend=None, **kwargs):
-    """Creates the process-wide group.  Missing rank / world_size / device come from the
-    launcher environment; `backend` may come from ORTHON_DISTRIBUTED_BACKEND."""
-    if _state.is_initialized():
+    if _group.is_active():
         raise RuntimeError("distributed process group is already initialized")
-    backend, kwargs = apply_env_defaults(backend, kwargs)
-    transport = get_backend_factory(backend)(**kwargs)
-    _state.set_active(_ProcessGroup(transport))
+    name, arguments = LaunchEnvironment.read().complete(backend, kwargs)
+    transport = get_backend_factory(name)(**arguments)
+    _group.activate(_group.GroupHandle(transport))
+    return transport
 
 
 def destroy_process_group():
-    if not _state.is_initialized():
-        return
-    group = _state.get_active()
-    try:
-        group.shutdown()
-    finally:
-        _state.clear_active()
+    if _group.is_active():
+        handle = _group.active()
+        try:
+            handle.shutdown()
+        finally:
+            _group.deactivate()
 
 
 def is_initialized():
-    return _state.is_initialized()
+    return _group.is_active()
 
 
 def get_rank():
-    return _state.get_active().rank
+    return _group.active().rank
 
 
 def get_world_size():
-    return _state.get_active().world_size
+    return _group.active().world_size
 
 
 def barrier():
-    return _state.get_active().barrier()
+    return _group.active().barrier()
 
 
 def all_reduce(tensor, op="sum", async_op=False):
-    return _state.get_active().all_reduce(tensor, op=op, async_op=async_op)
+    return _group.active().all_reduce(tensor, op=op, async_op=async_op)
 
 
 def broadcast(tensor, src=0, async_op=False):
-    return _state.get_active().broadcast(tensor, src=src, async_op=async_op)
+    return _group.active().broadcast(tensor, src=src, async_op=async_op)
 
 
 def spawn(fn, args=(), nprocs=2, backend="local"):

@@ -13,10 +13,9 @@ import traceback
 
 import numpy as np
 
-from . import _state
-from ._backend import Backend, _TransportFailure
+from . import group as _group
+from .group import Backend, Work, _TransportFailure
 from .store import ManagerStore, Store, StoreTimeout
-from .work import _CompletedWork
 
 COLLECTIVE_TIMEOUT_SECONDS = 30.0
 _NP = {"float32": np.float32, "float64": np.float64, "float16": np.float16, "int32": np.int32, "int64": np.int64,
@@ -121,7 +120,7 @@ class LocalBackend(Backend):
         for p in parts[1:]:
             total += np.frombuffer(p, dtype=_NP[tensor.dtype])
         self._write_back(tensor, total.tobytes())
-        return _CompletedWork() if async_op else tensor
+        return Work() if async_op else tensor
 
     def broadcast(self, tensor, src=0, async_op=False):
         self._open()
@@ -131,7 +130,7 @@ class LocalBackend(Backend):
         desc = ["broadcast", list(tensor.shape), tensor.dtype, src]
         parts = self._gather(desc, self._bytes_of(tensor) if self._rank == src else b"")
         self._write_back(tensor, parts[src])
-        return _CompletedWork() if async_op else tensor
+        return Work() if async_op else tensor
 
     def barrier(self):
         self._open()
@@ -176,7 +175,7 @@ def spawn(fn, args=(), nprocs=2, backend="local"):
     The first failing worker aborts the shared store; survivors are terminated, then killed."""
     if nprocs < 1:
         raise ValueError("nprocs must be >= 1")
-    if _state.is_initialized():
+    if _group.is_active():
         raise RuntimeError("cannot spawn while distributed is already initialized")
     ctx = mp.get_context("spawn")
     manager, handles = create_store(ctx)

@@ -7,9 +7,8 @@ import importlib.util
 import os
 
 from .. import _C
-from ._backend import Backend, _TransportFailure
+from .group import Backend, Work, _TransportFailure
 from .store import ManagerStore, Store, store_from_env
-from .work import Work
 
 RENDEZVOUS_TIMEOUT_SECONDS = 60.0
 _SUPPORTED = ("float32", "float16", "bfloat16")
@@ -30,15 +29,9 @@ def _bundled_nccl():
     return ""
 
 
-class _NativeWork(Work):
-    def __init__(self, work):
-        self._work = work
-
-    def wait(self):
-        return self._work.wait()
-
-    def is_completed(self):
-        return self._work.is_completed()
+def _NativeWork(native):
+    """Public handle over the native process group's Work (event-backed, polls the communicator)."""
+    return Work(wait=native.wait, probe=native.is_completed)
 
 
 class NcclBackend(Backend):

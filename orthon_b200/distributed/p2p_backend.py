@@ -15,10 +15,9 @@ import time
 import socket
 
 from .. import _C
-from ._backend import Backend, _TransportFailure
+from .group import Backend, Work, _TransportFailure
 from .nccl_backend import RENDEZVOUS_TIMEOUT_SECONDS
 from .store import ManagerStore, Store, store_from_env
-from .work import _CompletedWork
 
 STAGING_BYTES = 64 << 20
 _ESIZE = {"float32": 4, "float16": 2, "bfloat16": 2}
@@ -332,7 +331,7 @@ class PeerBackend(Backend):
         with _no_grad():
             if self._world > 1 and not self._peer_sum(tensor):
                 return self._fallback().all_reduce(tensor, op=op, async_op=async_op)
-        return _CompletedWork() if async_op else tensor
+        return Work() if async_op else tensor
 
     def broadcast(self, tensor, src=0, async_op=False):
         self._open()
@@ -346,7 +345,7 @@ class PeerBackend(Backend):
                     tensor.fill_(0.0)
                 if not self._peer_sum(tensor):
                     return self._fallback().broadcast(tensor, src=src, async_op=async_op)
-        return _CompletedWork() if async_op else tensor
+        return Work() if async_op else tensor
 
     def barrier(self):
         self._open()

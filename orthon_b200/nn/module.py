@@ -32,62 +32,74 @@ class Parameter:
         self._data = data
 
 
+def _check_member_name(owner, name, kind):
+    """Names of registered members are path components of state-dict keys: identifiers (children
+    may also be decimal, for containers) that do not shadow anything the class defines."""
+    if not isinstance(name, str):
+        raise TypeError(f"{kind} name must be a string")
+    well_formed = bool(name) and "." not in name and (name.isidentifier() or (kind == "module" and name.isdecimal()))
+    if not well_formed:
+        raise ValueError(f"invalid {kind} name {name!r}")
+    if name in _RESERVED or hasattr(type(owner), name):
+        raise KeyError(f"'{name}' is already an attribute of this module")
+
+
+_EXPECTED = {"parameter": (lambda v: isinstance(v, _C.Tensor), "registered parameter must be a Tensor"),
+             "module": (lambda v: isinstance(v, Module), "registered child must be a Module")}
+
+
 class Module:
+    """A name belongs to at most one of four places: the parameter, buffer or child registry, or
+    the instance dictionary (plain attributes).  Every write goes through `_set_member`, which
+    first decides whether the write is admissible and only then moves the name to its new place,
+    evicting it from wherever it was."""
+
     def __init__(self):
         d = object.__getattribute__(self, "__dict__")
-        d["_parameters"] = {}
-        d["_buffers"] = {}
-        d["_non_persistent_buffers"] = set()
-        d["_modules"] = {}
-        d["training"] = True
+        d.update(_parameters={}, _buffers={}, _modules={}, _non_persistent_buffers=set(), training=True)
 
     # ------------------------------------------------------------ registration
-    def _set_member(self, name, value, kind, *, persistent=True):
-        """Single entry point for every attribute write: validate first, then publish."""
-        attrs = object.__getattribute__(self, "__dict__")
-        params, buffers, modules = self._parameters, self._buffers, self._modules
-        if kind != "attribute":
-            if not isinstance(name, str):
-                raise TypeError(f"{kind} name must be a string")
-            legal = name.isidentifier() or (kind == "module" and name.isdecimal())
-            if not name or "." in name or not legal:
-                raise ValueError(f"invalid {kind} name {name!r}")
-            if hasattr(type(self), name) or name in _RESERVED:
-                raise KeyError(f"'{name}' is already an attribute of this module")
-        if kind == "buffer":
-            if name in params or name in modules or name in attrs:
-                raise KeyError(f"'{name}' is already an attribute or registered member")
-            if value is not None and not isinstance(value, _C.Tensor):
-                raise TypeError(f"buffer '{name}' expects a Tensor or None, got {type(value).__name__}")
-            persistent = bool(persistent)
-        elif name in buffers:
-            raise KeyError(f"cannot assign a {kind} to registered buffer '{name}'")
-        elif kind == "parameter" and not isinstance(value, _C.Tensor):
-            raise TypeError("registered parameter must be a Tensor")
-        elif kind == "module" and not isinstance(value, Module):
-            raise TypeError("registered child must be a Module")
+    def _registries(self):
+        return {"parameter": self._parameters, "buffer": self._buffers, "module": self._modules}
 
+    def _admit(self, name, value, kind):
+        registries = self._registries()
         if kind == "attribute":
-            object.__setattr__(self, name, value)  # descriptors may veto before cleanup
+            if name in registries["buffer"]:
+                raise KeyError(f"cannot assign a {kind} to registered buffer '{name}'")
+            return
+        _check_member_name(self, name, kind)
+        if kind == "buffer":
+            plain = object.__getattribute__(self, "__dict__")
+            if name in plain or name in registries["parameter"] or name in registries["module"]:
+                raise KeyError(f"'{name}' is already an attribute or registered member")
+            if not (value is None or isinstance(value, _C.Tensor)):
+                raise TypeError(f"buffer '{name}' expects a Tensor or None, got {type(value).__name__}")
+            return
+        if name in registries["buffer"]:  # a buffer slot keeps its role until it is re-registered
+            raise KeyError(f"cannot assign a {kind} to registered buffer '{name}'")
+        accepts, complaint = _EXPECTED[kind]
+        if not accepts(value):
+            raise TypeError(complaint)
+
+    def _set_member(self, name, value, kind, *, persistent=True):
+        self._admit(name, value, kind)
+        if kind == "attribute":
+            object.__setattr__(self, name, value)  # a descriptor may still refuse: nothing has moved yet
         else:
-            attrs.pop(name, None)
-        if kind != "parameter":
-            params.pop(name, None)
-        if kind != "module":
-            modules.pop(name, None)
-        if kind != "buffer":
-            buffers.pop(name, None)
+            object.__getattribute__(self, "__dict__").pop(name, None)
+        for other, table in self._registries().items():
+            if other != kind:
+                table.pop(name, None)
+        if kind == "buffer" and not persistent:
+            self._non_persistent_buffers.add(name)
+        else:
             self._non_persistent_buffers.discard(name)
-        if kind == "parameter":
-            params[name] = value
-        elif kind == "module":
-            modules[name] = value
-        elif kind == "buffer":
-            buffers[name] = value
-            (self._non_persistent_buffers.discard if persistent else self._non_persistent_buffers.add)(name)
+        if kind != "attribute":
+            self._registries()[kind][name] = value
 
     def register_buffer(self, name, tensor, persistent=True):
-        self._set_member(name, tensor, "buffer", persistent=persistent)
+        self._set_member(name, tensor, "buffer", persistent=bool(persistent))
 
     def register_parameter(self, name, tensor):
         self._set_member(name, tensor._data if isinstance(tensor, Parameter) else tensor, "parameter")
@@ -97,20 +109,21 @@ class Module:
 
     def __setattr__(self, name, value):
         if isinstance(value, Parameter):
-            self._set_member(name, value._data, "parameter")
-        elif isinstance(value, Module):
-            self._set_member(name, value, "module")
-        elif name in self._buffers:
-            self._set_member(name, value, "buffer", persistent=name not in self._non_persistent_buffers)
-        else:
-            self._set_member(name, value, "attribute")
+            return self._set_member(name, value._data, "parameter")
+        if isinstance(value, Module):
+            return self._set_member(name, value, "module")
+        if name in self._buffers:  # assignment to a buffer slot replaces the buffer, keeping its persistence
+            return self._set_member(name, value, "buffer", persistent=name not in self._non_persistent_buffers)
+        return self._set_member(name, value, "attribute")
 
     def __getattr__(self, name):
-        d = object.__getattribute__(self, "__dict__")
+        # Called only after normal lookup failed, i.e. for registered members (and during
+        # construction before __init__ ran, when the registries do not exist yet).
+        own = object.__getattribute__(self, "__dict__")
         for registry in ("_parameters", "_buffers", "_modules"):
-            table = d.get(registry)
-            if table is not None and name in table:
-                return table[name]
+            members = own.get(registry, ())
+            if name in members:
+                return members[name]
         raise AttributeError(f"'{type(self).__name__}' has no attribute '{name}'")
 
     # --------------------------------------------------------------- traversal

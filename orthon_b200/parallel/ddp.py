@@ -19,7 +19,7 @@ Parameters are broadcast from `src` at construction; buffers are not.
 (reference project: python/orthon/distributed/ddp.py:7-119)"""
 import weakref
 
-from ..distributed import _state
+from ..distributed import group as _group
 from .peer_reducer import PeerReducer
 from .reducer import Reducer
 
@@ -79,7 +79,7 @@ class DistributedDataParallel:
         _check_options(sync_grads, bucket_size_mb, overlap_grad_sync)
         self.module = module
         self._sync_grads = bool(sync_grads)
-        group = _state.get_active()
+        group = _group.active()
         owners = _trainable_owners(module)
         for _, parameter in owners:
             group.broadcast(parameter, src=src)

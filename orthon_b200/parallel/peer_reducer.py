@@ -73,6 +73,7 @@ class PeerReducer:
     # persistent GEMM CTA (see csrc/cuda/peer_reducer.cu).
     OVERLAP_THREADS = int(os.environ.get("ORTHON_PEER_OVERLAP_THREADS", 128))
     OVERLAP_CTAS = int(os.environ.get("ORTHON_PEER_OVERLAP_CTAS", 0))  # 0 = one per SM
+    SIDE_STREAM_UPDATE = os.environ.get("ORTHON_UPDATE_SIDE_STREAM", "1") != "0"  # single device: update beside backward
 
     @staticmethod
     def eligible(parameters, group):
@@ -388,6 +389,7 @@ class LocalFlatReducer(PeerReducer):
         if self.mode != "average":
             if b.seg is not None:
                 raise RuntimeError("per-parameter weight decay needs fused='reduce' on a single device")
+            beside_backward = beside_backward and self.SIDE_STREAM_UPDATE
             if beside_backward:
                 _C._stream_fence(self.device, 0, 1)  # the second stream waits for the gradients
             self._update_bucket(b, self.mode, self.hyper(), side_stream=beside_backward)

@@ -121,8 +121,8 @@ def nvls_reduce(rank, backend, dtype, n):
     os.environ["ORTHON_NVLS"] = "1"
     import orthon_b200.distributed as dist
     from orthon_b200 import _C
-    from orthon_b200.distributed import _state
-    be = _state.get_active().backend
+    from orthon_b200.distributed import group as _group
+    be = _group.active().backend
     ws = dist.get_world_size()
     dev = f"cuda:{rank}"
     esz = 4 if dtype == "float32" else 2
@@ -292,8 +292,8 @@ def found_inf_in_a_late_block(rank, backend, n):
     a high-numbered thread block reduces) must raise the found-inf word on every rank."""
     import orthon_b200.distributed as dist
     from orthon_b200 import _C
-    from orthon_b200.distributed import _state
-    be = _state.get_active().backend
+    from orthon_b200.distributed import group as _group
+    be = _group.active().backend
     ws = dist.get_world_size()
     dev = f"cuda:{rank}"
     flag_bytes = (_C._PEER_FLAG_BYTES + 255) & ~255
@@ -370,8 +370,8 @@ def missing_peer(rank, backend):
     and the group must stay failed; the other ranks, which were between steps, shut down normally."""
     import orthon_b200.distributed as dist
     from orthon_b200 import _C
-    from orthon_b200.distributed import _state
-    group = _state.get_active()
+    from orthon_b200.distributed import group as _group
+    group = _group.active()
     be = group.backend
     ws = dist.get_world_size()
     n = 1 << 16

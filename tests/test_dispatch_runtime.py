@@ -109,7 +109,7 @@ def test_pool_reuse_with_fake_devices(fake_cuda):
 
 
 def test_env_defaults_and_backend_registry(monkeypatch):
-    from orthon_b200.distributed import _env, get_backend_factory, register_backend
+    from orthon_b200.distributed import launch_env as _env, get_backend_factory, register_backend
     env = {"RANK": "3", "WORLD_SIZE": "8", "LOCAL_RANK": "3", "ORTHON_DISTRIBUTED_BACKEND": "nccl"}
     backend, kw = _env.apply_env_defaults(None, {}, env)
     assert backend == "nccl" and kw == {"rank": 3, "world_size": 8, "device": 3}
