@@ -35,6 +35,7 @@
 #include <unordered_map>
 
 #include "ob/cuda_common.cuh"
+#include "ob/gemm_plan.h"
 #include "ob/ops.h"
 #include "ob/tc05.cuh"
 
@@ -47,21 +48,24 @@ namespace {
 
 using namespace tc05;
 
-// Diagnostic route control: 0 = planner decides, 1 = force the SIMT kernel, 2 = require tcgen05.
-std::atomic<int> g_force_route{0};
-std::atomic<int> g_last_route{0};  // 1 = simt, 2 = tcgen05 128x128, 3 = tcgen05 128x256
-// float32 products: 0 = "highest" (every product on the exact float32 FMA kernel), 1 = "high" (large products as
-// bfloat16 piece products on the tensor cores).  Initial value from ORTHON_FLOAT32_MATMUL.
-std::atomic<int> g_f32_precision{-1};
-int f32_precision() {
-  int v = g_f32_precision.load(std::memory_order_relaxed);
-  if (v < 0) {
-    const char* e = std::getenv("ORTHON_FLOAT32_MATMUL");
-    v = (e != nullptr && std::string(e) == "high") ? 1 : 0;
-    g_f32_precision.store(v, std::memory_order_relaxed);
-  }
-  return v;
+// Planner options: the environment's values, read once, plus the settings that bindings can
+// change at run time (forced route for diagnostics, float32 precision, CTA-pair mode).
+std::atomic<int> g_force_route{0};     // 0 = planner decides, 1 = force the SIMT kernel, 2 = require tcgen05
+std::atomic<int> g_last_route{0};      // GemmRoute of the last product
+std::atomic<int> g_last_plan_bn{0};    // tile width of the last product
+std::atomic<int> g_f32_precision{-1};  // -1 = as the environment says
+std::atomic<int> g_pair_mode{-2};      // -2 = as the environment says
+GemmPlanOptions plan_options() {
+  static const GemmPlanOptions from_env = GemmPlanOptions::from_environment();
+  GemmPlanOptions o = from_env;
+  o.force_route = g_force_route.load(std::memory_order_relaxed);
+  const int f32 = g_f32_precision.load(std::memory_order_relaxed);
+  if (f32 >= 0) o.float32_precision = f32;
+  const int pair = g_pair_mode.load(std::memory_order_relaxed);
+  if (pair != -2) o.pair_mode = pair;
+  return o;
 }
+int f32_precision() { return plan_options().float32_precision; }
 
 constexpr int BM = 128;
 constexpr int BK = 64;
@@ -90,10 +94,12 @@ struct GemmParams {
 // TM = rows of the CTA tile: 128 (one MMA row block, accumulators double-buffered across tiles) or
 // 256 (two MMA row blocks share every B stage, which halves the B bytes fetched per flop; the two
 // accumulators are drained one after the other so the next tile can start on the first).
-template <int BN, int TM>
+// PAIR: the tile belongs to a pair of CTAs (cta_group::2): TM rows of A and BN / 2 columns of B
+// per CTA, 2 TM x BN outputs per pair.
+template <int BN, int TM, bool PAIR = false>
 struct SmemLayout {
   static constexpr int kABytes = TM * BK * 2;
-  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kBBytes = (PAIR ? BN / 2 : BN) * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kEpiBytes = kEpilogueWarps * 2 * 4096;  // two 32x64 staging tiles per epilogue warp
   static constexpr int kStages = (232448 - kEpiBytes - 256 - 1024) / kStageBytes > 6 ? 6 : (232448 - kEpiBytes - 256 - 1024) / kStageBytes;
@@ -115,13 +121,30 @@ __device__ __forceinline__ float gelu_grad(float z) {
 // EW = epilogue warps per MMA row block: 4, or 8 for 128-row tiles with short reductions, where
 // draining a 128 x 256 accumulator takes longer than computing the next one: two warps then share
 // each TMEM lane quarter and take half of the columns each.
-template <class T, int BN, int TM, int EW = kEpilogueWarps>
+//
+// PAIR = true is the two-CTA form (launched as clusters of two, TM = 128, BN = 256): the pair
+// computes a 256 x 256 tile with tcgen05.mma.cta_group::2.  CTA r of the pair loads rows
+// [r * 128, r * 128 + 128) of the A tile and columns [r * 128, r * 128 + 128) of the B tile (its
+// own non-multicast TMA loads, completion counted on the even CTA's barrier), holds the
+// accumulator rows of its A half in its own tensor memory (two 256-column accumulators, so the
+// epilogue of a tile overlaps the main loop of the next) and stores its own output rows.  The
+// even CTA issues every MMA and commits to both CTAs' barriers; each SM's tensor core reads 32 KB
+// of shared memory per 128 x 256 x 64 block instead of 48 KB, which is what a power-capped GPU
+// converts into clock.
+template <class T, int BN, int TM, int EW = kEpilogueWarps, bool PAIR = false>
 __global__ void __launch_bounds__(gemm_threads(TM, EW), 1)
 gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_z, GemmParams p) {
-  using L = SmemLayout<BN, TM>;
+  using L = SmemLayout<BN, TM, PAIR>;
   constexpr int H = TM / BM;  // MMA row blocks per tile
   static_assert(EW == 4 || (EW == 8 && H == 1 && BN == 256), "eight epilogue warps are for the 128 x 256 tile");
+  static_assert(!PAIR || BN == 256, "the pair form is a (2 TM) x 256 tile over two CTAs");
+  constexpr int TILE_M = PAIR ? 2 * TM : TM;        // rows of the scheduling tile
+  constexpr int BNC = PAIR ? BN / 2 : BN;           // B columns this CTA loads
+  const uint32_t crank = PAIR ? cluster_ctarank() : 0u;
+  const bool leader = crank == 0;
+  const long long first_tile = PAIR ? blockIdx.x / 2 : blockIdx.x;
+  const long long tile_step = PAIR ? gridDim.x / 2 : gridDim.x;
   constexpr bool kSplitCols = EW == 8;        // two warps per lane quarter, half of the columns each
   constexpr bool kOneStage = H == 2 || EW == 8;  // one 4 KB staging tile per epilogue warp
   extern __shared__ uint8_t smem_raw[];
@@ -134,7 +157,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (p.M + TM - 1) / TM, tiles_n = (p.N + BN - 1) / BN;
+  const int tiles_m = (p.M + TILE_M - 1) / TILE_M, tiles_n = (p.N + BN - 1) / BN;
   const int tiles_per_batch = tiles_m * tiles_n;
   const long long total_tiles = static_cast<long long>(tiles_per_batch) * p.nb0 * p.nb1;
   const int num_kb = (p.K + BK - 1) / BK;
@@ -144,12 +167,13 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < L::kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], EW); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], PAIR ? 2 * EW : EW); }
     mbar_init_fence();
   }
   if (warp == 1) tmem_alloc(tmem_slot, 2 * BN);
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -173,28 +197,36 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      // Pair form: the bytes of both CTAs are counted on the even CTA's barrier of the stage.
+      const uint32_t pair_full0 = PAIR ? mapa_u32(smem_u32(&full_bar[0]), 0u) : 0u;
+      for (long long t = first_tile; t < total_tiles && ok; t += tile_step) {
         int bidx, tm, tn;
         decode_tile(t, bidx, tm, tn);
         const int b0 = bidx / p.nb1, b1 = bidx - b0 * p.nb1;
         const int a0 = p.a_bc ? 0 : b0, a1 = p.a_bc ? 0 : b1, c0 = p.b_bc ? 0 : b0, c1 = p.b_bc ? 0 : b1;
+        const int row_a = tm * TILE_M + static_cast<int>(crank) * TM, col_b = tn * BN + static_cast<int>(crank) * BNC;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.err, kErrProducer)) { ok = false; break; }
-          mbar_expect_tx(&full_bar[stage], L::kStageBytes);
+          if (leader) mbar_expect_tx(&full_bar[stage], PAIR ? 2 * L::kStageBytes : L::kStageBytes);
           uint8_t* sa = smem + stage * L::kStageBytes;
           uint8_t* sb = sa + L::kABytes;
           const int k0 = kb * BK;
+          const uint32_t pair_full = pair_full0 + stage * 8;
+          auto load = [&](uint8_t* dst, const CUtensorMap* map, int x, int y, int z, int w) {
+            if (PAIR) tma_load_4d_pair(dst, map, pair_full, x, y, z, w);
+            else tma_load_4d(dst, map, &full_bar[stage], x, y, z, w);
+          };
           if (!p.a_mn) {
-            tma_load_4d(sa, &map_a, &full_bar[stage], k0, tm * TM, a1, a0);
+            load(sa, &map_a, k0, row_a, a1, a0);
           } else {
 #pragma unroll
-            for (int c = 0; c < TM / 64; ++c) tma_load_4d(sa + c * (BK * 128), &map_a, &full_bar[stage], tm * TM + c * 64, k0, a1, a0);
+            for (int c = 0; c < TM / 64; ++c) load(sa + c * (BK * 128), &map_a, row_a + c * 64, k0, a1, a0);
           }
           if (!p.b_mn) {
-            tma_load_4d(sb, &map_b, &full_bar[stage], k0, tn * BN, c1, c0);
+            load(sb, &map_b, k0, col_b, c1, c0);
           } else {
 #pragma unroll
-            for (int c = 0; c < BN / 64; ++c) tma_load_4d(sb + c * (BK * 128), &map_b, &full_bar[stage], tn * BN + c * 64, k0, c1, c0);
+            for (int c = 0; c < BNC / 64; ++c) load(sb + c * (BK * 128), &map_b, col_b + c * 64, k0, c1, c0);
           }
           if (++stage == L::kStages) { stage = 0; phase ^= 1; }
         }
@@ -202,17 +234,26 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   } else if (warp == 1) {
     // --------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      // Instruction descriptor: fp32 accumulate, A/B format, majors, N>>3, M>>4.
+    if (lane == 0 && leader) {
+      // Instruction descriptor: fp32 accumulate, A/B format, majors, N>>3, M>>4 (256 rows for a pair).
       const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
       const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(p.a_mn) << 15) |
                              (static_cast<uint32_t>(p.b_mn) << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
-                             (static_cast<uint32_t>(BM >> 4) << 24);
+                             (static_cast<uint32_t>((PAIR ? 2 * BM : BM) >> 4) << 24);
+      // Pair form: every commit goes to this CTA's barrier and to the peer's.
+      const uint32_t peer_empty0 = PAIR ? mapa_u32(smem_u32(&empty_bar[0]), 1u) : 0u;
+      const uint32_t peer_tmem_full0 = PAIR ? mapa_u32(smem_u32(&tmem_full[0]), 1u) : 0u;
+      // Descriptors are built once; every other one is this plus an offset in 16-byte units (the
+      // issuing thread has about 500 tensor cycles per 64-wide K block to spend, and rebuilding
+      // eight descriptors per block used most of them).
+      const uint64_t da0 = p.a_mn ? make_desc(smem_u32(smem), BK * 128, 1024) : make_desc(smem_u32(smem), 16, 1024);
+      const uint64_t db0 = p.b_mn ? make_desc(smem_u32(smem) + L::kABytes, BK * 128, 1024) : make_desc(smem_u32(smem) + L::kABytes, 16, 1024);
+      const uint32_t a_step = p.a_mn ? 2048u >> 4 : 32u >> 4, b_step = p.b_mn ? 2048u >> 4 : 32u >> 4;  // one K = 16 slice
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       int it = 0;
-      for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+      for (long long t = first_tile; t < total_tiles && ok; t += tile_step, ++it) {
         const uint32_t empty_parity = (use_of(it) & 1) ^ 1;
         for (int kb = 0; kb < num_kb && ok; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, p.err, kErrMma)) { ok = false; break; }
@@ -224,24 +265,29 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if (!ok) break;
             tc_fence_after();
           }
-          const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
-          const uint32_t sb = sa + L::kABytes;
+          const uint64_t da_s = da0 + static_cast<uint32_t>(stage * (L::kStageBytes >> 4));
+          const uint64_t db_s = db0 + static_cast<uint32_t>(stage * (L::kStageBytes >> 4));
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t db = p.b_mn ? make_desc(sb + k * 2048, BK * 128, 1024) : make_desc(sb + k * 32, 16, 1024);
+            const uint64_t db = db_s + k * b_step;
 #pragma unroll
             for (int h = 0; h < H; ++h) {
-              const uint32_t sah = sa + h * (BM * BK * 2);  // 128 rows further in either operand major
-              const uint64_t da = p.a_mn ? make_desc(sah + k * 2048, BK * 128, 1024) : make_desc(sah + k * 32, 16, 1024);
-              umma_f16(tmem_base + slot_of(it, h) * BN, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+              const uint64_t da = da_s + k * a_step + h * ((BM * BK * 2) >> 4);  // 128 rows further in either operand major
+              if (PAIR) umma_f16_pair(tmem_base + slot_of(it, h) * BN, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+              else umma_f16(tmem_base + slot_of(it, h) * BN, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
             }
           }
-          umma_commit(&empty_bar[stage]);  // frees the slot once these MMAs have read it
+          // Frees the slot (in both CTAs of a pair) once these MMAs have read it.
+          if (PAIR) { umma_commit_pair(smem_u32(&empty_bar[stage])); umma_commit_pair(peer_empty0 + stage * 8); }
+          else umma_commit(&empty_bar[stage]);
           if (++stage == L::kStages) { stage = 0; phase ^= 1; }
         }
         if (ok) {
 #pragma unroll
-          for (int h = 0; h < H; ++h) umma_commit(&tmem_full[slot_of(it, h)]);
+          for (int h = 0; h < H; ++h) {
+            if (PAIR) { umma_commit_pair(smem_u32(&tmem_full[slot_of(it, h)])); umma_commit_pair(peer_tmem_full0 + slot_of(it, h) * 8); }
+            else umma_commit(&tmem_full[slot_of(it, h)]);
+          }
         }
       }
     }
@@ -274,7 +320,9 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     constexpr int kSubs = BN / 32;
     const int sub_begin = kSplitCols ? my_h * (kSubs / 2) : 0, sub_end = kSplitCols ? sub_begin + kSubs / 2 : kSubs;
     int buf = 0;
-    for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+    // Pair form: the even CTA's MMA thread waits for the epilogue warps of both CTAs.
+    const uint32_t pair_tmem_empty0 = PAIR ? mapa_u32(smem_u32(&tmem_empty[0]), 0u) : 0u;
+    for (long long t = first_tile; t < total_tiles && ok; t += tile_step, ++it) {
       int bidx, tm, tn;
       decode_tile(t, bidx, tm, tn);
       const int b0 = bidx / p.nb1, b1 = bidx - b0 * p.nb1;
@@ -284,7 +332,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int acc = slot_of(it, h);
       if (!mbar_wait(&tmem_full[acc], use_of(it) & 1, p.err, kErrEpilogue)) { ok = false; break; }
       tc_fence_after();
-      const int row0 = tm * TM + h * BM + quarter * 32;
+      const int row0 = tm * TILE_M + static_cast<int>(crank) * TM + h * BM + quarter * 32;
       const int row = row0 + lane;
       const bool row_ok = row < p.M;
       const long long c_off = b0 * p.c_bs0 + b1 * p.c_bs1 + static_cast<long long>(row) * p.ldc;
@@ -440,7 +488,10 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (lane == 0) {
+        if (PAIR) mbar_arrive_cluster(pair_tmem_empty0 + acc * 8);
+        else mbar_arrive(&tmem_empty[acc]);
+      }
       }  // row block
     }
     if (staged) {
@@ -451,6 +502,9 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
   tc_fence_before();
   __syncthreads();
+  // Neither CTA of a pair may leave (or give up its tensor memory) while the other can still
+  // arrive on its barriers or while pair MMAs that write both tensor memories are in flight.
+  if (PAIR) cluster_sync_all();
   if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
 }
 
@@ -781,6 +835,7 @@ CUtensorMap make_map(const OperandView& o, bool mn_major, int box_rows, int nb0,
 
 std::mutex g_err_mu;
 int* g_err_flag[64] = {};
+int g_pair_clusters[64] = {};  // CTA pairs the device keeps resident at once (0 = not asked yet)
 
 int* error_flag(int device) {
   std::lock_guard<std::mutex> lock(g_err_mu);
@@ -799,12 +854,9 @@ struct Epilogue {
 
 template <class T>
 void launch_simt(const OperandView& a, const OperandView& b, Tensor& C, int M, int N, int K, int nb0, int nb1,
-                 long long ldc, long long c_bs0, long long c_bs1, const Epilogue& ep, cudaStream_t st) {
+                 long long ldc, long long c_bs0, long long c_bs1, const Epilogue& ep, cudaStream_t st, bool big) {
   const long long ldr = ep.residual.defined() ? ldc : 0;
-  // Large tiles once they fill the GPU at least once over; small problems keep the 64 x 64 tile
-  // for the sake of parallelism.
-  const long long big_tiles = static_cast<long long>((N + 127) / 128) * ((M + 127) / 128) * nb0 * nb1;
-  if (M >= 128 && N >= 128 && K >= 256 && big_tiles >= sm_count_for(C)) {  // short reductions do not amortise the 64-register prologue / epilogue
+  if (big) {  // the planner's choice: see plan_gemm
     dim3 grid128((N + 127) / 128, (M + 127) / 128, nb0 * nb1);
     gemm_simt128_kernel<T><<<grid128, 256, 0, st>>>(
         static_cast<const T*>(a.ptr), static_cast<const T*>(b.ptr), C.data_as<T>(), M, N, K, a.s_mn, a.s_k, b.s_k, b.s_mn, ldc,
@@ -823,14 +875,14 @@ void launch_simt(const OperandView& a, const OperandView& b, Tensor& C, int M, i
   check_launch("gemm (SIMT)");
 }
 
-template <class T, int BN, int TM, int EW = kEpilogueWarps>
+template <class T, int BN, int TM, int EW = kEpilogueWarps, bool PAIR = false>
 void launch_tc05(const OperandView& a, const OperandView& b, bool a_mn, bool b_mn, Tensor& C, int M, int N, int K,
                  int nb0, int nb1, long long ldc, long long c_bs0, long long c_bs1, const Epilogue& ep, cudaStream_t st,
                  bool out_f32 = false, DType out_f32_operands = DType::BF16) {
-  using L = SmemLayout<BN, TM>;
+  using L = SmemLayout<BN, TM, PAIR>;
   const DType dt = out_f32 ? out_f32_operands : C.dtype();  // operand type of the tensor maps
   const CUtensorMap ma = make_map(a, a_mn, TM, nb0, nb1, dt);
-  const CUtensorMap mb = make_map(b, b_mn, BN, nb0, nb1, dt);
+  const CUtensorMap mb = make_map(b, b_mn, PAIR ? BN / 2 : BN, nb0, nb1, dt);
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.nb0 = nb0; p.nb1 = nb1; p.a_mn = a_mn; p.b_mn = b_mn;
   p.a_bc = a.bcast ? 1 : 0; p.b_bc = b.bcast ? 1 : 0; p.bias_rows = ep.bias_rows ? 1 : 0;
@@ -864,13 +916,41 @@ void launch_tc05(const OperandView& a, const OperandView& b, bool a_mn, bool b_m
   p.tma_store = tma_store ? 1 : 0;
   static std::once_flag once;
   std::call_once(once, [] {
-    OB_CUDA(cudaFuncSetAttribute(gemm_tc05_kernel<T, BN, TM, EW>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    OB_CUDA(cudaFuncSetAttribute(gemm_tc05_kernel<T, BN, TM, EW, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
   });
-  const long long tiles = static_cast<long long>((M + TM - 1) / TM) * ((N + BN - 1) / BN) * nb0 * nb1;
-  const int grid = static_cast<int>(std::min<long long>(tiles, sm_count_for(C)));
-  gemm_tc05_kernel<T, BN, TM, EW><<<grid, gemm_threads(TM, EW), L::kTotal, st>>>(ma, mb, mc, mz, p);
-  check_launch("gemm_tc05");
+  constexpr int kTileRows = PAIR ? 2 * TM : TM;
+  const long long tiles = static_cast<long long>((M + kTileRows - 1) / kTileRows) * ((N + BN - 1) / BN) * nb0 * nb1;
+  if (!PAIR) {
+    const int grid = static_cast<int>(std::min<long long>(tiles, sm_count_for(C)));
+    gemm_tc05_kernel<T, BN, TM, EW, PAIR><<<grid, gemm_threads(TM, EW), L::kTotal, st>>>(ma, mb, mc, mz, p);
+    check_launch("gemm_tc05");
+    return;
+  }
+  // Clusters of two CTAs; as many clusters as the device can keep resident at once (SMs that
+  // cannot be paired inside their GPC stay idle), each walking the tile list with that stride.
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cfg.blockDim = dim3(gemm_threads(TM, EW));
+  cfg.dynamicSmemBytes = L::kTotal;
+  cfg.stream = st;
+  int& resident = g_pair_clusters[C.device().index];
+  if (resident == 0) {
+    cfg.gridDim = dim3(2 * static_cast<unsigned>(sm_count_for(C) / 2));
+    int n = 0;
+    OB_CUDA(cudaOccupancyMaxActiveClusters(&n, gemm_tc05_kernel<T, BN, TM, EW, PAIR>, &cfg));
+    resident = std::max(1, n);
+  }
+  cfg.gridDim = dim3(2 * static_cast<unsigned>(std::min<long long>(tiles, resident)));
+  OB_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc05_kernel<T, BN, TM, EW, PAIR>, ma, mb, mc, mz, p));
+  check_launch("gemm_tc05 (CTA pairs)");
 }
+
 
 // Shared driver for Matmul and Linear.  `A`/`B` are the stored tensors, flags select op().
 void gemm_dispatch(const Tensor& A_in, bool ta, const Tensor& B_in, bool tb, Tensor& C, const Epilogue& ep, cudaStream_t st) {
@@ -899,59 +979,17 @@ void gemm_dispatch(const Tensor& A_in, bool ta, const Tensor& B_in, bool tb, Ten
   const long long c_bs0 = nbd == 2 ? C.strides()[0] : 0, c_bs1 = nbd >= 1 ? C.strides()[nbd - 1] : 0;
   const DType dt = C.dtype();
 
-  const int force = g_force_route.load(std::memory_order_relaxed);
-  if (dt == DType::F32) {
-    // Under the "high" float32 precision setting, large products go through the tensor cores as
-    // six bfloat16 piece products (see split3_kernel); small ones, and epilogues with a residual
-    // or a stored pre-activation, stay on the float32 FMA kernel, as does everything under the
-    // default "highest" setting.  The piece products are exact, but tensor memory accumulates by
-    // truncation, once per 16 elements of the reduction: the relative error grows to about
-    // 1.3e-8 * K (1e-5 at K = 1024) where the FMA kernel stays near 1e-6.
-    static const long long split_min = [] { const char* e = std::getenv("ORTHON_GEMM_F32_SPLIT_MIN"); return e ? std::atoll(e) : (1LL << 22); }();
-    const bool can_split = Runtime::instance().cuda(C.device().index).supports_tcgen05() && !ep.residual.defined() &&
-                           !ep.preact.defined() && ep.act <= 2 && static_cast<long long>(K) * 6 + 8 < (1LL << 31);
-    const bool split = can_split && force != 1 && (force == 2 || (f32_precision() == 1 && static_cast<long long>(M) * N * K >= split_min));
-    if (!split) {
-      if (force == 2) throw std::runtime_error("matmul diagnostics: this float32 problem cannot take the tcgen05 route");
-      g_last_route.store(1, std::memory_order_relaxed);
-      launch_simt<float>(a, b, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);
-      return;
-    }
-    const int Kp = static_cast<int>((static_cast<long long>(K) * 6 + 7) / 8 * 8);
-    auto split_operand = [&](const OperandView& o, int role, Tensor& holder) {
-      const int nb = o.bcast ? 1 : nb0 * nb1;
-      holder = Tensor::empty({static_cast<int64_t>(nb), o.mn, static_cast<int64_t>(Kp)}, DType::BF16, C.device());
-      if (Kp != K * 6) OB_CUDA(cudaMemsetAsync(holder.data(), 0, holder.nbytes(), st));
-      const int mn_fast = (o.s_mn == 1 && o.s_k != 1) ? 1 : 0;
-      dim3 grid(static_cast<unsigned>((o.k + 31) / 32), static_cast<unsigned>((o.mn + 31) / 32), static_cast<unsigned>(nb));
-      auto* dst = static_cast<__nv_bfloat16*>(holder.data());
-      const auto* src = static_cast<const float*>(o.ptr);
-      const long long sb0 = o.bcast ? 0 : o.bs0, sb1 = o.bcast ? 0 : o.bs1;
-      const int inner_nb = o.bcast ? 1 : nb1;
-      if (role == 0) split3_kernel<0><<<grid, dim3(32, 8), 0, st>>>(src, dst, static_cast<int>(o.mn), static_cast<int>(o.k), o.s_mn, o.s_k, sb0, sb1, inner_nb, Kp, mn_fast);
-      else split3_kernel<1><<<grid, dim3(32, 8), 0, st>>>(src, dst, static_cast<int>(o.mn), static_cast<int>(o.k), o.s_mn, o.s_k, sb0, sb1, inner_nb, Kp, mn_fast);
-      check_launch("gemm float32 split");
-      OperandView v{};
-      v.ptr = holder.data();
-      v.mn = o.mn; v.k = Kp; v.s_mn = Kp; v.s_k = 1;
-      v.bs1 = o.bcast ? 0 : o.mn * static_cast<long long>(Kp);
-      v.bs0 = o.bcast ? 0 : v.bs1 * nb1;
-      v.bcast = o.bcast;
-      return v;
-    };
-    Tensor a_pieces, b_pieces;
-    if (a.mn > 65535LL * 32 || b.mn > 65535LL * 32) throw std::invalid_argument("matmul: float32 operand too tall for the split kernel grid");
-    const OperandView a6 = split_operand(a, 0, a_pieces), b6 = split_operand(b, 1, b_pieces);
-    const bool wide32 = N > 128;
-    g_last_route.store(wide32 ? 3 : 2, std::memory_order_relaxed);
-    if (wide32) launch_tc05<__nv_bfloat16, 256, 128>(a6, b6, false, false, C, M, N, Kp, nb0, nb1, ldc, c_bs0, c_bs1, ep, st, true);
-    else launch_tc05<__nv_bfloat16, 128, 128>(a6, b6, false, false, C, M, N, Kp, nb0, nb1, ldc, c_bs0, c_bs1, ep, st, true);
-    return;
-  }
-  // Operands that TMA cannot describe are packed once (the packed copy is K-major).
-  const bool tiny = static_cast<long long>(M) * N * K < (1LL << 18) && force != 2;
-  bool use_tc = !tiny && force != 1 && Runtime::instance().cuda(C.device().index).supports_tcgen05();
-  if (use_tc) {
+  GemmProblem prob;
+  prob.dtype = dt;
+  prob.m = M; prob.n = N; prob.k = K;
+  prob.batch = static_cast<int64_t>(nb0) * nb1;
+  prob.has_bias = ep.bias.defined(); prob.has_residual = ep.residual.defined(); prob.has_preact = ep.preact.defined();
+  prob.act = ep.act;
+  prob.tcgen05 = Runtime::instance().cuda(C.device().index).supports_tcgen05();
+  prob.sms = sm_count_for(C);
+  GemmPlanOptions opts = plan_options();
+  if (dt != DType::F32 && prob.tcgen05 && opts.force_route != 1 && (static_cast<long long>(M) * N * K >= (1LL << 18) || opts.force_route == 2)) {
+    // Operands that TMA cannot describe are packed once (the packed copy is K-major).
     if (!tma_compatible(a, nb0, nb1)) {
       A = Tensor::empty(A.shape(), A.dtype(), A.device());
       strided_copy_cuda(A_in, A, st);
@@ -962,90 +1000,96 @@ void gemm_dispatch(const Tensor& A_in, bool ta, const Tensor& B_in, bool tb, Ten
       strided_copy_cuda(B_in, B, st);
       b = view_of(B, tb, false);
     }
-    use_tc = tma_compatible(a, nb0, nb1) && tma_compatible(b, nb0, nb1);
+    prob.tma_ok = tma_compatible(a, nb0, nb1) && tma_compatible(b, nb0, nb1);
   }
-  if (!use_tc) {
-    if (force == 2) throw std::runtime_error("matmul diagnostics: this problem cannot take the tcgen05 route");
-    g_last_route.store(1, std::memory_order_relaxed);
-    if (dt == DType::BF16) launch_simt<__nv_bfloat16>(a, b, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);
-    else launch_simt<__half>(a, b, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);
-    return;
-  }
+  GemmPlan plan = plan_gemm(prob, opts);
   const bool a_mn = !(a.s_k == 1 || (a.k == 1 && a.s_mn != 1));
   const bool b_mn = !(b.s_k == 1 || (b.k == 1 && b.s_mn != 1));
-  // Split-K: a small output with a long reduction (weight gradients of a narrow model: 512 x 512
-  // over 16384 tokens) gives the persistent grid a handful of tiles.  The reduction is then cut
-  // into S slices that run as S batch entries of the same kernel (the slice index is a batch
-  // stride along K), float32 partials go to scratch and a second pass adds them in a fixed order.
-  {
-    static const int splitk_off = [] { const char* e = std::getenv("ORTHON_GEMM_SPLITK"); return (e != nullptr && e[0] == '0') ? 1 : 0; }();
-    const long long sms = sm_count_for(C);
-    const long long tiles_wide = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256);
-    const bool plain = !ep.bias.defined() && !ep.residual.defined() && !ep.preact.defined() && ep.act == 0;
-    int splits = 1;
-    if (!splitk_off && plain && nb0 * nb1 == 1 && N % 4 == 0 && tiles_wide * 4 <= sms && K >= 4096) {
-      while (splits < 32 && tiles_wide * splits * 2 <= sms && K % (splits * 2 * 64) == 0 && K / (splits * 2) >= 512) splits *= 2;
-    }
-    if (splits > 1) {
-      const long long Ks = K / splits;
-      OperandView as = a, bs = b;
-      as.k = Ks; bs.k = Ks;
-      as.bs1 = Ks * a.s_k; bs.bs1 = Ks * b.s_k;
-      as.bs0 = 0; bs.bs0 = 0;
-      as.bcast = false; bs.bcast = false;
-      if (tma_compatible(as, 1, splits) && tma_compatible(bs, 1, splits)) {
-        Tensor partial = Tensor::empty({static_cast<int64_t>(splits), static_cast<int64_t>(M), static_cast<int64_t>(N)}, DType::F32, C.device());
-        Epilogue none;
-        const long long mn = static_cast<long long>(M) * N;
-        const bool wide_s = N > 128 && tiles_wide * splits * 2 > sms;
-        g_last_route.store(wide_s ? 3 : 2, std::memory_order_relaxed);
+  if (plan.route == GemmRoute::Tc05SplitK) {
+    // The K slices run as batch entries of the same kernel (the slice index is a batch stride along
+    // K); float32 partials go to scratch and a second pass adds them in a fixed order.
+    const int splits = plan.splits;
+    const long long Ks = K / splits;
+    OperandView as = a, bs = b;
+    as.k = Ks; bs.k = Ks;
+    as.bs1 = Ks * a.s_k; bs.bs1 = Ks * b.s_k;
+    as.bs0 = 0; bs.bs0 = 0;
+    as.bcast = false; bs.bcast = false;
+    if (tma_compatible(as, 1, splits) && tma_compatible(bs, 1, splits)) {
+      Tensor partial = Tensor::empty({static_cast<int64_t>(splits), static_cast<int64_t>(M), static_cast<int64_t>(N)}, DType::F32, C.device());
+      Epilogue none;
+      const long long mn = static_cast<long long>(M) * N;
+      g_last_route.store(static_cast<int>(plan.route), std::memory_order_relaxed);
+      g_last_plan_bn.store(plan.bn, std::memory_order_relaxed);
 #define OB_SPLITK_LAUNCH(TT)                                                                                                   \
   do {                                                                                                                         \
-    if (wide_s) launch_tc05<TT, 256, 128>(as, bs, a_mn, b_mn, partial, M, N, static_cast<int>(Ks), 1, splits, N, 0, mn, none, st, true, dt); \
-    else launch_tc05<TT, 128, 128>(as, bs, a_mn, b_mn, partial, M, N, static_cast<int>(Ks), 1, splits, N, 0, mn, none, st, true, dt);        \
-    splitk_reduce_kernel<TT><<<ew_grid(mn / 4 + 1, 256, static_cast<int>(sms)), 256, 0, st>>>(                                \
+    if (plan.bn == 256) launch_tc05<TT, 256, 128>(as, bs, a_mn, b_mn, partial, M, N, static_cast<int>(Ks), 1, splits, N, 0, mn, none, st, true, dt); \
+    else launch_tc05<TT, 128, 128>(as, bs, a_mn, b_mn, partial, M, N, static_cast<int>(Ks), 1, splits, N, 0, mn, none, st, true, dt);      \
+    splitk_reduce_kernel<TT><<<ew_grid(mn / 4 + 1, 256, prob.sms), 256, 0, st>>>(                                             \
         partial.data_as<float>(), C.data_as<TT>(), splits, mn, N, ldc);                                                        \
   } while (0)
-        if (dt == DType::BF16) OB_SPLITK_LAUNCH(__nv_bfloat16);
-        else OB_SPLITK_LAUNCH(__half);
+      if (dt == DType::BF16) OB_SPLITK_LAUNCH(__nv_bfloat16);
+      else OB_SPLITK_LAUNCH(__half);
 #undef OB_SPLITK_LAUNCH
-        check_launch("gemm_tc05 (split-K)");
-        return;
-      }
+      check_launch("gemm_tc05 (split-K)");
+      return;
     }
+    opts.splitk = false;  // the slices are not TMA-describable: plan again without them
+    plan = plan_gemm(prob, opts);
   }
-  // Tile width: 256 columns whenever the problem is wider than one 128-column tile.  Narrow tiles
-  // fill the last wave of the persistent grid better but run at about two thirds of the wide
-  // tile's rate (measured on 8192 x 2048 x 8192: 900 against 1330 TFLOP/s), so they pay only when
-  // the wide tiling would leave at least half of the SMs without a tile: then twice as many
-  // narrow tiles still fit in one wave and each finishes sooner.
-  bool wide = N > 128;
-  {
-    static const int force_bn = [] { const char* e = std::getenv("ORTHON_GEMM_BN"); return e ? std::atoi(e) : 0; }();
-    const long long tiles_wide = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256) * nb0 * nb1;
-    if (force_bn == 128 || (force_bn != 256 && wide && tiles_wide * 2 <= sm_count_for(C))) wide = false;
+  g_last_route.store(static_cast<int>(plan.route), std::memory_order_relaxed);
+  g_last_plan_bn.store(plan.bn, std::memory_order_relaxed);
+  switch (plan.route) {
+    case GemmRoute::Simt64:
+    case GemmRoute::Simt128:
+      if (dt == DType::F32) launch_simt<float>(a, b, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st, plan.route == GemmRoute::Simt128);
+      else if (dt == DType::BF16) launch_simt<__nv_bfloat16>(a, b, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st, plan.route == GemmRoute::Simt128);
+      else launch_simt<__half>(a, b, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st, plan.route == GemmRoute::Simt128);
+      return;
+    case GemmRoute::Tc05Float32: {
+      // A' = [hi | hi | mid | mid | hi | lo], B' = [hi | mid | hi | mid | lo | hi] along K (see split3_kernel).
+      const int Kp = static_cast<int>((static_cast<long long>(K) * 6 + 7) / 8 * 8);
+      auto split_operand = [&](const OperandView& o, int role, Tensor& holder) {
+        const int nb = o.bcast ? 1 : nb0 * nb1;
+        holder = Tensor::empty({static_cast<int64_t>(nb), o.mn, static_cast<int64_t>(Kp)}, DType::BF16, C.device());
+        if (Kp != K * 6) OB_CUDA(cudaMemsetAsync(holder.data(), 0, holder.nbytes(), st));
+        const int mn_fast = (o.s_mn == 1 && o.s_k != 1) ? 1 : 0;
+        dim3 grid(static_cast<unsigned>((o.k + 31) / 32), static_cast<unsigned>((o.mn + 31) / 32), static_cast<unsigned>(nb));
+        auto* dst = static_cast<__nv_bfloat16*>(holder.data());
+        const auto* src = static_cast<const float*>(o.ptr);
+        const long long sb0 = o.bcast ? 0 : o.bs0, sb1 = o.bcast ? 0 : o.bs1;
+        const int inner_nb = o.bcast ? 1 : nb1;
+        if (role == 0) split3_kernel<0><<<grid, dim3(32, 8), 0, st>>>(src, dst, static_cast<int>(o.mn), static_cast<int>(o.k), o.s_mn, o.s_k, sb0, sb1, inner_nb, Kp, mn_fast);
+        else split3_kernel<1><<<grid, dim3(32, 8), 0, st>>>(src, dst, static_cast<int>(o.mn), static_cast<int>(o.k), o.s_mn, o.s_k, sb0, sb1, inner_nb, Kp, mn_fast);
+        check_launch("gemm float32 split");
+        OperandView v{};
+        v.ptr = holder.data();
+        v.mn = o.mn; v.k = Kp; v.s_mn = Kp; v.s_k = 1;
+        v.bs1 = o.bcast ? 0 : o.mn * static_cast<long long>(Kp);
+        v.bs0 = o.bcast ? 0 : v.bs1 * nb1;
+        v.bcast = o.bcast;
+        return v;
+      };
+      Tensor a_pieces, b_pieces;
+      if (a.mn > 65535LL * 32 || b.mn > 65535LL * 32) throw std::invalid_argument("matmul: float32 operand too tall for the split kernel grid");
+      const OperandView a6 = split_operand(a, 0, a_pieces), b6 = split_operand(b, 1, b_pieces);
+      if (plan.bn == 256) launch_tc05<__nv_bfloat16, 256, 128>(a6, b6, false, false, C, M, N, Kp, nb0, nb1, ldc, c_bs0, c_bs1, ep, st, true);
+      else launch_tc05<__nv_bfloat16, 128, 128>(a6, b6, false, false, C, M, N, Kp, nb0, nb1, ldc, c_bs0, c_bs1, ep, st, true);
+      return;
+    }
+    default:
+      break;
   }
-  g_last_route.store(wide ? 3 : 2, std::memory_order_relaxed);
-  // 256-row tiles (two MMA row blocks per B stage) when the reduction is long enough to amortise
-  // their epilogue, which overlaps the next tile only partly (measured: K >= 2048) and they fill the waves of the persistent
-  // grid at least to 80 %.
-  static const int force_tm = [] { const char* e = std::getenv("ORTHON_GEMM_TM"); return e ? std::atoi(e) : 0; }();
-  const long long sms = sm_count_for(C);
-  const long long tiles256 = static_cast<long long>((M + 255) / 256) * ((N + 255) / 256) * nb0 * nb1;
-  const double eff256 = static_cast<double>(tiles256) / static_cast<double>(((tiles256 + sms - 1) / sms) * sms);
-  static const int tall_min_k = [] { const char* e = std::getenv("ORTHON_GEMM_TALL_MIN_K"); return e ? std::atoi(e) : 2048; }();
-  const bool tall = wide && force_tm != 128 && !ep.preact.defined() &&
-                    (force_tm == 256 || (M >= 512 && K >= tall_min_k && eff256 >= 0.8));
-  if (tall) g_last_route.store(3, std::memory_order_relaxed);
-  // Short reductions: the epilogue, not the MMA loop, sets the pace of a tile; eight warps drain it.
-  static const int short_k_max = [] { const char* e = std::getenv("ORTHON_GEMM_EW8_MAX_K"); return e ? std::atoi(e) : 1024; }();
-  const bool short_k = !tall && K <= short_k_max && !ep.preact.defined();
-#define OB_GEMM_LAUNCH(TT)                                                                                           \
-  do {                                                                                                               \
-    if (tall) launch_tc05<TT, 256, 256>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);          \
-    else if (wide && short_k) launch_tc05<TT, 256, 128, 8>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st); \
-    else if (wide) launch_tc05<TT, 256, 128>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);     \
-    else launch_tc05<TT, 128, 128>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);               \
+  const bool pair = plan.route == GemmRoute::Tc05Pair;
+#define OB_GEMM_LAUNCH(TT)                                                                                                    \
+  do {                                                                                                                        \
+    if (pair && plan.tm == 256) launch_tc05<TT, 256, 256, 4, true>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st); \
+    else if (pair && plan.epilogue_warps == 8) launch_tc05<TT, 256, 128, 8, true>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st); \
+    else if (pair) launch_tc05<TT, 256, 128, 4, true>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);      \
+    else if (plan.tm == 256) launch_tc05<TT, 256, 256>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);     \
+    else if (plan.bn == 256 && plan.epilogue_warps == 8) launch_tc05<TT, 256, 128, 8>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st); \
+    else if (plan.bn == 256) launch_tc05<TT, 256, 128>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);     \
+    else launch_tc05<TT, 128, 128>(a, b, a_mn, b_mn, C, M, N, K, nb0, nb1, ldc, c_bs0, c_bs1, ep, st);                         \
   } while (0)
   if (dt == DType::BF16) OB_GEMM_LAUNCH(__nv_bfloat16);
   else OB_GEMM_LAUNCH(__half);
@@ -1091,6 +1135,9 @@ bool tc05_encode_map(CUtensorMap* out, DType dt, int rank, void* base, const uin
   return encode_cached(out, dt, rank, base, d, s, b, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
 }
 
+// CTA pairs of the pair-form GEMM that are resident at once on `device` (0 before its first launch).
+int gemm_pair_clusters(int device) { return g_pair_clusters[device]; }
+
 // (hits, misses) of the tensor-map cache since the process started.
 void tensor_map_cache_stats(long long* hits, long long* misses) {
   *hits = g_map_hits.load(std::memory_order_relaxed);
@@ -1102,7 +1149,16 @@ void tensor_map_cache_stats(long long* hits, long long* misses) {
 void set_gemm_route(int route) { g_force_route.store(route, std::memory_order_relaxed); }
 void set_float32_matmul_precision(int level) { g_f32_precision.store(level ? 1 : 0, std::memory_order_relaxed); }
 int float32_matmul_precision() { return f32_precision(); }
-int last_gemm_route() { return g_last_route.load(std::memory_order_relaxed); }
+void set_gemm_pair_mode(int mode) { g_pair_mode.store(mode, std::memory_order_relaxed); }
+// Route of the last product in the numbering the diagnostics expose: 1 = SIMT, 2 = tcgen05 with
+// 128-column tiles, 3 = tcgen05 with 256-column tiles, 4 = tcgen05 CTA pairs.
+int last_gemm_route() {
+  const int route = g_last_route.load(std::memory_order_relaxed);
+  if (route == 0) return 0;
+  if (route <= static_cast<int>(GemmRoute::Simt128)) return 1;
+  if (route == static_cast<int>(GemmRoute::Tc05Pair)) return 4;
+  return g_last_plan_bn.load(std::memory_order_relaxed) == 256 ? 3 : 2;
+}
 
 // Reads and clears the GEMM error word of a device (0 = no error).  Synchronizes the device.
 int take_gemm_error(int device) {

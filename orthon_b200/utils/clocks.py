@@ -27,7 +27,7 @@ class ClockSampler:
         return False
 
     def _finish(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        out = {"sm_mhz": None, "sm_max_mhz": None, "power_w": None, "reasons": [], "samples": 0}
         if self._proc is None:
             return out
         self._proc.terminate()
@@ -36,7 +36,7 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self._proc.kill()
             text, _ = self._proc.communicate()
-        clocks, reasons = [], set()
+        clocks, watts, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for line in text.splitlines():
             cells = [c.strip() for c in line.split(",")]
@@ -47,10 +47,16 @@ class ClockSampler:
                 out["sm_max_mhz"] = float(cells[2])
             except ValueError:
                 continue
+            try:
+                watts.append(float(cells[3]))
+            except ValueError:
+                pass
             for name, cell in zip(names, cells[5:9]):
                 if cell.lower() == "active":
                     reasons.add(name)
         if clocks:
             out["sm_mhz"] = statistics.median(clocks)
+        if watts:
+            out["power_w"] = statistics.median(watts)
         out["reasons"], out["samples"] = sorted(reasons), len(clocks)
         return out
