@@ -71,7 +71,7 @@ class PeerReducer:
     NVLS_MIN_WORLD = int(os.environ.get("ORTHON_NVLS_MIN_WORLD", 0))
     # Block size of launches that run beside a backward pass: small enough to share an SM with a
     # persistent GEMM CTA (see csrc/cuda/peer_reducer.cu).
-    OVERLAP_THREADS = int(os.environ.get("ORTHON_PEER_OVERLAP_THREADS", 128))
+    OVERLAP_THREADS = int(os.environ.get("ORTHON_PEER_OVERLAP_THREADS", 512))
     OVERLAP_CTAS = int(os.environ.get("ORTHON_PEER_OVERLAP_CTAS", 0))  # 0 = one per SM
     SIDE_STREAM_UPDATE = os.environ.get("ORTHON_UPDATE_SIDE_STREAM", "1") != "0"  # single device: update beside backward
 
@@ -169,7 +169,7 @@ class PeerReducer:
         status, found_inf = self.backend.status_tensors()
         _C._stream_fence(self.device, 0, 1)  # communication stream waits for the gradients
         fused = self.mode != "average"
-        with trace_range(f"peer_reduce bucket {i}", self.device):
+        with trace_range(f"peer_reduce bucket {i}", self.device, 1):
             _C._peer_reduce(self.rank, self.world, self.device, b.grads, b.staging, b.flags, b.n, b.dtype,
                             self.backend.next_epoch(), scale, self.mode, oneshot,
                             master=b.master_flat if fused else None, m=b.m_flat if self.mode == "adam" else None,
@@ -398,8 +398,8 @@ class LocalFlatReducer(PeerReducer):
 
     def _update_bucket(self, b, kind, h, side_stream=False):
         model = b.param_flat if b.master_flat is not b.param_flat else None
-        stream, threads = (1, PeerReducer.OVERLAP_THREADS) if side_stream else (0, 0)
-        with _no_grad(), trace_range(f"optimizer bucket {kind}", self.device):
+        stream, threads = (1, 256) if side_stream else (0, 0)
+        with _no_grad(), trace_range(f"optimizer bucket {kind}", self.device, stream):
             if kind == "adam":
                 _C._adam_step_(b.master_flat, b.m_flat, b.v_flat, b.grad_flat, model, h["lr"], h["beta1"], h["beta2"], h["eps"],
                                h.get("weight_decay", 0.0), h["bias_c1"], h["bias_c2"], h.get("grad_scale", 1.0), stream, threads)

@@ -1,13 +1,20 @@
 """Lightweight tracing: named ranges with CUDA-event device times, off unless enabled.
 
-    enable_tracing(True)
-    with trace_range("bucket 3"):
+    enable_tracing(True)                 # or ORTHON_TRACE=1 in the environment
+    with trace_range("bucket 3", device, stream_kind=1):
         ...
     for name, ms in collected_ranges(): ...
+    for name, stream, start_ms, end_ms in timeline(): ...   # offsets from the first recorded event
+
+The reducers wrap every bucket launch (communication stream) and the optimizers every step in a
+range, so with tracing on a training step yields a timeline that shows which reductions ran
+beside the backward pass and which were left for its tail.  Ranges cost two event records each and
+nothing when tracing is off.
 """
+import os
 from contextlib import contextmanager
 
-_enabled = False
+_enabled = os.environ.get("ORTHON_TRACE", "0") not in ("", "0")
 _ranges = []
 
 
@@ -17,26 +24,52 @@ def enable_tracing(on=True):
     _ranges.clear()
 
 
+def tracing_enabled():
+    return _enabled
+
+
 @contextmanager
-def trace_range(name, device=0):
+def trace_range(name, device=0, stream_kind=0):
     if not _enabled:
         yield
         return
     from .. import _C
     if _C.cuda_available():
-        start = _C.CudaEvent.record(device)
-        yield
-        stop = _C.CudaEvent.record(device)
-        _ranges.append((name, start, stop))
+        start = _C.CudaEvent.record(device, stream_kind)
+        try:
+            yield
+        finally:
+            _ranges.append((name, stream_kind, start, _C.CudaEvent.record(device, stream_kind)))
     else:
         import time
         t0 = time.perf_counter()
-        yield
-        _ranges.append((name, None, (time.perf_counter() - t0) * 1e3))
+        try:
+            yield
+        finally:
+            _ranges.append((name, stream_kind, None, (time.perf_counter() - t0) * 1e3))
 
 
 def collected_ranges():
+    """(name, duration in ms) of every finished range, in completion order."""
     out = []
-    for name, start, stop in _ranges:
+    for name, _, start, stop in _ranges:
         out.append((name, stop if start is None else stop.elapsed_ms_since(start)))
     return out
+
+
+def timeline():
+    """(name, stream kind, start ms, end ms) relative to the earliest recorded range start.
+    Waits for the device."""
+    rows = [r for r in _ranges if r[2] is not None]
+    if not rows:
+        return []
+    for _, _, _, stop in rows:
+        stop.synchronize()
+    base = rows[0][2]
+    offsets = [(name, kind, start.elapsed_ms_since(base), stop.elapsed_ms_since(base)) for name, kind, start, stop in rows]
+    shift = min(o[2] for o in offsets)
+    return [(name, kind, a - shift, b - shift) for name, kind, a, b in offsets]
+
+
+def clear_ranges():
+    _ranges.clear()

@@ -324,7 +324,8 @@ def participation(rank, backend, case):
     """Rank-divergent participation on the default (non-overlapped) schedule.
     case 'partial': only rank 0 uses head b -> idle ranks contribute zeros, all get the average.
     case 'unused' : nobody uses head b -> its gradient stays None everywhere.
-    case 'invalid': rank 0 assigns a gradient of the wrong shape -> every rank is told."""
+    case 'invalid': the optimizer update is fused into the reduction and rank 0 has no gradient
+                    for head b -> no rank applies the step and every rank is told."""
     import orthon_b200 as ob
     import orthon_b200.distributed as dist
     from orthon_b200 import nn
@@ -347,20 +348,30 @@ def participation(rank, backend, case):
     ddp = dist.DDP(model, sync_grads=False, bucket_size_mb=1)
     x = ob.from_numpy(np.random.default_rng(3).standard_normal((2, 4)).astype(np.float32))
     x = x if dev == "cpu" else x.to(dev)
-    ddp.zero_grad()
-    ddp(x, case == "partial" and rank == 0).sum().backward()
-    error = None
-    if case == "invalid" and rank == 0:
-        bad = ob.from_numpy(np.zeros((5, 3), dtype=np.float32))
-        model.a.weight.set_grad(bad if dev == "cpu" else bad.to(dev))
-    try:
-        ddp.all_reduce_gradients()
-        ddp.wait_for_gradient_sync()
-    except RuntimeError as exc:
-        error = str(exc)
+    error, unchanged = None, None
+    if case == "invalid":
+        opt = ob.amp.MixedPrecisionOptimizer(ddp, ob.optim.SGD, fused="update", lr=0.5)
+        before = _flat_params(model)
+        opt.zero_grad()
+        ddp(x, rank != 0).sum().backward()
+        try:
+            opt.step()
+            ddp.wait_for_gradient_sync()
+        except RuntimeError as exc:
+            error = str(exc)
+        ob.cuda_synchronize()
+        unchanged = bool(np.array_equal(before, _flat_params(model)))
+    else:
+        ddp.zero_grad()
+        ddp(x, case == "partial" and rank == 0).sum().backward()
+        try:
+            ddp.all_reduce_gradients()
+            ddp.wait_for_gradient_sync()
+        except RuntimeError as exc:
+            error = str(exc)
     dist.barrier()
     gb = model.b.weight.grad
-    return {"error": error, "b": None if gb is None else gb.numpy().tolist(),
+    return {"error": error, "b": None if gb is None else gb.numpy().tolist(), "unchanged": unchanged,
             "a": None if error else model.a.weight.grad.numpy().tolist(), "reducer": type(ddp._reducer).__name__}
 
 

@@ -131,8 +131,10 @@ def test_participation_consensus(world):
     for r in res:
         assert r["error"] is None and r["b"] is None and r["a"] is not None
     res = dist.spawn(W.participation, args=("p2p", "invalid"), nprocs=world, backend="p2p")
-    for r in res:
-        assert r["error"] is not None and "rejected an invalid gradient profile" in r["error"]
+    assert "needs a gradient for every parameter" in res[0]["error"]          # the rank that lacks the gradient
+    for r in res[1:]:
+        assert "rejected an invalid gradient profile" in r["error"]           # everybody else is told
+    assert all(r["unchanged"] for r in res)                                   # and nobody applied the step
 
 
 @pytest.mark.parametrize("world", _worlds(2))
