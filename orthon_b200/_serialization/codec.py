@@ -68,7 +68,8 @@ class Decoder:
         shape, dtype, nbytes = node.get("shape"), node.get("dtype"), node.get("nbytes")
         digest, payload = node.get("sha256"), node.get("payload")
         if (not isinstance(shape, list) or not all(type(d) is int and d >= 0 for d in shape)
-                or dtype not in _DTYPE_SIZES or type(nbytes) is not int or nbytes < 0 or not isinstance(digest, str)):
+                or dtype not in _DTYPE_SIZES or type(nbytes) is not int or nbytes < 0 or not isinstance(digest, str)
+                or len(digest) != 64):
             fail(f"{where}: malformed tensor record")
         count = 1
         for d in shape:
@@ -81,7 +82,7 @@ class Decoder:
         data = self._read(payload, nbytes, where)
         if hashlib.sha256(data).hexdigest() != digest:
             fail(f"{where}: payload checksum mismatch")
-        return _C._tensor_from_bytes(data, shape if shape else [1], dtype)
+        return _C._tensor_from_bytes(data, shape, dtype)
 
     def decode(self, node, where):
         if not isinstance(node, dict) or "k" not in node:

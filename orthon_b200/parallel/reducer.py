@@ -85,6 +85,10 @@ class Reducer:
             return True
         if g.dtype not in _ELEMENT_BYTES:
             return False
+        # Averaging scales the gradient in place in its own dtype: the CPU backend does that for
+        # float32 / float64 only, the CUDA backend for float32 / float16 / bfloat16.
+        if g.dtype not in (("float32", "float16", "bfloat16") if g.device.is_cuda() else ("float32", "float64")):
+            return False
         try:
             self.group.validate_gradient_dtype(g.dtype)
         except (RuntimeError, ValueError, NotImplementedError):

@@ -57,6 +57,33 @@ def test_no_alloc_sum_matches_pool_backed_sum_twice():
         assert abs(got - float(host.astype(np.float64).sum())) <= 1e-6 * scale
 
 
+def test_no_alloc_sum_edge_cases():
+    """The branches the main test does not reach: an input that is not 16-byte aligned (element
+    by element instead of four at a time), an empty input, and a size large enough that the
+    number of partials hits its ceiling of 1024 and every block walks several chunks."""
+    fn = _entry()
+    rng = np.random.default_rng(7)
+    out = _C._empty_on([1], "float32", "cuda:0")
+    host = rng.standard_normal(100_001).astype(np.float32)
+    x = _C.from_numpy(host).to("cuda:0")
+    shifted = _C._view_flat(x, 1, [100_000])                 # starts 4 bytes past a 16-byte boundary
+    assert shifted._data_ptr % 16 == 4
+    code, message = _call(fn, shifted, out)
+    assert code == 0, message
+    want = float(host[1:].astype(np.float64).sum())
+    assert abs(out.tolist()[0] - want) <= 1e-6 * float(np.abs(host).sum())
+    err = ctypes.create_string_buffer(256)
+    out.fill_(5.0)
+    code = fn(x._data_ptr, 0, out._data_ptr, _C._cuda_stream_handle(0), err, 256)   # n = 0: the sum of nothing
+    assert code == 0 and out.tolist()[0] == 0.0
+    n = 4096 * 1024 * 2 + 13                                   # more than 1024 chunks of 4096 elements
+    big = rng.standard_normal(n).astype(np.float32)
+    xb = _C.from_numpy(big).to("cuda:0")
+    code, message = _call(fn, xb, out)
+    assert code == 0, message
+    assert abs(out.tolist()[0] - float(big.astype(np.float64).sum())) <= 1e-6 * float(np.abs(big).sum())
+
+
 def test_no_alloc_sum_rejects_bad_requests():
     fn = _entry()
     out = _C._empty_on([1], "float32", "cuda:0")
