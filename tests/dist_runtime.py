@@ -338,7 +338,7 @@ def manual_gradients(rank):
 
 def amp_rounds(rank, mode):
     """Three AMP rounds with hand-set gradients on different parameters per rank.  'enabled':
-    rank 1 overflows in round 1; 'disabled' / 'direct': no scaling."""
+    rank 1 overflows in the second cycle; 'disabled' / 'direct': no scaling."""
     import orthon_b200 as ob
     import orthon_b200.distributed as dist
     from orthon_b200 import nn
