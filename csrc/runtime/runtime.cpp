@@ -265,6 +265,13 @@ Allocation MemoryPool::acquire(Device dev, size_t bytes, StreamHandle stream) {
         break;
       }
       if (!usable) continue;
+      // The block's last owner may still have work queued on its stream that touches the block
+      // (release does not record an event for the owning stream: same-stream reuse, the common
+      // case, needs none).  Handing it to another stream therefore orders that stream after
+      // everything the old one has queued so far: an event recorded now covers it.
+      if (dev.is_cuda() && c.stream != nullptr && stream != nullptr && c.stream != stream) {
+        CompletionToken::record_on(dev.index, c.stream).enqueue_wait_on(stream);
+      }
       ptr = c.ptr;
       got = c.capacity;
       stats_.cached_bytes -= got;
