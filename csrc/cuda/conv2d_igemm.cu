@@ -137,6 +137,7 @@ std::atomic<int> g_conv_last{0};   // 1 = direct, 2 = tcgen05 lowering
 void set_conv_route(int route) { g_conv_force.store(route, std::memory_order_relaxed); }
 int last_conv_route() { return g_conv_last.load(std::memory_order_relaxed); }
 void note_conv_route(int route) { g_conv_last.store(route, std::memory_order_relaxed); }
+int conv_forced_route() { return g_conv_force.load(std::memory_order_relaxed); }
 
 bool conv_igemm_enabled(const Tensor& x, const Geom* unused = nullptr) {
   (void)unused;

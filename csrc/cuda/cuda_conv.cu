@@ -13,7 +13,15 @@ namespace cu {
 template <class T> bool conv_fprop_igemm(OpCall& c);
 template <class T> bool conv_dgrad_igemm(OpCall& c);
 template <class T> bool conv_wgrad_igemm(OpCall& c);
-void note_conv_route(int route);  // diagnostics: 1 = direct kernels, 2 = tcgen05 lowering
+// Implicit GEMM (gather in the producer, no column matrix): 16-bit types only.
+template <class T> bool conv_fprop_tc05(OpCall& c);
+template <class T> bool conv_dgrad_tc05(OpCall& c);
+template <class T> bool conv_wgrad_tc05(OpCall& c);
+template <> inline bool conv_fprop_tc05<float>(OpCall&) { return false; }
+template <> inline bool conv_dgrad_tc05<float>(OpCall&) { return false; }
+template <> inline bool conv_wgrad_tc05<float>(OpCall&) { return false; }
+void note_conv_route(int route);  // diagnostics: 1 = direct kernels, 2 = tcgen05 lowering, 3 = tcgen05 implicit GEMM
+int conv_forced_route();
 
 namespace {
 
@@ -126,6 +134,7 @@ __global__ void conv_bgrad_kernel(const T* __restrict__ gy, T* __restrict__ db, 
 
 template <class T>
 void k_conv(OpCall& c) {
+  if (conv_forced_route() == 0 && conv_fprop_tc05<T>(c)) { note_conv_route(3); return; }
   if (conv_fprop_igemm<T>(c)) { note_conv_route(2); return; }
   note_conv_route(1);
   const ConvGeom g = geom_of(c.in[0].shape(), c.in[1].shape(), c.i);
@@ -136,6 +145,7 @@ void k_conv(OpCall& c) {
 
 template <class T>
 void k_conv_dgrad(OpCall& c) {
+  if (conv_forced_route() == 0 && conv_dgrad_tc05<T>(c)) { note_conv_route(3); return; }
   if (conv_dgrad_igemm<T>(c)) { note_conv_route(2); return; }
   note_conv_route(1);
   const ConvGeom g = geom_of(c.out[0].shape(), c.in[1].shape(), c.i);
@@ -146,6 +156,7 @@ void k_conv_dgrad(OpCall& c) {
 
 template <class T>
 void k_conv_wgrad(OpCall& c) {
+  if (conv_forced_route() == 0 && conv_wgrad_tc05<T>(c)) { note_conv_route(3); return; }
   if (conv_wgrad_igemm<T>(c)) { note_conv_route(2); return; }
   note_conv_route(1);
   const ConvGeom g = geom_of(c.in[1].shape(), c.out[0].shape(), c.i);

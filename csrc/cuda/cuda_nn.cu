@@ -318,22 +318,120 @@ __global__ void embedding_fwd_kernel(const I* __restrict__ idx, const T* __restr
   }
 }
 
-template <class T, class I>
-__global__ void embedding_bwd_kernel(const I* __restrict__ idx, const T* __restrict__ g, float* __restrict__ acc,
-                                     int64_t n, int64_t V, int64_t D) {
-  const int lane = threadIdx.x & 31;
-  const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-  for (int64_t i = warp; i < n; i += nwarps) {
-    const int64_t row = checked_index(idx, i, V);
-    for (int64_t j = lane; j < D; j += 32) atomicAdd(acc + row * D + j, to_f(g[i * D + j]));
+// Embedding backward, deterministic: dW[v] = sum over the positions i with idx[i] == v of g[i],
+// added in increasing i.  Three steps, no floating-point atomics:
+//   1. embedding_keys_kernel   validates the indices and writes (row, position) pairs;
+//   2. embedding_sort_kernel   one thread block sorts the pairs by row with a stable LSD radix
+//                              sort (8 bits per pass, as many passes as the vocabulary needs), so
+//                              positions stay in increasing order inside a row;
+//   3. embedding_segment_kernel one warp per pair; the warp whose pair starts a run of equal rows
+//                              walks the run and adds the gradient rows in float32 registers, eight
+//                              columns per lane at a time, then rounds once into dW.
+// Rows that no position names keep the zeros written before step 3.
+// (replaces the float32 atomicAdd scatter of the reference: src/backends/cuda/embedding_kernels.cu:65-148)
+template <class I>
+__global__ void embedding_keys_kernel(const I* __restrict__ idx, int* __restrict__ keys, int* __restrict__ pos, int64_t n, int64_t V) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    keys[i] = static_cast<int>(checked_index(idx, i, V));
+    pos[i] = static_cast<int>(i);
+  }
+}
+
+constexpr int kSortThreads = 1024;
+
+// Stable: within a tile of 1024 pairs a thread's rank among equal digits is its count of
+// lower-numbered threads with that digit (warp match + per-warp counts scanned in warp order),
+// and tiles are processed in order with running per-digit bases.
+__global__ void __launch_bounds__(kSortThreads) embedding_sort_kernel(int* __restrict__ keys_a, int* __restrict__ pos_a,
+                                                                      int* __restrict__ keys_b, int* __restrict__ pos_b, int n, int passes) {
+  __shared__ int base[256];
+  __shared__ int warp_count[kSortThreads / 32][256];
+  __shared__ int tile_total[256];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int *kin = keys_a, *pin = pos_a, *kout = keys_b, *pout = pos_b;
+  for (int pass = 0; pass < passes; ++pass) {
+    const int shift = pass * 8;
+    if (tid < 256) base[tid] = 0;
+    __syncthreads();
+    for (int i = tid; i < n; i += kSortThreads) atomicAdd(&base[(kin[i] >> shift) & 255], 1);  // integer counts: order-free
+    __syncthreads();
+    if (tid == 0) {  // exclusive scan of 256 counts
+      int run = 0;
+      for (int d = 0; d < 256; ++d) { const int c = base[d]; base[d] = run; run += c; }
+    }
+    __syncthreads();
+    for (int t0 = 0; t0 < n; t0 += kSortThreads) {
+      for (int j = tid; j < (kSortThreads / 32) * 256; j += kSortThreads) (&warp_count[0][0])[j] = 0;
+      __syncthreads();
+      const int i = t0 + tid;
+      const bool live = i < n;
+      const int key = live ? kin[i] : 0, p = live ? pin[i] : 0;
+      const int digit = (key >> shift) & 255;
+      const unsigned active = __ballot_sync(0xFFFFFFFFu, live);
+      int rank = 0;
+      if (live) {
+        const unsigned peers = __match_any_sync(active, digit);
+        rank = __popc(peers & ((1u << lane) - 1u));
+        if (rank == 0) warp_count[warp][digit] = __popc(peers);
+      }
+      __syncthreads();
+      if (tid < 256) {  // per digit: offsets of the warps inside the tile, in warp order
+        int run = 0;
+        for (int w = 0; w < kSortThreads / 32; ++w) { const int c = warp_count[w][tid]; warp_count[w][tid] = run; run += c; }
+        tile_total[tid] = run;
+      }
+      __syncthreads();
+      if (live) {
+        const int dst = base[digit] + warp_count[warp][digit] + rank;
+        kout[dst] = key;
+        pout[dst] = p;
+      }
+      __syncthreads();
+      if (tid < 256) base[tid] += tile_total[tid];
+      __syncthreads();
+    }
+    int* t = kin; kin = kout; kout = t;
+    t = pin; pin = pout; pout = t;
+    __syncthreads();
   }
 }
 
 template <class T>
-__global__ void f32_to_T_kernel(const float* __restrict__ a, T* __restrict__ o, int64_t n) {
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) o[i] = from_f<T>(a[i]);
+__global__ void embedding_segment_kernel(const int* __restrict__ keys, const int* __restrict__ pos, const T* __restrict__ g,
+                                         T* __restrict__ dw, int64_t n, int64_t D) {
+  constexpr int N = Pack<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int64_t j0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (j0 >= n) return;
+  const int row = keys[j0];
+  if (j0 > 0 && keys[j0 - 1] == row) return;  // not the head of its run
+  int64_t j1 = j0 + 1;
+  while (j1 < n && keys[j1] == row) ++j1;
+  T* out = dw + static_cast<int64_t>(row) * D;
+  const bool vec = (D % N == 0) && ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(dw)) & 15u) == 0;
+  if (vec) {
+    for (int64_t c0 = static_cast<int64_t>(lane) * N; c0 < D; c0 += 32 * N) {
+      float acc[N];
+#pragma unroll
+      for (int k = 0; k < N; ++k) acc[k] = 0.f;
+      for (int64_t j = j0; j < j1; ++j) {
+        const Pack<T> p = load_pack(g + static_cast<int64_t>(pos[j]) * D + c0);
+#pragma unroll
+        for (int k = 0; k < N; ++k) acc[k] += to_f(p.v[k]);
+      }
+      Pack<T> q;
+#pragma unroll
+      for (int k = 0; k < N; ++k) q.v[k] = from_f<T>(acc[k]);
+      store_pack(out + c0, q);
+    }
+  } else {
+    for (int64_t c = lane; c < D; c += 32) {
+      float acc = 0.f;
+      for (int64_t j = j0; j < j1; ++j) acc += to_f(g[static_cast<int64_t>(pos[j]) * D + c]);
+      out[c] = from_f<T>(acc);
+    }
+  }
 }
 
 template <class T>
@@ -355,23 +453,24 @@ void k_embedding_bwd(OpCall& c) {
   const int64_t n = idx.numel(), V = dw.shape()[0], D = dw.shape()[1];
   cudaStream_t st = stream_of(c);
   const int sms = sm_count_for(dw);
-  // Accumulate in float32 (directly in dW when it already is float32), then round once.
-  ScratchLease lease;
-  float* acc;
-  if (dw.dtype() == DType::F32) {
-    acc = dw.data_as<float>();
-  } else {
-    lease = ScratchLease(dw.device(), sizeof(float) * V * D, st);
-    acc = static_cast<float*>(lease.data());
-  }
-  OB_CUDA(cudaMemsetAsync(acc, 0, sizeof(float) * V * D, st));
-  const int grid = ew_grid(n * 32, kThreads, sms);
-  if (idx.dtype() == DType::I64)
-    embedding_bwd_kernel<T, int64_t><<<grid, kThreads, 0, st>>>(idx.data_as<int64_t>(), g.data_as<T>(), acc, n, V, D);
-  else
-    embedding_bwd_kernel<T, int32_t><<<grid, kThreads, 0, st>>>(idx.data_as<int32_t>(), g.data_as<T>(), acc, n, V, D);
-  if (dw.dtype() != DType::F32)
-    f32_to_T_kernel<T><<<ew_grid(V * D, kThreads, sms), kThreads, 0, st>>>(acc, dw.data_as<T>(), V * D);
+  OB_CUDA(cudaMemsetAsync(dw.data(), 0, dw.nbytes(), st));
+  if (n == 0) return;
+  if (n >= (int64_t(1) << 31) || V >= (int64_t(1) << 31)) throw std::invalid_argument("embedding backward: more than 2^31 - 1 indices or rows");
+  // Two (row, position) buffers for the ping-pong passes of the sort.
+  ScratchLease lease(dw.device(), sizeof(int) * 4 * static_cast<size_t>(n), st);
+  int* keys_a = static_cast<int*>(lease.data());
+  int *pos_a = keys_a + n, *keys_b = pos_a + n, *pos_b = keys_b + n;
+  const int grid = ew_grid(n, kThreads, sms);
+  if (idx.dtype() == DType::I64) embedding_keys_kernel<int64_t><<<grid, kThreads, 0, st>>>(idx.data_as<int64_t>(), keys_a, pos_a, n, V);
+  else embedding_keys_kernel<int32_t><<<grid, kThreads, 0, st>>>(idx.data_as<int32_t>(), keys_a, pos_a, n, V);
+  int passes = 1;
+  while (passes < 4 && (V - 1) >> (8 * passes)) ++passes;
+  embedding_sort_kernel<<<1, kSortThreads, 0, st>>>(keys_a, pos_a, keys_b, pos_b, static_cast<int>(n), passes);
+  const int* keys = (passes & 1) ? keys_b : keys_a;
+  const int* pos = (passes & 1) ? pos_b : pos_a;
+  const int64_t warps_per_block = kThreads / 32;
+  embedding_segment_kernel<T><<<static_cast<unsigned>((n + warps_per_block - 1) / warps_per_block), kThreads, 0, st>>>(
+      keys, pos, g.data_as<T>(), dw.data_as<T>(), n, D);
   check_launch("embedding backward");
 }
 

@@ -229,6 +229,49 @@ def test_conv_and_pool(dtype):
     close(xx.grad, t.grad, dtype)
 
 
+CONV_CASES = [
+    # (N, C, H, W, K, R, S, stride, pad): the three layers of the small CNN, then shapes that leave tiles partly empty
+    (8, 3, 32, 32, 32, 3, 3, 1, 1), (8, 32, 32, 32, 64, 3, 3, 2, 1), (8, 64, 16, 16, 128, 3, 3, 2, 1),
+    (2, 5, 12, 12, 7, 3, 3, 1, 1), (3, 4, 9, 11, 20, 3, 3, 2, 0), (1, 16, 8, 8, 24, 1, 1, 1, 0), (2, 6, 10, 10, 130, 3, 3, 1, 1),
+    (2, 40, 16, 16, 16, 5, 5, 1, 2), (5, 8, 20, 20, 8, 3, 3, 3, 1),
+    # strides larger than the filter: some input pixels are reached by no tap
+    (2, 8, 8, 8, 16, 1, 1, 2, 0), (2, 4, 9, 9, 8, 2, 2, 3, 0),
+]
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("case", CONV_CASES)
+def test_conv_implicit_gemm_forward_and_gradients(dtype, case):
+    N, C, H, W, K, R, S, stride, pad = case
+    rng = np.random.default_rng(sum(case))
+    x = rng.standard_normal((N, C, H, W)); w = rng.standard_normal((K, C, R, S)) * (1.0 / np.sqrt(C * R * S)); b = rng.standard_normal((K,))
+    xx, ww, bb = dev_tensor(x, dtype, True), dev_tensor(w, dtype, True), dev_tensor(b, dtype, True)
+    t, tw, tb = (ref_round(v_, dtype).requires_grad_(True) for v_ in (x, w, b))
+    y = _C.conv2d(xx, ww, bb, stride, stride, pad, pad)
+    assert _C._conv2d_last_route() == "tcgen05_implicit_gemm"
+    ty = torch.nn.functional.conv2d(t, tw, tb, stride=stride, padding=pad)
+    close(y, ty, dtype)
+    weight = rng.standard_normal(tuple(ty.shape))
+    gw = dev_tensor(weight, dtype)
+    (y * gw).sum().backward()
+    (ty * ref_round(weight, dtype)).sum().backward()
+    scale = 4 * np.sqrt(N * ty.shape[2] * ty.shape[3] / 64.0) + 4
+    close(xx.grad, t.grad, dtype, 4); close(ww.grad, tw.grad, dtype, scale); close(bb.grad, tb.grad, dtype, scale)
+    assert _C._cuda_index_errors() == 0
+
+
+def test_conv_skips_the_input_gradient_nobody_asked_for():
+    rng = np.random.default_rng(3)
+    xx = dev_tensor(rng.standard_normal((2, 3, 8, 8)), "bfloat16")            # does not require grad
+    ww = dev_tensor(rng.standard_normal((4, 3, 3, 3)), "bfloat16", True)
+    before = _C._kernel_launch_count()
+    y = _C.conv2d(xx, ww, None, 1, 1, 1, 1)
+    y.sum().backward()
+    assert xx.grad is None and ww.grad is not None
+    _C._conv2d_force_route("auto")
+    assert _C._kernel_launch_count() - before <= 12
+
+
 def test_adam_fused_matches_formula():
     rng = np.random.default_rng(11)
     p0, g = rng.standard_normal(1000), rng.standard_normal(1000)
@@ -276,7 +319,14 @@ def test_diagnostic_routes():
     xx, ww = dev_tensor(x, "bfloat16"), dev_tensor(w, "bfloat16")
     y_direct = diag.conv2d_direct(xx, ww, None, (1, 1), (1, 1))
     assert _C._conv2d_last_route() == "direct"
-    assert diag.conv2d_dispatch_path(xx, ww, None, (1, 1), (1, 1)) == "tcgen05_lowering"
+    assert diag.conv2d_dispatch_path(xx, ww, None, (1, 1), (1, 1)) == "tcgen05_implicit_gemm"
+    _C._conv2d_force_route("lowering")
+    try:
+        y_lowered = _C.conv2d(xx, ww, None, 1, 1, 1, 1)
+        assert _C._conv2d_last_route() == "tcgen05_lowering"
+    finally:
+        _C._conv2d_force_route("auto")
+    close(y_lowered, torch.nn.functional.conv2d(ref_round(x, "bfloat16"), ref_round(w, "bfloat16"), padding=1), "bfloat16")
     y_auto = _C.conv2d(xx, ww, None, 1, 1, 1, 1)
     ty = torch.nn.functional.conv2d(ref_round(x, "bfloat16"), ref_round(w, "bfloat16"), padding=1)
     close(y_direct, ty, "bfloat16"); close(y_auto, ty, "bfloat16")
@@ -423,3 +473,33 @@ def test_split_k_gemm_small_output_long_reduction(dtype):
     ob.matmul(txs, tw).sum().backward()
     expect = ref_round(xs, dtype).double().T @ torch.ones(16384, 512, dtype=torch.float64)
     close(tw.grad, expect.float(), dtype, scale=2.0)
+
+
+def test_embedding_backward_is_deterministic_and_sums_in_position_order():
+    """Many positions share few rows, so the order of the additions matters for the rounded
+    result: two runs must agree bit for bit and match a float32 reference that adds in
+    increasing position."""
+    rng = np.random.default_rng(12)
+    n, V, D = 4099, 37, 72
+    idx_np = rng.integers(0, V - 3, size=n).astype(np.int64)        # rows V-3.. stay untouched
+    g_np = rng.standard_normal((n, D)).astype(np.float32)
+    for dtype, tol in (("float32", 0.0), ("bfloat16", 0.0)):
+        w = _C.from_numpy(np.zeros((V, D), dtype=np.float32), dtype).to("cuda:0")
+        w.requires_grad_(True)
+        idx = _C.from_numpy(idx_np).to("cuda:0")
+        g = _C.from_numpy(g_np, dtype).to("cuda:0")
+        runs = []
+        for _ in range(2):
+            w.zero_grad()
+            (ob.embedding(idx, w) * g).sum().backward()
+            runs.append(w.grad.numpy().astype(np.float32).copy())
+        assert np.array_equal(runs[0], runs[1])
+        g_used = g.numpy().astype(np.float32)
+        want = np.zeros((V, D), dtype=np.float32)
+        for i in range(n):                                           # increasing position, float32 accumulation
+            want[idx_np[i]] += g_used[i]
+        if dtype == "bfloat16":
+            want = torch.tensor(want).to(torch.bfloat16).to(torch.float32).numpy()
+        assert np.array_equal(runs[0], want)
+        assert not runs[0][V - 3:].any()
+    assert _C._cuda_index_errors() == 0
