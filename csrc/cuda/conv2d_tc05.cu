@@ -27,6 +27,7 @@
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
+#include <vector>
 
 #include "ob/cuda_common.cuh"
 #include "ob/ops.h"
@@ -44,10 +45,8 @@ namespace {
 using namespace tc05;
 
 constexpr int kConvThreads = 256;
-constexpr int kStageGather = 256 * 128;   // up to 256 gathered rows of 128 bytes
-constexpr int kStageTma = 256 * 128;      // up to 256 TMA rows of 128 bytes
-constexpr int kStageBytes = kStageGather + kStageTma;
-constexpr int kConvSmem = 2 * kStageBytes + 1024 + 256;
+constexpr int kMaxStages = 4;
+constexpr int kConvSmemMax = 227 * 1024;
 enum : int { kErrConvWait = 21 };
 
 struct ConvParams {
@@ -62,6 +61,8 @@ struct ConvParams {
   void* out;                   // fprop: out, dgrad: dx, wgrad: float32 partials [splits][128][ldp]
   const void* bias;            // fprop
   int ldp;                     // wgrad: row length of the partials
+  int gather_bytes, stage_bytes, stages;   // one ring slot = gathered tile then TMA tile (both multiples of 1024 bytes)
+  int tmem_cols;               // accumulator columns to allocate: a power of two >= max(32, bn)
   int* err;
 };
 
@@ -105,25 +106,92 @@ __device__ __forceinline__ StrideClass stride_class(const ConvParams& p, int z) 
   return c;
 }
 
+// ---- the fast gather: 8 consecutive pixels that share an image and an output row
+// When the row length is a multiple of 8 every aligned group of 8 pixels has one window-corner row
+// y0, corner columns x0 + e * step and is wholly inside or wholly outside the problem.  Whether
+// column e is inside for horizontal tap tj does not depend on the plane or the vertical tap, so it
+// is worked out once per group: bit 8 * tj + e of `xm`.  A row of the gathered tile is then one
+// vertical test, one mask byte and 8 predicated loads at fixed offsets from one pointer.
 template <class T>
-__global__ void __launch_bounds__(kConvThreads, 1)
+struct Chunk {
+  const T* ptr;              // element under the window corner of pixel 0 in plane 0 (may point outside: only masked-in elements are read)
+  int y0;                    // corner row; kNoPixel for a group past the end of the problem
+  unsigned long long xm;
+};
+template <class T>
+__device__ __forceinline__ Chunk<T> make_chunk(const T* src, bool exists, int off0, int y0, int x0, int step, const GatherGeom& g) {
+  Chunk<T> c{src + off0, exists ? y0 : kNoPixel, 0ull};
+  for (int tj = 0; tj < g.ts; ++tj) {
+    unsigned m = 0;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) m |= (static_cast<unsigned>(x0 + e * step + g.sign * tj) < static_cast<unsigned>(g.xlim) ? 1u : 0u) << e;
+    c.xm |= static_cast<unsigned long long>(m) << (8 * tj);
+  }
+  return c;
+}
+template <class T>
+__device__ __forceinline__ uint4 gather8(const T* q, unsigned m, int step) {
+  Pack<T> pk;
+  const T zero = from_f<T>(0.f);
+  if (step == 1) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) pk.v[e] = (m >> e) & 1u ? q[e] : zero;
+  } else if (step == 2) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) pk.v[e] = (m >> e) & 1u ? q[2 * e] : zero;
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) pk.v[e] = (m >> e) & 1u ? q[e * step] : zero;
+  }
+  return *reinterpret_cast<uint4*>(&pk);
+}
+// A tap index as digits (plane a, vertical ti, horizontal tj) that is advanced by a fixed stride
+// without dividing.
+struct TapCursor {
+  int tap, a, ti, tj;
+};
+__device__ __forceinline__ TapCursor tap_cursor(int tap, const GatherGeom& g) {
+  const int per_plane = g.tr * g.ts;
+  TapCursor c;
+  c.tap = tap; c.a = tap / per_plane;
+  const int t2 = tap - c.a * per_plane;
+  c.ti = t2 / g.ts; c.tj = t2 - c.ti * g.ts;
+  return c;
+}
+__device__ __forceinline__ void advance(TapCursor& c, const TapCursor& by, const GatherGeom& g) {
+  c.tap += by.tap;
+  c.tj += by.tj;
+  if (c.tj >= g.ts) { c.tj -= g.ts; ++c.ti; }
+  c.ti += by.ti;
+  if (c.ti >= g.tr) { c.ti -= g.tr; ++c.a; }
+  c.a += by.a;
+}
+template <class T>
+__device__ __forceinline__ uint4 gather_row(const Chunk<T>& ch, const TapCursor& c, bool live, int step, const GatherGeom& g) {
+  const bool y_ok = static_cast<unsigned>(ch.y0 + g.sign * c.ti) < static_cast<unsigned>(g.ylim);
+  const unsigned m = (live && y_ok) ? static_cast<unsigned>(ch.xm >> (8 * c.tj)) & 0xffu : 0u;
+  return gather8<T>(ch.ptr + (c.a * g.plane + g.sign * (c.ti * g.rowlen + c.tj)), m, step);
+}
+
+template <class T, int MODE, bool FAST>
+__global__ void __launch_bounds__(kConvThreads, 2)
 conv_tc05_kernel(const __grid_constant__ CUtensorMap map_t, ConvParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + 2 * kStageBytes);
-  uint64_t* empty_bar = full_bar + 2;
-  uint64_t* done_bar = empty_bar + 2;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + p.stages * p.stage_bytes);
+  uint64_t* empty_bar = full_bar + kMaxStages;
+  uint64_t* done_bar = empty_bar + kMaxStages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int mode = p.mode;
+  constexpr int mode = MODE;
   const T* src = static_cast<const T*>(p.src);
 
   if (tid == 0) {
-    for (int s = 0; s < 2; ++s) { mbar_init(&full_bar[s], kConvThreads + 1); mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], kConvThreads + 1); mbar_init(&empty_bar[s], 1); }
     mbar_init(done_bar, 1);
     mbar_init_fence();
   }
-  if (warp == 4) tmem_alloc(tmem_slot, 256);
+  if (warp == 4) tmem_alloc(tmem_slot, p.tmem_cols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -137,7 +205,9 @@ conv_tc05_kernel(const __grid_constant__ CUtensorMap map_t, ConvParams p) {
                          (static_cast<uint32_t>(128 >> 4) << 24);
   const long long items = mode == 2 ? static_cast<long long>(p.tiles_n) * p.splits
                                     : static_cast<long long>(p.tiles_m) * p.tiles_n * p.classes;
-  unsigned kb_count = 0, tile_count = 0;   // running counters: ring slot and phase of every barrier
+  int stage = 0;                           // ring slot and its phase run on across items
+  uint32_t phase = 0;
+  unsigned tile_count = 0;
   bool ok = true;
 
   for (long long item = blockIdx.x; item < items && ok; item += gridDim.x) {
@@ -175,10 +245,26 @@ conv_tc05_kernel(const __grid_constant__ CUtensorMap map_t, ConvParams p) {
     // fprop / dgrad: this thread always gathers the same 8 consecutive pixels (chunk `tid & 15` of the
     // 128-pixel tile), for the rows `tid >> 4`, +16, +32, +48 of every reduction block.
     Pix fixed[8];
-    if (mode != 2) {
-      const long long mfirst = m0 + (tid & 15) * 8;
-      int img = static_cast<int>(mfirst / pix_per_img);
-      int rem = static_cast<int>(mfirst - static_cast<long long>(img) * pix_per_img);
+    Chunk<T> chunk8{};
+    TapCursor cur{}, stride_taps{};
+    const int step = mode == 1 ? 1 : p.sw;   // distance between the source columns of neighbouring pixels
+    if (FAST) {
+      stride_taps = tap_cursor(mode == 2 ? kConvThreads / 8 : 16, gg);
+      cur = tap_cursor(mode == 2 ? n0 + (tid >> 3) : (tid >> 4), gg);
+    }
+    if (FAST && mode != 2) {
+      const int mfirst = static_cast<int>(m0) + (tid & 15) * 8;
+      const int img = mfirst / pix_per_img, rem = mfirst - img * pix_per_img;
+      const int py = rem / row_pix, px = rem - py * row_pix;
+      const int y0 = mode == 0 ? py * p.sh - p.ph : py + sc.qa;
+      const int x0 = mode == 0 ? px * p.sw - p.pw : px + sc.qb;
+      const int off0 = mode == 0 ? img * p.C * HW + y0 * p.W + x0 : img * p.K * P + y0 * p.OW + x0;
+      chunk8 = make_chunk<T>(src, mfirst < m_total, off0, y0, x0, step, gg);
+    }
+    if (!FAST && mode != 2) {
+      const int mfirst = static_cast<int>(m0) + (tid & 15) * 8;   // the host admits only problems whose pixel counts fit an int
+      int img = mfirst / pix_per_img;
+      int rem = mfirst - img * pix_per_img;
       int py = rem / row_pix, px = rem - py * row_pix;
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
@@ -197,12 +283,10 @@ conv_tc05_kernel(const __grid_constant__ CUtensorMap map_t, ConvParams p) {
       }
     }
 
-    for (int kb = 0; kb < num_kb && ok; ++kb, ++kb_count) {
-      const int stage = kb_count & 1;
-      const uint32_t phase = (kb_count >> 1) & 1;
+    for (int kb = 0; kb < num_kb && ok; ++kb) {
       if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.err, kErrConvWait)) { ok = false; break; }
-      uint8_t* gat = smem + stage * kStageBytes;
-      uint8_t* tma = gat + kStageGather;
+      uint8_t* gat = smem + stage * p.stage_bytes;
+      uint8_t* tma = gat + p.gather_bytes;
       if (tid == 128) {
         // The operand that needs no gathering: weights (fprop, dgrad) or the output gradient (wgrad).
         if (mode != 2) {
@@ -218,8 +302,17 @@ conv_tc05_kernel(const __grid_constant__ CUtensorMap map_t, ConvParams p) {
       if (mode != 2) {
         // 64 rows (reduction taps) x 128 pixels: two 64-pixel halves of 8 KB each.
         const int chunk = tid & 15, half = chunk >> 3, c16 = chunk & 7;
-#pragma unroll 2
-        for (int j = 0; j < 4; ++j) {
+        if (FAST) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int row = (tid >> 4) + 16 * j;
+            const uint4 v = gather_row<T>(chunk8, cur, cur.tap < rows_total, step, gg);
+            advance(cur, stride_taps, gg);
+            *reinterpret_cast<uint4*>(gat + half * 8192 + row * 128 + ((c16 ^ (row & 7)) << 4)) = v;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < (FAST ? 0 : 4); ++j) {
           const int row = (tid >> 4) + 16 * j;
           const int tap = kb * 64 + row;
           Pack<T> pk;
@@ -240,8 +333,29 @@ conv_tc05_kernel(const __grid_constant__ CUtensorMap map_t, ConvParams p) {
         const int gkb = split * p.kb_per_split + kb;
         const int img = gkb / kb_img, off = (gkb - img * kb_img) * 64;
         const int c16 = tid & 7;
+        if (FAST) {
+          const int first = off + c16 * 8;
+          const int oh = first / p.OW, ow = first - oh * p.OW;
+          const int y0 = oh * p.sh - p.ph, x0 = ow * p.sw - p.pw;
+          const bool exists = img < p.N && first < P;
+          const Chunk<T> ch = make_chunk<T>(src, exists, img * p.C * HW + y0 * p.W + x0, y0, x0, step, gg);
+          const uint32_t one2 = std::is_same<T, __nv_bfloat16>::value ? 0x3f803f80u : 0x3c003c00u;
+          TapCursor c = cur;
+#pragma unroll 2
+          for (int row = tid >> 3; row < p.bn; row += kConvThreads / 8) {
+            uint4 v;
+            if (c.tap == rows_total - 1) {   // the column of ones: its product with the output gradient is the bias gradient
+              const uint32_t o = exists ? one2 : 0u;
+              v = make_uint4(o, o, o, o);
+            } else {
+              v = gather_row<T>(ch, c, c.tap < rows_total - 1, step, gg);
+            }
+            advance(c, stride_taps, gg);
+            *reinterpret_cast<uint4*>(gat + row * 128 + ((c16 ^ (row & 7)) << 4)) = v;
+          }
+        }
         Pix px[8];
-        {
+        if (!FAST) {
           const int first = off + c16 * 8;
           int oh = first / p.OW, ow = first - oh * p.OW;
 #pragma unroll
@@ -256,7 +370,7 @@ conv_tc05_kernel(const __grid_constant__ CUtensorMap map_t, ConvParams p) {
           }
         }
 #pragma unroll 1
-        for (int row = tid >> 3; row < p.bn; row += kConvThreads / 8) {
+        for (int row = tid >> 3; row < (FAST ? 0 : p.bn); row += kConvThreads / 8) {
           const int tap = n0 + row;
           Pack<T> pk;
           if (tap < rows_total - 1) {
@@ -288,6 +402,7 @@ conv_tc05_kernel(const __grid_constant__ CUtensorMap map_t, ConvParams p) {
         umma_commit(&empty_bar[stage]);
         if (kb == num_kb - 1) umma_commit(done_bar);
       }
+      if (++stage == p.stages) { stage = 0; phase ^= 1; }
     }
 
     // ---- epilogue: warps 0-3 own the four TMEM lane quarters
@@ -346,20 +461,30 @@ conv_tc05_kernel(const __grid_constant__ CUtensorMap map_t, ConvParams p) {
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem_base, 256);
+  if (warp == 4) tmem_dealloc(tmem_base, p.tmem_cols);
 }
 
-// wgrad second pass: dw[k, tap] and db[k] from the float32 partials, slices added in index order.
+// wgrad second pass: dw[k, tap] and db[k] from the float32 partials.  A block owns 32 consecutive
+// outputs; its 8 warps each add every 8th slice in index order and the 8 sums are added in warp
+// order, so the result does not depend on scheduling.
 template <class T>
-__global__ void conv_wgrad_finish_kernel(const float* __restrict__ partial, T* __restrict__ dw, T* __restrict__ db, int splits,
-                                         int K, int CRS, int ldp) {
+__global__ void __launch_bounds__(256) conv_wgrad_finish_kernel(const float* __restrict__ partial, T* __restrict__ dw, T* __restrict__ db,
+                                                                int splits, int K, int CRS, int ldp) {
+  __shared__ float part[8][32];
   const int total = K * (CRS + 1);
-  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-    const int k = i / (CRS + 1), tap = i - k * (CRS + 1);
-    float acc = 0.f;
-    for (int s = 0; s < splits; ++s) acc += partial[(static_cast<int64_t>(s) * 128 + k) * ldp + tap];
-    if (tap < CRS) dw[static_cast<int64_t>(k) * CRS + tap] = from_f<T>(acc);
-    else if (db != nullptr) db[k] = from_f<T>(acc);
+  const int i = blockIdx.x * 32 + (threadIdx.x & 31), g = threadIdx.x >> 5;
+  const int k = i < total ? i / (CRS + 1) : 0, tap = i < total ? i - k * (CRS + 1) : 0;
+  float acc = 0.f;
+  if (i < total)
+    for (int s = g; s < splits; s += 8) acc += partial[(static_cast<int64_t>(s) * 128 + k) * ldp + tap];
+  part[g][threadIdx.x & 31] = acc;
+  __syncthreads();
+  if (g == 0 && i < total) {
+    float sum = 0.f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) sum += part[q][threadIdx.x];
+    if (tap < CRS) dw[static_cast<int64_t>(k) * CRS + tap] = from_f<T>(sum);
+    else if (db != nullptr) db[k] = from_f<T>(sum);
   }
 }
 
@@ -415,13 +540,54 @@ bool fits_int32(const ConvParams& p) {
 
 int round16(int v) { return (v + 15) & ~15; }
 
-// One CTA per SM at most; each walks the work items with a stride of the grid.
-template <class T>
-void launch(const CUtensorMap& map, const ConvParams& p, long long items, int sms, cudaStream_t st) {
-  static const bool once = (cudaFuncSetAttribute(conv_tc05_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kConvSmem), true);
+int g_last_launch[4] = {0, 0, 0, 0};   // grid, dynamic shared memory, ring slots, CTAs per SM of the latest launch (diagnostics)
+
+int round1k(int v) { return (v + 1023) & ~1023; }
+
+// Ring geometry of a launch: as many slots as fit (2 to 4), kept under half of the shared memory
+// when three slots allow it so that two CTAs share an SM and one's gathers hide the other's waits.
+void plan_ring(ConvParams& p) {
+  const int rows_bytes = round1k(p.bn * 128);
+  p.gather_bytes = p.mode == 2 ? rows_bytes : 16384;
+  p.stage_bytes = p.gather_bytes + (p.mode == 2 ? 16384 : rows_bytes);
+  const int half = 110 * 1024, whole = kConvSmemMax - 2048;
+  const int budget = 3 * p.stage_bytes <= half ? half : whole;
+  p.stages = std::max(2, std::min(kMaxStages, budget / p.stage_bytes));
+  int cols = 32;
+  while (cols < p.bn) cols *= 2;
+  p.tmem_cols = cols;
+}
+
+// A persistent grid: as many CTAs as can be resident (shared memory, registers and the 512 columns
+// of tensor memory decide), each walking the work items with a stride of the grid.
+template <class T, int MODE, bool FAST>
+void launch_mode(const CUtensorMap& map, const ConvParams& p, long long items, int sms, cudaStream_t st) {
+  // The largest shared-memory carve-out, or a CTA that needs under half of it gets an SM configured for one CTA only.
+  static const bool once = (cudaFuncSetAttribute(conv_tc05_kernel<T, MODE, FAST>, cudaFuncAttributeMaxDynamicSharedMemorySize, kConvSmemMax),
+                            prefer_max_shared_carveout(conv_tc05_kernel<T, MODE, FAST>), true);
   (void)once;
-  const unsigned grid = static_cast<unsigned>(std::max<long long>(1, std::min<long long>(items, sms)));
-  conv_tc05_kernel<T><<<grid, kConvThreads, kConvSmem, st>>>(map, p);
+  const int smem = p.stages * p.stage_bytes + 1024 + 256;
+  // Registers allow two CTAs per SM (the launch bounds say so); shared memory and the 512 columns of tensor memory decide.
+  const int resident = std::max(1, std::min({2, kConvSmemMax / (smem + 1024), 512 / p.tmem_cols}));
+  const unsigned grid = static_cast<unsigned>(std::max<long long>(1, std::min<long long>(items, static_cast<long long>(sms) * resident)));
+  g_last_launch[0] = static_cast<int>(grid); g_last_launch[1] = smem; g_last_launch[2] = p.stages; g_last_launch[3] = resident;
+  conv_tc05_kernel<T, MODE, FAST><<<grid, kConvThreads, smem, st>>>(map, p);
+}
+// The fast gather needs groups of 8 pixels that never straddle an output row (for the input
+// gradient: a row of any stride class) and at most 8 horizontal taps.
+bool fast_gather(const ConvParams& p) {
+  if (p.S > 8) return false;
+  if (p.mode == 1) return p.W % (8 * p.sw) == 0;
+  return p.OW % 8 == 0;
+}
+
+template <class T>
+void launch(const CUtensorMap& map, ConvParams& p, long long items, int sms, cudaStream_t st) {
+  plan_ring(p);
+  const bool fast = fast_gather(p);
+  if (p.mode == 0) fast ? launch_mode<T, 0, true>(map, p, items, sms, st) : launch_mode<T, 0, false>(map, p, items, sms, st);
+  else if (p.mode == 1) fast ? launch_mode<T, 1, true>(map, p, items, sms, st) : launch_mode<T, 1, false>(map, p, items, sms, st);
+  else fast ? launch_mode<T, 2, true>(map, p, items, sms, st) : launch_mode<T, 2, false>(map, p, items, sms, st);
 }
 
 // Tensor map over `mats` row-major [rows, ld] matrices of 16-bit elements laid one after another:
@@ -434,6 +600,9 @@ bool matrix_map(CUtensorMap* out, DType dt, void* base, int inner, int rows, int
 }
 
 }  // namespace
+
+// {grid, dynamic shared memory bytes, ring slots, resident CTAs per SM} of the latest implicit-GEMM launch.
+std::vector<int> conv_tc05_last_launch() { return std::vector<int>(g_last_launch, g_last_launch + 4); }
 
 template <class T>
 bool conv_fprop_tc05(OpCall& c) {
@@ -517,7 +686,9 @@ bool conv_wgrad_tc05(OpCall& c) {
   const int kb_img = (P + 63) / 64;
   const long long kb_total = static_cast<long long>(p.N) * kb_img;
   // One wave of (column tile, reduction slice) items; a slice is at least 4 blocks of 64 pixels.
-  int splits = static_cast<int>(std::max<long long>(1, std::min<long long>((kb_total + 3) / 4, sms / p.tiles_n)));
+  plan_ring(p);
+  const int per_sm = 3 * p.stage_bytes <= 110 * 1024 ? 2 : 1;
+  int splits = static_cast<int>(std::max<long long>(1, std::min<long long>((kb_total + 3) / 4, (sms * per_sm) / p.tiles_n)));
   p.kb_per_split = static_cast<int>((kb_total + splits - 1) / splits);
   splits = static_cast<int>((kb_total + p.kb_per_split - 1) / p.kb_per_split);
   p.splits = splits;
@@ -534,7 +705,7 @@ bool conv_wgrad_tc05(OpCall& c) {
   }
   launch<T>(map, p, static_cast<long long>(p.tiles_n) * splits, sms, st);
   T* db = c.out[1].defined() ? c.out[1].data_as<T>() : nullptr;
-  conv_wgrad_finish_kernel<T><<<ew_grid(static_cast<int64_t>(p.K) * rows, 256, sms), 256, 0, st>>>(
+  conv_wgrad_finish_kernel<T><<<static_cast<unsigned>((static_cast<int64_t>(p.K) * rows + 31) / 32), 256, 0, st>>>(
       partial.data_as<float>(), dw.data_as<T>(), db, splits, p.K, CRS, p.ldp);
   if (db != nullptr) c.i[4] = 1;
   check_launch("conv2d weight gradient (implicit GEMM)");

@@ -6,6 +6,7 @@
 //
 // Replaces (reference project paths): src/backends/cuda/{binary_kernels,unary_kernels,
 // cast_kernels}.cu and the transfer helpers in src/backends/cuda/adapters.cpp.
+#include <cstdlib>
 #include <atomic>
 #include <type_traits>
 #include <vector>
@@ -20,12 +21,29 @@ int sm_count_for(const Tensor& t) { return Runtime::instance().cuda(t.device().i
 static std::atomic<uint64_t> g_launches{0};
 uint64_t kernel_launch_count() { return g_launches.load(); }
 
+unsigned int take_index_errors();
+
 // Called once per kernel wrapper after its launches; also counts the wrapper for the
 // launch statistics the benchmarks report.
+//
+// ORTHON_DEBUG_BOUNDS=1 turns every wrapper into a checkpoint: the device is drained, an
+// asynchronous fault is reported against the wrapper that caused it, and an index that a kernel
+// had to clamp (embedding ids, class targets) raises std::out_of_range naming the wrapper, instead
+// of only being counted.
 void check_launch(const char* what) {
   g_launches.fetch_add(1, std::memory_order_relaxed);
-  const cudaError_t e = cudaGetLastError();
+  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string("CUDA launch failed in ") + what + ": " + cudaGetErrorString(e));
+  static const bool debug_bounds = [] {
+    const char* v = std::getenv("ORTHON_DEBUG_BOUNDS");
+    return v != nullptr && v[0] == '1';
+  }();
+  if (!debug_bounds) return;
+  e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) throw std::runtime_error(std::string("CUDA kernel failed in ") + what + ": " + cudaGetErrorString(e));
+  const unsigned int clamped = take_index_errors();
+  if (clamped != 0)
+    throw std::out_of_range(std::string(what) + ": " + std::to_string(clamped) + " index value(s) outside the valid range");
 }
 
 namespace {

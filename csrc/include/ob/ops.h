@@ -92,6 +92,9 @@ Tensor cross_entropy_host(const Tensor& logits, const std::vector<int64_t>& targ
 Tensor nll_loss(const Tensor& log_probs, const Tensor& targets, const std::string& reduction);
 Tensor embedding(const Tensor& indices, const Tensor& weight);
 Tensor conv2d(const Tensor& x, const Tensor& w, const Tensor& b, int sh, int sw, int ph, int pw);
+// The three gradients of conv2d for an output gradient g: {dx (undefined unless want_dx), dw, db (undefined unless has_bias)}.
+std::vector<Tensor> conv2d_backward(const Tensor& g, const Tensor& x, const Tensor& w, bool has_bias, int sh, int sw, int ph, int pw,
+                                    bool want_dx);
 Tensor maxpool2d(const Tensor& x, int kh, int kw, int sh, int sw, int ph, int pw);
 Tensor layer_norm(const Tensor& x, const Tensor& w, const Tensor& b, double eps);
 // q,k,v: [B, H, T, D] (any strides with a contiguous last dim).  Additive mask optional

@@ -500,6 +500,33 @@ Tensor embedding(const Tensor& indices, const Tensor& weight) {
 }
 
 // ------------------------------------------------------------------ conv / pool
+std::vector<Tensor> conv2d_backward(const Tensor& g, const Tensor& x, const Tensor& w, bool has_bias, int sh, int sw, int ph, int pw,
+                                    bool want_dx) {
+  Tensor gc = contiguous(g);
+  Tensor dx;
+  if (want_dx) {
+    OpCall ci;
+    dx = Tensor::empty(x.shape(), x.dtype(), x.device());
+    ci.in[0] = gc; ci.in[1] = w; ci.out[0] = dx;
+    ci.i[0] = sh; ci.i[1] = sw; ci.i[2] = ph; ci.i[3] = pw;
+    run_kernel(OperatorId::Conv2dBackwardInput, x.device(), x.dtype(), ci);
+  }
+  OpCall cw;
+  Tensor dw = Tensor::empty(w.shape(), w.dtype(), w.device());
+  Tensor db;
+  if (has_bias) db = Tensor::empty({w.shape()[0]}, w.dtype(), w.device());
+  cw.in[0] = gc; cw.in[1] = x; cw.out[0] = dw;
+  if (has_bias) cw.out[1] = db;   // a kernel that also reduces the bias gradient fills it and sets i[4]
+  cw.i[0] = sh; cw.i[1] = sw; cw.i[2] = ph; cw.i[3] = pw;
+  run_kernel(OperatorId::Conv2dBackwardWeight, x.device(), x.dtype(), cw);
+  if (has_bias && cw.i[4] == 0) {
+    OpCall cb;
+    cb.in[0] = gc; cb.out[0] = db;
+    run_kernel(OperatorId::Conv2dBackwardBias, x.device(), x.dtype(), cb);
+  }
+  return {dx, dw, db};
+}
+
 namespace {
 int64_t conv_extent(int64_t in, int64_t pad, int64_t k, int64_t stride, const char* what) {
   const int64_t padded = in + 2 * pad;
@@ -513,31 +540,10 @@ struct Conv2dNode : Node {
   int sh, sw, ph, pw;
   const char* name() const override { return "Conv2DNode"; }
   std::vector<Tensor> backward(const Tensor& g) override {
-    Tensor gc = contiguous(g);
     // The input gradient is only computed when something upstream wants it (the first layer of a
     // network usually has an input that does not require grad).
-    Tensor dx;
-    if (!edges().empty() && edges()[0].kind != GraphEdge::None) {
-      OpCall ci;
-      dx = Tensor::empty(x.shape(), x.dtype(), x.device());
-      ci.in[0] = gc; ci.in[1] = w; ci.out[0] = dx;
-      ci.i[0] = sh; ci.i[1] = sw; ci.i[2] = ph; ci.i[3] = pw;
-      run_kernel(OperatorId::Conv2dBackwardInput, x.device(), x.dtype(), ci);
-    }
-    OpCall cw;
-    Tensor dw = Tensor::empty(w.shape(), w.dtype(), w.device());
-    Tensor db;
-    if (has_bias) db = Tensor::empty({w.shape()[0]}, w.dtype(), w.device());
-    cw.in[0] = gc; cw.in[1] = x; cw.out[0] = dw;
-    if (has_bias) cw.out[1] = db;   // a kernel that also reduces the bias gradient fills it and sets i[4]
-    cw.i[0] = sh; cw.i[1] = sw; cw.i[2] = ph; cw.i[3] = pw;
-    run_kernel(OperatorId::Conv2dBackwardWeight, x.device(), x.dtype(), cw);
-    if (has_bias && cw.i[4] == 0) {
-      OpCall cb;
-      cb.in[0] = gc; cb.out[0] = db;
-      run_kernel(OperatorId::Conv2dBackwardBias, x.device(), x.dtype(), cb);
-    }
-    return {dx, dw, db};
+    const bool want_dx = !edges().empty() && edges()[0].kind != GraphEdge::None;
+    return conv2d_backward(g, x, w, has_bias, sh, sw, ph, pw, want_dx);
   }
   void release_saved() override { x = Tensor(); w = Tensor(); }
 };

@@ -503,3 +503,28 @@ def test_embedding_backward_is_deterministic_and_sums_in_position_order():
         assert np.array_equal(runs[0], want)
         assert not runs[0][V - 3:].any()
     assert _C._cuda_index_errors() == 0
+
+
+def test_debug_bounds_switch_names_the_kernel_that_clamped_an_index():
+    """With ORTHON_DEBUG_BOUNDS=1 every kernel wrapper drains the device and an out-of-range index raises at once."""
+    import os
+    import subprocess
+    import sys
+    code = (
+        "import numpy as np\n"
+        "from orthon_b200 import _C\n"
+        "from orthon_b200.nn.embedding import embedding\n"
+        "w = _C.from_numpy(np.ones((10, 8), np.float32), 'float32').to('cuda:0')\n"
+        "ok = _C.from_numpy(np.array([1, 9], np.int64)).to('cuda:0')\n"
+        "embedding(ok, w)\n"
+        "bad = _C.from_numpy(np.array([1, 10], np.int64)).to('cuda:0')\n"
+        "try:\n"
+        "    embedding(bad, w)\n"
+        "except IndexError as e:\n"
+        "    print('RAISED', e)\n"
+    )
+    env = dict(os.environ, ORTHON_DEBUG_BOUNDS="1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    assert "RAISED embedding: " in out.stdout and "index value(s) outside the valid range" in out.stdout
