@@ -111,7 +111,9 @@ def worker(rank, dtypes, max_mb, iters):
                          "nccl_bus_gbs": bus(worst[2]),
                          "nvls_average_ms": float(worst[4]), "nvls_adam_ms": float(worst[5]),
                          "nvls_average_bus_gbs": bus(worst[4]) if worst[4] > 0 else None,
-                         "fused_average_frac_of_nvlink_roofline": bus(worst[0]) / NVLINK_PEER_GBS})
+                         "fused_average_frac_of_nvlink_roofline": bus(worst[0]) / NVLINK_PEER_GBS,
+                         "fused_average_frac_of_nominal_900": bus(worst[0]) / 900.0,
+                         "nvls_average_frac_of_nominal_900": bus(worst[4]) / 900.0 if worst[4] > 0 else None})
             size *= 2
         be.check_status()
     nccl_be.shutdown()

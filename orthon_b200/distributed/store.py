@@ -154,6 +154,9 @@ class TorchStore(Store):
             pass
 
 
+_PROCESS_STORES = {}
+
+
 def store_from_env(rank, world_size, environ=None):
     """ORTHON_STORE_DIR (set by the launcher) wins; otherwise a torchrun-style rendezvous."""
     environ = os.environ if environ is None else environ
@@ -162,6 +165,12 @@ def store_from_env(rank, world_size, environ=None):
         return FileStore(directory)
     host, port = environ.get("MASTER_ADDR"), environ.get("MASTER_PORT")
     if host and port:
-        # A second port keeps clear of the launcher's own rendezvous store.
-        return TorchStore(host, int(port) + 17, rank, world_size)
+        # A second port keeps clear of the launcher's own rendezvous store.  The connection (and on
+        # rank 0 the server) lives as long as the process: a group that is destroyed and created
+        # again finds the same store, told apart by the generation counters the backends keep in
+        # it, and a rank that is already rejoining never talks to a server that is being torn down.
+        key = (host, int(port) + 17, int(rank), int(world_size))
+        if key not in _PROCESS_STORES:
+            _PROCESS_STORES[key] = TorchStore(*key)
+        return _PROCESS_STORES[key]
     raise RuntimeError("no rendezvous available: set ORTHON_STORE_DIR or MASTER_ADDR/MASTER_PORT, or pass store=")
