@@ -233,14 +233,37 @@ void AutogradEngine::backward(const Tensor& root, bool retain_graph) {
         if (!offered) { node->grad_out.assign(edges.size(), Tensor()); offered = true; }
         node->grad_out[i] = Tensor(m.grad_slot);
       }
+      // A producer that already holds a partial sum from its other consumers (the skip path of
+      // a residual connection) and that this node reaches through one edge only: offer the sum
+      // as an addend.
+      bool addends = false;
+      for (size_t i = 0; i < edges.size(); ++i) {
+        const GraphEdge& e = edges[i];
+        if (e.kind != GraphEdge::Producer) continue;
+        auto it = grads.find(e.node.get());
+        if (it == grads.end() || !it->second.defined()) continue;
+        size_t same = 0;
+        for (const GraphEdge& o : edges) same += (o.kind == GraphEdge::Producer && o.node.get() == e.node.get()) ? 1 : 0;
+        if (same != 1) continue;
+        if (!addends) { node->grad_addend.assign(edges.size(), Tensor()); node->addend_taken.assign(edges.size(), 0); addends = true; }
+        node->grad_addend[i] = it->second;
+      }
       std::vector<Tensor> in_grads;
+      std::vector<char> taken;
       try {
         in_grads = node->backward(g);
       } catch (...) {
         node->grad_out.clear();
+        node->grad_addend.clear();
+        node->addend_taken.clear();
         throw;
       }
       if (offered) node->grad_out.clear();
+      if (addends) {
+        taken.swap(node->addend_taken);
+        node->grad_addend.clear();
+        node->addend_taken.clear();
+      }
       if (in_grads.size() > edges.size())
         throw std::runtime_error(std::string("backward: ") + node->name() + " returned too many gradients");
       for (size_t i = 0; i < edges.size(); ++i) {
@@ -277,7 +300,8 @@ void AutogradEngine::backward(const Tensor& root, bool retain_graph) {
           if (has) {
             check_grad(in_grads[i], e.node->out_shape, e.node->out_dtype, e.node->out_device, node->name());
             Tensor& slot = grads[e.node.get()];
-            slot = accumulate(slot, in_grads[i]);
+            if (i < taken.size() && taken[i]) slot = in_grads[i];   // the formula already added the running sum
+            else slot = accumulate(slot, in_grads[i]);
           }
           if (--task.deps[e.node.get()] == 0) settle(e.node);
         }

@@ -543,7 +543,7 @@ __global__ void layernorm_fwd_kernel(const T* __restrict__ x, const T* __restric
 template <class T, int MAXC>
 __global__ void layernorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ g,
                                      const float* __restrict__ mean, const float* __restrict__ rstd, T* __restrict__ dx,
-                                     float* __restrict__ partial, int64_t R, int64_t D) {
+                                     float* __restrict__ partial, int64_t R, int64_t D, const T* __restrict__ addend) {
   __shared__ float smem[32];
   float dw_acc[MAXC], db_acc[MAXC];
 #pragma unroll
@@ -576,7 +576,8 @@ __global__ void layernorm_bwd_kernel(const T* __restrict__ x, const T* __restric
         const float xh = (to_f(xr[j]) - m) * rs;
         const float gv = to_f(gr[j]);
         const float gy = w ? gv * to_f(w[j]) : gv;
-        dx[r * D + j] = from_f<T>(rs * (gy - s1 * invD - xh * s2 * invD));
+        const float extra = addend ? to_f(addend[r * D + j]) : 0.f;
+        dx[r * D + j] = from_f<T>(rs * (gy - s1 * invD - xh * s2 * invD) + extra);
       }
     }
   }
@@ -679,7 +680,7 @@ __global__ void layernorm_fwd_fast(const T* __restrict__ x, const T* __restrict_
 template <class T, int CH>
 __global__ void layernorm_bwd_fast(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ g,
                                    const float* __restrict__ mean, const float* __restrict__ rstd, T* __restrict__ dx,
-                                   float* __restrict__ partial, int64_t R, int64_t D) {
+                                   float* __restrict__ partial, int64_t R, int64_t D, const T* __restrict__ addend) {
   constexpr int N = Pack<T>::N;
   __shared__ float smem[64];
   const int64_t npack = D / N;
@@ -722,9 +723,11 @@ __global__ void layernorm_bwd_fast(const T* __restrict__ x, const T* __restrict_
     for (int c = 0; c < CH; ++c) {
       const int64_t p = static_cast<int64_t>(c) * blockDim.x + threadIdx.x;
       if (p < npack) {
-        Pack<T> out;
+        Pack<T> out, extra;
+        if (addend) extra = load_pack(addend + r * D + p * N);
 #pragma unroll
-        for (int k = 0; k < N; ++k) out.v[k] = from_f<T>(rs * (gy[c][k] - s1 * invD - xh[c][k] * s2 * invD));
+        for (int k = 0; k < N; ++k)
+          out.v[k] = from_f<T>(rs * (gy[c][k] - s1 * invD - xh[c][k] * s2 * invD) + (addend ? to_f(extra.v[k]) : 0.f));
         store_pack(dx + r * D + p * N, out);
       }
     }
@@ -935,15 +938,16 @@ void k_layernorm_bwd(OpCall& c) {
     partial = static_cast<float*>(lease.data());
   }
   const T* pw = c.in[1].defined() ? c.in[1].data_as<T>() : nullptr;
+  const T* padd = c.in[5].defined() ? c.in[5].data_as<T>() : nullptr;   // running gradient of the input, added to dx
   if (fast) {
     const T* px = x.data_as<T>();
     const T* pg = c.in[2].data_as<T>();
     const float* pmn = c.in[3].data_as<float>();
     const float* prs = c.in[4].data_as<float>();
     T* pdx = c.out[0].data_as<T>();
-    if (fch == 1) layernorm_bwd_fast<T, 1><<<nblocks, fth, 0, st>>>(px, pw, pg, pmn, prs, pdx, partial, R, D);
-    else if (fch == 2) layernorm_bwd_fast<T, 2><<<nblocks, fth, 0, st>>>(px, pw, pg, pmn, prs, pdx, partial, R, D);
-    else layernorm_bwd_fast<T, 4><<<nblocks, fth, 0, st>>>(px, pw, pg, pmn, prs, pdx, partial, R, D);
+    if (fch == 1) layernorm_bwd_fast<T, 1><<<nblocks, fth, 0, st>>>(px, pw, pg, pmn, prs, pdx, partial, R, D, padd);
+    else if (fch == 2) layernorm_bwd_fast<T, 2><<<nblocks, fth, 0, st>>>(px, pw, pg, pmn, prs, pdx, partial, R, D, padd);
+    else layernorm_bwd_fast<T, 4><<<nblocks, fth, 0, st>>>(px, pw, pg, pmn, prs, pdx, partial, R, D, padd);
     if (need_params) {
       const float* rows = partial;
       int nrows = nblocks;
@@ -963,7 +967,7 @@ void k_layernorm_bwd(OpCall& c) {
 #define LN_BWD(MAXC)                                                                                          \
   layernorm_bwd_kernel<T, MAXC><<<nblocks, threads, 0, st>>>(x.data_as<T>(), pw, c.in[2].data_as<T>(),           \
                                                              c.in[3].data_as<float>(), c.in[4].data_as<float>(), \
-                                                             c.out[0].data_as<T>(), partial, R, D)
+                                                             c.out[0].data_as<T>(), partial, R, D, padd)
   if (cols <= 2) LN_BWD(2);
   else if (cols <= 4) LN_BWD(4);
   else if (cols <= 8) LN_BWD(8);

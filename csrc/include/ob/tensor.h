@@ -162,6 +162,15 @@ class Node : public std::enable_shared_from_this<Node> {
   // Formulas that ignore the offer stay correct.
   std::vector<Tensor> grad_out;
   Tensor grad_destination(size_t input) const { return input < grad_out.size() ? grad_out[input] : Tensor(); }
+  // Addend offers, also set around one backward() call: grad_addend[i], when defined, is the sum
+  // of the gradients that input i's producer has received so far from other consumers.  A
+  // formula that can add it while it writes its own result (one pass instead of a separate
+  // addition) returns result + addend for input i and calls take_addend(i); the engine then
+  // replaces the producer's running sum instead of adding to it.  Ignoring the offer is correct.
+  std::vector<Tensor> grad_addend;
+  std::vector<char> addend_taken;
+  Tensor offered_addend(size_t input) const { return input < grad_addend.size() ? grad_addend[input] : Tensor(); }
+  void take_addend(size_t input) { if (input < addend_taken.size()) addend_taken[input] = 1; }
   // Output metadata recorded at attach time, used to validate incoming gradients.
   Shape out_shape;
   DType out_dtype = DType::F32;

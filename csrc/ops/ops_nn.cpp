@@ -649,6 +649,14 @@ struct LayerNormNode : Node {
     c.in[2] = reshape(contiguous(g), {-1, D});
     c.in[3] = mean;
     c.in[4] = rstd;
+    // The gradient that already reached the input along the residual path is added in the same
+    // pass (CUDA kernels only; the CPU kernels leave the addition to the engine).
+    Tensor addend = offered_addend(0);
+    if (addend.defined() && x2.device().is_cuda() && addend.is_contiguous() && addend.numel() == x2.numel() &&
+        addend.dtype() == x2.dtype() && addend.device() == x2.device() && reinterpret_cast<uintptr_t>(addend.data()) % 16 == 0) {
+      c.in[5] = addend;
+      take_addend(0);
+    }
     c.out[0] = dx;
     c.out[1] = dw;
     c.out[2] = db;

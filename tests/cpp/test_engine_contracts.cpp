@@ -182,6 +182,64 @@ TEST(engine_gradient_shape_is_validated) {
   CHECK_THROWS_WITH(out.backward(), "WrongShapeNode");
   CHECK(!a.grad().defined());
 }
+TEST(engine_addend_offer_replaces_the_running_sum_when_taken) {
+  // y = h + f(h) with h = 3 * x: the skip path delivers its gradient to h's producer first; f is then
+  // offered that running sum.  A formula that takes the offer returns (own + addend) and the engine
+  // must not add the addend a second time; one that ignores it is accumulated as before.
+  struct Branch : Node {
+    bool take = false;
+    int offers = 0;
+    const char* name() const override { return "BranchNode"; }
+    std::vector<Tensor> backward(const Tensor& g) override {
+      Tensor own = ops::mul_scalar(g, 10.0);
+      Tensor addend = offered_addend(0);
+      if (addend.defined()) ++offers;
+      if (take && addend.defined()) {
+        take_addend(0);
+        return {ops::add(own, addend)};
+      }
+      return {own};
+    }
+  };
+  for (bool take : {false, true}) {
+    Tensor x = leaf({1, 2});
+    Tensor h = ops::mul_scalar(x, 3.0);
+    Tensor out = Tensor::zeros({2}, DType::F32, kCpu);
+    auto node = std::make_shared<Branch>();
+    node->take = take;
+    node->set_inputs({h});
+    node->out_shape = out.shape(); node->out_dtype = out.dtype(); node->out_device = out.device();
+    out.requires_grad_(true);
+    out.impl()->ag().grad_fn = node;
+    out.impl()->ag().history = History::Live;
+    ops::add(h, out).backward();
+    CHECK(node->offers == 1);
+    CHECK(vals(x.grad()) == (V{33, 33}));   // 3 * (1 + 10) either way
+    CHECK(node->grad_addend.empty() && node->addend_taken.empty());
+  }
+}
+TEST(engine_addend_is_not_offered_to_a_node_that_reaches_the_producer_twice) {
+  struct Twice : Node {
+    int offers = 0;
+    const char* name() const override { return "TwiceNode"; }
+    std::vector<Tensor> backward(const Tensor& g) override {
+      if (offered_addend(0).defined() || offered_addend(1).defined()) ++offers;
+      return {g, g};
+    }
+  };
+  Tensor x = leaf({1});
+  Tensor h = ops::mul_scalar(x, 2.0);
+  Tensor out = Tensor::zeros({1}, DType::F32, kCpu);
+  auto node = std::make_shared<Twice>();
+  node->set_inputs({h, h});
+  node->out_shape = out.shape(); node->out_dtype = out.dtype(); node->out_device = out.device();
+  out.requires_grad_(true);
+  out.impl()->ag().grad_fn = node;
+  out.impl()->ag().history = History::Live;
+  ops::add(h, out).backward();
+  CHECK(node->offers == 0);
+  CHECK(vals(x.grad()) == (V{6}));
+}
 TEST(engine_deep_chains_do_not_recurse) {
   Tensor x = leaf({1});
   Tensor y = x;

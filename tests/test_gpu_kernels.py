@@ -528,3 +528,25 @@ def test_debug_bounds_switch_names_the_kernel_that_clamped_an_index():
     out = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=300)
     assert out.returncode == 0, out.stderr
     assert "RAISED embedding: " in out.stdout and "index value(s) outside the valid range" in out.stdout
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("shape", [(64, 512), (33, 2048), (7, 200)])
+def test_layer_norm_backward_adds_the_residual_gradient_in_the_same_pass(dtype, shape):
+    """y = h + LayerNorm(h): the skip path's gradient reaches h first and the LayerNorm formula adds it while it
+    writes its own input gradient; the sum must match the reference either way."""
+    rng = np.random.default_rng(shape[0])
+    x = rng.standard_normal(shape); w = rng.standard_normal((shape[1],)); b = rng.standard_normal((shape[1],))
+    up = rng.standard_normal(shape)
+    xx, ww, bb = dev_tensor(x, dtype, True), dev_tensor(w, dtype, True), dev_tensor(b, dtype, True)
+    h = xx * 2.0
+    before = _C._kernel_launch_count()
+    y = h + ob.layer_norm(h, shape[1], ww, bb)
+    (y * dev_tensor(up, dtype)).sum().backward()
+    t, tw, tb = (ref_round(v_, dtype).requires_grad_(True) for v_ in (x, w, b))
+    th = t * 2.0
+    ty = th + torch.nn.functional.layer_norm(th, (shape[1],), tw, tb)
+    (ty * ref_round(up, dtype)).sum().backward()
+    close(xx.grad, t.grad, dtype, 8); close(ww.grad, tw.grad, dtype, 8); close(bb.grad, tb.grad, dtype, 8)
+    # Without the fused addition the same graph takes one more kernel wrapper (the engine's add).
+    assert _C._kernel_launch_count() - before > 0
