@@ -9,12 +9,14 @@
 The reducers wrap every bucket launch (communication stream) and the optimizers every step in a
 range, so with tracing on a training step yields a timeline that shows which reductions ran
 beside the backward pass and which were left for its tail.  Ranges cost two event records each and
-nothing when tracing is off.
+nothing when tracing is off.  With ORTHON_NVTX=1 every range is also an NVTX range on the calling
+thread, for a profiler that is attached to the process (no events are recorded for that alone).
 """
 import os
 from contextlib import contextmanager
 
 _enabled = os.environ.get("ORTHON_TRACE", "0") not in ("", "0")
+_nvtx = os.environ.get("ORTHON_NVTX", "0") not in ("", "0")
 _ranges = []
 
 
@@ -30,6 +32,21 @@ def tracing_enabled():
 
 @contextmanager
 def trace_range(name, device=0, stream_kind=0):
+    if _nvtx:
+        from .. import _C
+        _C._nvtx_push(str(name))
+        try:
+            with _event_range(name, device, stream_kind):
+                yield
+        finally:
+            _C._nvtx_pop()
+    else:
+        with _event_range(name, device, stream_kind):
+            yield
+
+
+@contextmanager
+def _event_range(name, device, stream_kind):
     if not _enabled:
         yield
         return
