@@ -53,7 +53,7 @@ def _check_sync(p, master):
 
 
 class MixedPrecisionOptimizer:
-    def __init__(self, model, optimizer_cls, fused="auto", **optimizer_kwargs):
+    def __init__(self, model, optimizer_cls, fused="auto", bucket_size_mb=None, **optimizer_kwargs):
         """`fused` selects how the step is scheduled when the gradients can live in flat buckets
         (one CUDA device, one dtype; across ranks: the peer-memory transport):
 
@@ -66,7 +66,10 @@ class MixedPrecisionOptimizer:
         * "update": the optimizer update itself runs inside the reduction kernel during backward
           (no GradScaler: there is no point at which a step could be skipped).  One backward per
           `zero_grad()`, as above.
-        * False keeps the per-parameter path."""
+        * False keeps the per-parameter path.
+
+        `bucket_size_mb` sizes the flat buckets when the optimizer builds them itself (a plain
+        module on one GPU; a DistributedDataParallel wrapper brings its own)."""
         if fused not in ("auto", "reduce", "overlap", "update", False):
             raise ValueError("fused must be 'auto', 'reduce', 'overlap', 'update' or False")
         check = getattr(model, "_validate_master_gradient_sync", None)
@@ -80,6 +83,7 @@ class MixedPrecisionOptimizer:
         params = tuple(model.parameters())
         for p in params:
             _check_param(p)
+        self._bucket_size_mb = bucket_size_mb
         if fused is not False and self._try_init_fused(model, params, optimizer_cls, fused, optimizer_kwargs):
             return
         self._states = tuple(_State(p, p.dtype, p if p.dtype == "float32" else _new_master(p, p.device), p.device)
@@ -107,7 +111,7 @@ class MixedPrecisionOptimizer:
                     owners.append((n, p))
             if any(not p.requires_grad for _, p in owners) or not LocalFlatReducer.eligible(owners):
                 return False
-            reducer = LocalFlatReducer(owners)
+            reducer = LocalFlatReducer(owners, self._bucket_size_mb)
             for _, p in owners:
                 p._register_post_accumulate_grad_hook(lambda r=reducer, k=id(p): r.mark(k))
         if not isinstance(reducer, PeerReducer):
