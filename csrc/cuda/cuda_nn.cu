@@ -696,23 +696,44 @@ __global__ void layernorm_bwd_fast(const T* __restrict__ x, const T* __restrict_
       dw_acc[c][k] = db_acc[c][k] = 0.f;
     }
   }
+  // The loads of the next row are issued before the current row's two block-wide sums, so a
+  // block always has a row of DRAM requests in flight while it synchronises.  The row is kept as
+  // loaded (16-bit packs) and the normalised values are formed twice rather than held in float32
+  // registers: that keeps the block small enough for several per SM.
+  Pack<T> cx[CH], cg[CH], ca[CH], nx[CH], ng[CH], na[CH];
+  float cm = 0.f, crs = 0.f, nm = 0.f, nrs = 0.f;
+  auto fetch = [&](int64_t r, Pack<T>* fx, Pack<T>* fg, Pack<T>* fa, float& fm, float& frs) {
+    fm = mean[r]; frs = rstd[r];
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int64_t p = static_cast<int64_t>(c) * blockDim.x + threadIdx.x;
+      if (p < npack) {
+        fx[c] = load_pack(x + r * D + p * N);
+        fg[c] = load_pack(g + r * D + p * N);
+        if (addend) fa[c] = load_pack(addend + r * D + p * N);
+      }
+    }
+  };
+  constexpr bool kAhead = CH == 1;   // wider rows would pay for the second set of packs with their occupancy
+  if (kAhead && static_cast<int64_t>(blockIdx.x) < R) fetch(blockIdx.x, cx, cg, ca, cm, crs);
   for (int64_t r = blockIdx.x; r < R; r += gridDim.x) {
-    const float m = mean[r], rs = rstd[r];
-    float xh[CH][N], gy[CH][N];
+    const bool more = kAhead && r + gridDim.x < R;
+    if (more) fetch(r + gridDim.x, nx, ng, na, nm, nrs);
+    if (!kAhead) fetch(r, cx, cg, ca, cm, crs);
+    const float m = cm, rs = crs;
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
       const int64_t p = static_cast<int64_t>(c) * blockDim.x + threadIdx.x;
       if (p < npack) {
-        Pack<T> px = load_pack(x + r * D + p * N), pg = load_pack(g + r * D + p * N);
 #pragma unroll
         for (int k = 0; k < N; ++k) {
-          const float gv = to_f(pg.v[k]);
-          xh[c][k] = (to_f(px.v[k]) - m) * rs;
-          gy[c][k] = gv * wv[c][k];
-          s1 += gy[c][k];
-          s2 += gy[c][k] * xh[c][k];
-          dw_acc[c][k] += gv * xh[c][k];
+          const float gv = to_f(cg[c].v[k]);
+          const float xh = (to_f(cx[c].v[k]) - m) * rs;
+          const float gy = gv * wv[c][k];
+          s1 += gy;
+          s2 += gy * xh;
+          dw_acc[c][k] += gv * xh;
           db_acc[c][k] += gv;
         }
       }
@@ -723,13 +744,20 @@ __global__ void layernorm_bwd_fast(const T* __restrict__ x, const T* __restrict_
     for (int c = 0; c < CH; ++c) {
       const int64_t p = static_cast<int64_t>(c) * blockDim.x + threadIdx.x;
       if (p < npack) {
-        Pack<T> out, extra;
-        if (addend) extra = load_pack(addend + r * D + p * N);
+        Pack<T> out;
 #pragma unroll
-        for (int k = 0; k < N; ++k)
-          out.v[k] = from_f<T>(rs * (gy[c][k] - s1 * invD - xh[c][k] * s2 * invD) + (addend ? to_f(extra.v[k]) : 0.f));
+        for (int k = 0; k < N; ++k) {
+          const float xh = (to_f(cx[c].v[k]) - m) * rs;
+          const float gy = to_f(cg[c].v[k]) * wv[c][k];
+          out.v[k] = from_f<T>(rs * (gy - s1 * invD - xh * s2 * invD) + (addend ? to_f(ca[c].v[k]) : 0.f));
+        }
         store_pack(dx + r * D + p * N, out);
       }
+    }
+    if (more) {
+#pragma unroll
+      for (int c = 0; c < CH; ++c) { cx[c] = nx[c]; cg[c] = ng[c]; ca[c] = na[c]; }
+      cm = nm; crs = nrs;
     }
   }
   if (partial) {
@@ -928,7 +956,16 @@ void k_layernorm_bwd(OpCall& c) {
   // Rows are walked by persistent blocks.  Narrow rows give small blocks (64 threads for 512
   // columns), so more of them are needed per SM to keep enough loads in flight: up to 1024
   // resident threads per SM (64 registers each), at most 16 blocks.
-  const int per_sm = fast ? std::max(4, std::min(16, 1024 / std::max(fth, 1))) : 4;
+  int per_sm = fast ? std::max(4, std::min(16, 1024 / std::max(fth, 1))) : 4;
+  if (fast) {
+    // Never more blocks than can be resident: the rows are dealt out statically.
+    int resident = per_sm;
+    const cudaError_t e = fch == 1 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, layernorm_bwd_fast<T, 1>, fth, 0)
+                          : fch == 2 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, layernorm_bwd_fast<T, 2>, fth, 0)
+                                     : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, layernorm_bwd_fast<T, 4>, fth, 0);
+    if (e == cudaSuccess && resident >= 1) per_sm = std::min(per_sm, resident);
+    else (void)cudaGetLastError();
+  }
   const int nblocks = static_cast<int>(std::min<int64_t>(R, static_cast<int64_t>(sms) * per_sm));
   const bool need_params = c.out[1].defined() || c.out[2].defined();
   ScratchLease lease;
