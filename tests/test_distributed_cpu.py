@@ -55,3 +55,39 @@ def _mismatch(rank):
 def test_descriptor_mismatch_aborts_group():
     with pytest.raises(RuntimeError, match="mismatch"):
         dist.spawn(_mismatch, nprocs=2, backend="local")
+
+
+def _free_port():
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_rendezvous_store_outlives_a_group_so_it_can_be_created_again():
+    """torchrun-style rendezvous: the store of a process is created once and found again by the next group."""
+    from orthon_b200.distributed import store as store_mod
+    env = {"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(_free_port())}
+    first = store_mod.store_from_env(0, 1, environ=env)
+    first.set("generation/0/key", b"a")
+    second = store_mod.store_from_env(0, 1, environ=env)
+    assert second is first
+    assert second.get("generation/0/key") == b"a"
+    assert second.add("p2p/generation/0", 1) == 1 and second.add("p2p/generation/0", 1) == 2
+    other = store_mod.store_from_env(0, 1, environ={"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(_free_port())})
+    assert other is not first
+
+
+def test_store_directory_wins_over_the_rendezvous_address(tmp_path):
+    from orthon_b200.distributed import store as store_mod
+    env = {"ORTHON_STORE_DIR": str(tmp_path), "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": "1"}
+    s = store_mod.store_from_env(0, 2, environ=env)
+    assert isinstance(s, store_mod.FileStore)
+    s.set("k", b"v")
+    assert store_mod.store_from_env(1, 2, environ=env).get("k") == b"v"
+
+
+def test_no_rendezvous_information_is_an_error():
+    from orthon_b200.distributed import store as store_mod
+    with pytest.raises(RuntimeError, match="no rendezvous available"):
+        store_mod.store_from_env(0, 1, environ={})
