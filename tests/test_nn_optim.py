@@ -263,3 +263,24 @@ def test_diagnostics_pool_switches():
     stats = diag.memory_pool_stats()
     assert {"current_bytes", "peak_bytes", "cached_bytes"} <= set(stats)
     assert isinstance(diag.dispatch_kernels(), (list, tuple, dict))
+
+
+def test_conv2d_backward_entry_point_matches_autograd_and_skips_the_input_gradient_on_request():
+    """`_C._conv2d_backward` is the formula the autograd node runs; benchmarks call it directly."""
+    import numpy as np
+    import torch
+    from orthon_b200 import _C
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((2, 3, 7, 6)).astype(np.float32)
+    w = rng.standard_normal((4, 3, 3, 3)).astype(np.float32)
+    g = rng.standard_normal((2, 4, 4, 3)).astype(np.float32)   # stride 2, padding 1
+    dx, dw, db = _C._conv2d_backward(_C.from_numpy(g), _C.from_numpy(x), _C.from_numpy(w), True, 2, 2, 1, 1, True)
+    tx, tw = torch.tensor(x, requires_grad=True), torch.tensor(w, requires_grad=True)
+    tb = torch.zeros(4, requires_grad=True)
+    torch.nn.functional.conv2d(tx, tw, tb, stride=2, padding=1).backward(torch.tensor(g))
+    assert np.allclose(dx.numpy(), tx.grad.numpy(), atol=1e-4)
+    assert np.allclose(dw.numpy(), tw.grad.numpy(), atol=1e-4)
+    assert np.allclose(db.numpy(), tb.grad.numpy(), atol=1e-4)
+    none_dx, dw2, no_bias = _C._conv2d_backward(_C.from_numpy(g), _C.from_numpy(x), _C.from_numpy(w), False, 2, 2, 1, 1, False)
+    assert none_dx is None and no_bias is None
+    assert np.allclose(dw2.numpy(), dw.numpy())
