@@ -25,8 +25,9 @@ Two schedules:
   local gradients.
 
 Buckets of at least NVLS_MIN_BYTES go through the in-switch (multimem) variant of the kernel
-when ORTHON_NVLS_MIN_WORLD enables it for the group's size and the backend could bind the buckets
-to an NVLink multicast object; everything else uses the one-shot / two-shot peer-load variants.
+when the group has at least ORTHON_NVLS_MIN_WORLD ranks (4 unless set) and the backend could bind
+the buckets to an NVLink multicast object; everything else uses the one-shot / two-shot peer-load
+variants.
 """
 import os
 
@@ -62,13 +63,18 @@ class _Bucket:
 
 
 class PeerReducer:
-    ONESHOT_BYTES = 512 << 10
-    NVLS_MIN_BYTES = int(os.environ.get("ORTHON_NVLS_MIN_BYTES", 1 << 20))  # smaller buckets use peer loads
-    # In-switch reduction moves S bytes per GPU and direction instead of 2 S (w-1)/w, which only
-    # pays as the world grows.  Measured on NVLink 5: 392 against 683 GB/s bus at 2 GPUs and a tie at
-    # 4 (683 against 668 at 1 GB, behind for 25 MB buckets).  So the peer-load kernels are the
-    # default everywhere and ORTHON_NVLS_MIN_WORLD=<ranks> opts in.
-    NVLS_MIN_WORLD = int(os.environ.get("ORTHON_NVLS_MIN_WORLD", 0))
+    # One-shot (every rank reads every copy) pays while (world - 1) x bucket stays small.  Measured
+    # crossover against the two-shot kernel: 512 KB at 2 ranks, about 32 KB at 4, 16 KB at 8.
+    ONESHOT_BYTES_BY_WORLD = {1: 512 << 10, 2: 512 << 10, 3: 32 << 10, 4: 32 << 10}
+    ONESHOT_BYTES_LARGE_WORLD = 16 << 10
+    # In-switch reduction (multimem) moves S bytes per GPU and direction instead of 2 S (w-1)/w.
+    # Measured on NVLink 5 / NVSwitch, 1 GB buckets, bus GB/s: 2 GPUs 392 against 683 for peer loads;
+    # 4 GPUs 686 against 651 (and the 1.3 B step 83.1 against 84.4 ms); 8 GPUs 830 against 625 (step
+    # 82.7 against 85.0 ms), ahead from 8 KB buckets on at both sizes.  So groups of 4 ranks and more
+    # use it wherever the box could bind the buckets to a multicast object; ORTHON_NVLS_MIN_WORLD
+    # moves the threshold (0 turns it off), ORTHON_NVLS=0 never binds.
+    NVLS_MIN_BYTES = int(os.environ.get("ORTHON_NVLS_MIN_BYTES", 8 << 10))  # smaller buckets use peer loads
+    NVLS_MIN_WORLD = int(os.environ.get("ORTHON_NVLS_MIN_WORLD", 4))
     # Block size of launches that run beside a backward pass: small enough to share an SM with a
     # persistent GEMM CTA (see csrc/cuda/peer_reducer.cu).
     OVERLAP_THREADS = int(os.environ.get("ORTHON_PEER_OVERLAP_THREADS", 512))
@@ -165,7 +171,8 @@ class PeerReducer:
         if b.seg is not None and self.mode != "average":
             hyper["seg_end"], hyper["seg_wd"] = b.seg
         nbytes = b.n * _ELEMENT_BYTES[b.dtype]
-        oneshot = nbytes <= self.ONESHOT_BYTES
+        in_switch = bool(b.mc) and nbytes >= self.NVLS_MIN_BYTES and 0 < self.NVLS_MIN_WORLD <= self.world
+        oneshot = not in_switch and nbytes <= self.ONESHOT_BYTES_BY_WORLD.get(self.world, self.ONESHOT_BYTES_LARGE_WORLD)
         status, found_inf = self.backend.status_tensors()
         _C._stream_fence(self.device, 0, 1)  # communication stream waits for the gradients
         fused = self.mode != "average"
@@ -176,8 +183,7 @@ class PeerReducer:
                             v=b.v_flat if self.mode == "adam" else None,
                             model=b.param_flat if (fused and b.param_flat is not None and b.master_flat is not b.param_flat) else None,
                             hyper=hyper, status=status, found_inf=found_inf, stream_kind=1,
-                            mc_grads=b.mc if (b.mc and not oneshot and nbytes >= self.NVLS_MIN_BYTES
-                                              and 0 < self.NVLS_MIN_WORLD <= self.world) else 0,
+                            mc_grads=b.mc if in_switch else 0,
                             ctas=self.OVERLAP_CTAS if beside_backward else 0,
                             threads=self.OVERLAP_THREADS if beside_backward else 512,
                             wait_ms=self.backend.wait_ms, invalid=bool(invalid), usage=usage)
