@@ -320,6 +320,11 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     constexpr int kSubs = BN / 32;
     const int sub_begin = kSplitCols ? my_h * (kSubs / 2) : 0, sub_end = kSplitCols ? sub_begin + kSubs / 2 : kSubs;
     int buf = 0;
+    // One staging tile and two outputs: the second output (stored pre-activation or activation
+    // derivative) waits, packed to 16 bits in registers, until the store of the result has read
+    // the tile, and then goes out through the same tile.
+    const bool defer_z = kOneStage && staged && Zb != nullptr;
+    uint4 zp0[4], zp1[4];   // the two 32-column halves of a 64-column group (named, not indexed: they stay in registers)
     // Pair form: the even CTA's MMA thread waits for the epilogue warps of both CTAs.
     const uint32_t pair_tmem_empty0 = PAIR ? mapa_u32(smem_u32(&tmem_empty[0]), 0u) : 0u;
     for (long long t = first_tile; t < total_tiles && ok; t += tile_step, ++it) {
@@ -448,9 +453,31 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             d[j] = cdf + v[j] * 0.3989422804014327f * __expf(-0.5f * v[j] * v[j]);
             v[j] *= cdf;
           }
-          if (Zb) emit(Zb, ebuf, true, d);
+          if (defer_z) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              Pack<T> pk;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) pk.v[j] = from_f<T>(d[q * 8 + j]);
+              if (half == 0) zp0[q] = *reinterpret_cast<uint4*>(&pk);
+              else zp1[q] = *reinterpret_cast<uint4*>(&pk);
+            }
+          } else if (Zb) {
+            emit(Zb, ebuf, true, d);
+          }
         } else {
-          if (Zb) emit(Zb, ebuf, true, v);
+          if (defer_z) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              Pack<T> pk;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) pk.v[j] = from_f<T>(v[q * 8 + j]);
+              if (half == 0) zp0[q] = *reinterpret_cast<uint4*>(&pk);
+              else zp1[q] = *reinterpret_cast<uint4*>(&pk);
+            }
+          } else if (Zb) {
+            emit(Zb, ebuf, true, v);
+          }
           if (p.act == 1) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
@@ -485,6 +512,19 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         emit(Cb, kOneStage ? ebuf : (Zb ? ebuf + 4096 : ebuf + buf * 4096), false, v);
         if (!kOneStage && staged && !Zb && (half == 1 || col0 + 32 >= p.N)) buf ^= 1;
+        if (defer_z && (half == 1 || col0 + 32 >= p.N)) {
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the result's store has read the tile
+          __syncwarp();
+#pragma unroll
+          for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(ebuf + lane * 128 + ((q ^ (lane & 7)) << 4)) = zp0[q];
+          if (half == 1) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(ebuf + lane * 128 + (((4 + q) ^ (lane & 7)) << 4)) = zp1[q];
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) tma_store_4d(&map_z, ebuf, col0 - half * 32, row0, b1, b0);
+        }
       }
       tc_fence_before();
       __syncwarp();

@@ -44,6 +44,7 @@ struct GemmPlanOptions {
   bool splitk = true;
   int pair_mode = -1;           // -1 planner decides, 0 never, 1 256 x 256 pair tiles, 2 512 x 256 pair tiles
   int pair_ew8_max_k = 4096;
+  bool tall_preact = true;      // 256-row tiles also for epilogues that store a second output
   static GemmPlanOptions from_environment();
 };
 

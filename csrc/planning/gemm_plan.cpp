@@ -28,6 +28,7 @@ GemmPlanOptions GemmPlanOptions::from_environment() {
   o.splitk = env_int("ORTHON_GEMM_SPLITK", 1) != 0;
   o.pair_mode = env_int("ORTHON_GEMM_PAIR", o.pair_mode);
   o.pair_ew8_max_k = env_int("ORTHON_GEMM_PAIR_EW8_MAX_K", o.pair_ew8_max_k);
+  o.tall_preact = env_int("ORTHON_GEMM_TALL_PREACT", 1) != 0;
   return o;
 }
 
@@ -107,7 +108,10 @@ GemmPlan plan_gemm(const GemmProblem& p, const GemmPlanOptions& o) {
   // their epilogue, which overlaps the next tile only partly, and the waves fill to 80 %.
   const long long tiles256 = ceil_div(p.m, 256) * ceil_div(p.n, 256) * p.batch;
   const double eff256 = static_cast<double>(tiles256) / static_cast<double>(ceil_div(tiles256, p.sms) * p.sms);
-  const bool tall = wide && o.force_tm != 128 && !p.has_preact &&
+  // A second output (stored pre-activation) goes through the same staging tile after the result,
+  // which lengthens the epilogue; the tile still pays (measured on the first MLP product of the
+  // 1.3 B model).  ORTHON_GEMM_TALL_PREACT=0 keeps such products on the 128-row tile.
+  const bool tall = wide && o.force_tm != 128 && (!p.has_preact || o.tall_preact) &&
                     (o.force_tm == 256 || (p.m >= 512 && p.k >= o.tall_min_k && eff256 >= 0.8));
   // CTA pairs.  Measured under the power cap (1.3 B transformer shapes, 8192 tokens) the pair tiles
   // tie with the single-CTA 256 x 256 tile wherever that one is eligible, so the planner keeps the

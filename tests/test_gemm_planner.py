@@ -94,7 +94,8 @@ def test_tall_tiles_on_transformer_shapes(name, m, n, k, tm):
 
 
 def test_tall_tiles_respect_their_conditions():
-    assert plan(m=8192, n=8192, k=2048, preact=True)["tm"] == 128          # the stored pre-activation needs the double staging buffers
+    assert plan(m=8192, n=8192, k=2048, preact=True, act=4)["tm"] == 256   # a second output goes through the same staging tile
+    assert plan(m=8192, n=8192, k=2048, preact=True, options={"tall_preact": False})["tm"] == 128
     assert plan(m=256, n=8192, k=8192)["tm"] == 128                        # fewer than 512 rows
     assert plan(m=8192, n=8192, k=2047)["tm"] == 128
     assert plan(m=8192, n=8192, k=1024, options={"tall_min_k": 1024})["tm"] == 256
@@ -156,11 +157,12 @@ def test_plan_text_names_route_tile_and_reason():
 def test_options_come_from_the_environment(monkeypatch):
     for name, value in (("ORTHON_FLOAT32_MATMUL", "high"), ("ORTHON_GEMM_BN", "128"), ("ORTHON_GEMM_TM", "256"),
                         ("ORTHON_GEMM_TALL_MIN_K", "512"), ("ORTHON_GEMM_EW8_MAX_K", "64"), ("ORTHON_GEMM_SPLITK", "0"),
-                        ("ORTHON_GEMM_PAIR", "2"), ("ORTHON_GEMM_PAIR_EW8_MAX_K", "128"), ("ORTHON_GEMM_F32_SPLIT_MIN", "77")):
+                        ("ORTHON_GEMM_PAIR", "2"), ("ORTHON_GEMM_PAIR_EW8_MAX_K", "128"), ("ORTHON_GEMM_F32_SPLIT_MIN", "77"),
+                        ("ORTHON_GEMM_TALL_PREACT", "0")):
         monkeypatch.setenv(name, value)
     o = _C._gemm_plan_options_from_environment()
     assert o == {"float32_precision": 1, "float32_split_min": 77, "force_bn": 128, "force_tm": 256, "tall_min_k": 512,
-                 "ew8_max_k": 64, "splitk": False, "pair_mode": 2, "pair_ew8_max_k": 128}
+                 "ew8_max_k": 64, "splitk": False, "pair_mode": 2, "pair_ew8_max_k": 128, "tall_preact": False}
     for name in ("ORTHON_FLOAT32_MATMUL", "ORTHON_GEMM_BN", "ORTHON_GEMM_TM", "ORTHON_GEMM_TALL_MIN_K", "ORTHON_GEMM_EW8_MAX_K",
                  "ORTHON_GEMM_SPLITK", "ORTHON_GEMM_PAIR", "ORTHON_GEMM_PAIR_EW8_MAX_K", "ORTHON_GEMM_F32_SPLIT_MIN"):
         monkeypatch.delenv(name)

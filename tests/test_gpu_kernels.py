@@ -337,10 +337,13 @@ def test_diagnostic_routes():
     close(y_direct, ty, "bfloat16"); close(y_auto, ty, "bfloat16")
 
 
-@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
-def test_fused_mlp_gelu(dtype):
+@pytest.mark.parametrize("dtype,shape", [("bfloat16", (384, 256, 512)), ("float32", (384, 256, 512)),
+                                         # 256-row tiles with the activation derivative as a second output of the same
+                                         # staging tile (16 x 9 tiles fill one wave), and a width that ends in a half group
+                                         ("bfloat16", (4096, 2048, 2304)), ("float16", (1024, 2048, 9440))])
+def test_fused_mlp_gelu(dtype, shape):
     rng = np.random.default_rng(31)
-    M, E, F = 384, 256, 512
+    M, E, F = shape
     arrs = [rng.standard_normal((M, E)), rng.standard_normal((E, F)) * 0.05, rng.standard_normal((F,)) * 0.1,
             rng.standard_normal((F, E)) * 0.05, rng.standard_normal((E,)) * 0.1]
     xs = [dev_tensor(a, dtype, True) for a in arrs]
