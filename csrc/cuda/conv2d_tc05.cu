@@ -5,20 +5,27 @@
 // TMA, accumulators live in tensor memory.
 //
 //   fprop  out[n, k, oh, ow] = sum_{c,r,s} x[n, c, oh*sh-ph+r, ow*sw-pw+s] * w[k, c, r, s] + b[k]
-//          M = N*OH*OW output pixels (128 per CTA), N = K channels, reduction C*R*S.
+//          M = N*OH*OW output pixels (128 per tile), N = K channels, reduction C*R*S.
 //          A (gathered, pixel-contiguous = MN-major) x B (weights [K, CRS], TMA, K-major).
 //   dgrad  dx[n, c, ih, iw] = sum_{k,r,s} gy[n, k, (ih+ph-r)/sh, (iw+pw-s)/sw] * w[k, c, r, s]
-//          M = N*H*W input pixels, N = C channels, reduction K*R*S.
-//          A (gathered from gy, MN-major) x B (weights permuted to [C, K*R*S], TMA, K-major).
+//          done per stride class (ih mod sh, iw mod sw): the pixels of a class see only the filter
+//          rows r = ra0 + sh*ri and columns s = sb0 + sw*si, so nothing is multiplied by the zeros a
+//          strided convolution leaves between its taps, and no index is divided in the inner loop.
+//          M = pixels of the class, N = C channels, reduction K * taps of the class.
+//          A (gathered from gy, MN-major) x B (weights permuted per class to [C, K*taps], TMA).
 //   wgrad  dw[k, (c,r,s)] = sum_{n,oh,ow} gy[n, k, oh, ow] * x[n, c, oh*sh-ph+r, ow*sw-pw+s]
 //          M = K channels, N = C*R*S (+ one column of ones whose result is the bias gradient),
 //          reduction N*OH*OW pixels cut into slices (split-K) with float32 partials and a fixed-order
 //          second pass.  A (gy, TMA, K-major) x B (gathered, K-major).
 //
 // In all three the gathered tile is "rows of 64 consecutive pixels": row = one (c, r, s) (or
-// (k, r, s)) tap, 128 bytes, chunk c of row q stored at q * 128 + ((c ^ (q & 7)) << 4), which is
+// (k, ri, si)) tap, 128 bytes, chunk c of row q stored at q * 128 + ((c ^ (q & 7)) << 4), which is
 // both the MN-major A layout (fprop, dgrad) and the K-major B layout (wgrad) of a 128-byte-swizzled
-// tile.  Every mbarrier wait is bounded.  bfloat16 and float16; float32 stays on the GEMM lowering.
+// tile.  CTAs are persistent (a grid of at most two per SM walks the work items; the ring of
+// operand slots and its barrier phases run on across items).  When output rows are a multiple of 8
+// pixels a thread's 8 pixels share one row: one vertical test and one precomputed column mask then
+// cover 8 loads (FAST); other shapes take a per-element path.  Every mbarrier wait is bounded.
+// bfloat16 and float16; float32 stays on the GEMM lowering.
 //
 // Replaces (reference project paths): src/backends/cuda/conv2d_cuda.cu:311-2121 (tiled forward,
 // input-gradient and weight-gradient kernels and their selectors :1173-1202, :1778-1812).
