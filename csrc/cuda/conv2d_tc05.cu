@@ -36,6 +36,7 @@
 #include <cstring>
 #include <vector>
 
+#include "ob/conv_plan.h"
 #include "ob/cuda_common.cuh"
 #include "ob/ops.h"
 #include "ob/tc05.cuh"
@@ -52,8 +53,8 @@ namespace {
 using namespace tc05;
 
 constexpr int kConvThreads = 256;
-constexpr int kMaxStages = 4;
-constexpr int kConvSmemMax = 227 * 1024;
+constexpr int kMaxStages = kConvPlanMaxStages;
+constexpr int kConvSmemMax = kConvPlanSmemMax;
 enum : int { kErrConvWait = 21 };
 
 struct ConvParams {
@@ -96,21 +97,8 @@ __device__ __forceinline__ T gather_one(const T* __restrict__ src, const GatherG
   return ok ? src[q.off + base] : from_f<T>(0.f);
 }
 
-// Geometry of one dgrad stride class z = a * sw + b: input pixels (a + sh*i, b + sw*j), which only
-// see the filter rows r = ra0 + sh*ri and columns s = sb0 + sw*si.
-struct StrideClass {
-  int a, b, ra0, sb0, ra, sb, ha, wb, qa, qb;
-};
 __device__ __forceinline__ StrideClass stride_class(const ConvParams& p, int z) {
-  StrideClass c;
-  c.a = z / p.sw; c.b = z - c.a * p.sw;
-  c.ra0 = (c.a + p.ph) % p.sh; c.sb0 = (c.b + p.pw) % p.sw;
-  c.ra = c.ra0 < p.R ? (p.R - c.ra0 + p.sh - 1) / p.sh : 0;
-  c.sb = c.sb0 < p.S ? (p.S - c.sb0 + p.sw - 1) / p.sw : 0;
-  c.ha = c.a < p.H ? (p.H - c.a + p.sh - 1) / p.sh : 0;
-  c.wb = c.b < p.W ? (p.W - c.b + p.sw - 1) / p.sw : 0;
-  c.qa = (c.a + p.ph) / p.sh; c.qb = (c.b + p.pw) / p.sw;
-  return c;
+  return stride_class_of(z, p.H, p.W, p.R, p.S, p.sh, p.sw, p.ph, p.pw);
 }
 
 // ---- the fast gather: 8 consecutive pixels that share an image and an output row
@@ -522,13 +510,23 @@ __global__ void conv_pad_rows_kernel(const T* __restrict__ w, T* __restrict__ wp
   }
 }
 
-ConvParams base_params(const Shape& x, const Shape& w, const int64_t* i, int device) {
+ConvGeometry geometry_of(const Shape& x, const Shape& w, const int64_t* i) {
+  ConvGeometry g;
+  g.N = static_cast<int>(x[0]); g.C = static_cast<int>(x[1]); g.H = static_cast<int>(x[2]); g.W = static_cast<int>(x[3]);
+  g.K = static_cast<int>(w[0]); g.R = static_cast<int>(w[2]); g.S = static_cast<int>(w[3]);
+  g.sh = static_cast<int>(i[0]); g.sw = static_cast<int>(i[1]); g.ph = static_cast<int>(i[2]); g.pw = static_cast<int>(i[3]);
+  return g;
+}
+
+// Kernel arguments from the plan (pointers are filled in by the caller).
+ConvParams params_of(const ConvGeometry& g, const ConvPlan& plan, int device) {
   ConvParams p{};
-  p.N = static_cast<int>(x[0]); p.C = static_cast<int>(x[1]); p.H = static_cast<int>(x[2]); p.W = static_cast<int>(x[3]);
-  p.K = static_cast<int>(w[0]); p.R = static_cast<int>(w[2]); p.S = static_cast<int>(w[3]);
-  p.sh = static_cast<int>(i[0]); p.sw = static_cast<int>(i[1]); p.ph = static_cast<int>(i[2]); p.pw = static_cast<int>(i[3]);
-  p.OH = (p.H + 2 * p.ph - p.R) / p.sh + 1;
-  p.OW = (p.W + 2 * p.pw - p.S) / p.sw + 1;
+  p.mode = static_cast<int>(plan.pass);
+  p.N = g.N; p.C = g.C; p.H = g.H; p.W = g.W; p.K = g.K; p.R = g.R; p.S = g.S;
+  p.OH = plan.out_h; p.OW = plan.out_w; p.sh = g.sh; p.sw = g.sw; p.ph = g.ph; p.pw = g.pw;
+  p.rows_total = plan.rows_total; p.bn = plan.bn; p.tiles_m = plan.tiles_m; p.tiles_n = plan.tiles_n;
+  p.classes = plan.classes; p.splits = plan.splits; p.kb_per_split = plan.kb_per_split; p.ldp = plan.ldp;
+  p.gather_bytes = plan.gather_bytes; p.stage_bytes = plan.stage_bytes; p.stages = plan.stages; p.tmem_cols = plan.tmem_cols;
   p.err = tc05_error_flag(device);
   return p;
 }
@@ -540,61 +538,25 @@ bool route_allowed(const Tensor& t) {
   return Runtime::instance().cuda(t.device().index).supports_tcgen05();
 }
 
-bool fits_int32(const ConvParams& p) {
-  const long long lim = (1LL << 31) - 1;
-  return static_cast<long long>(p.N) * p.C * p.H * p.W < lim && static_cast<long long>(p.N) * p.K * p.OH * p.OW < lim;
-}
-
-int round16(int v) { return (v + 15) & ~15; }
-
 int g_last_launch[4] = {0, 0, 0, 0};   // grid, dynamic shared memory, ring slots, CTAs per SM of the latest launch (diagnostics)
 
-int round1k(int v) { return (v + 1023) & ~1023; }
-
-// Ring geometry of a launch: as many slots as fit (2 to 4), kept under half of the shared memory
-// when three slots allow it so that two CTAs share an SM and one's gathers hide the other's waits.
-void plan_ring(ConvParams& p) {
-  const int rows_bytes = round1k(p.bn * 128);
-  p.gather_bytes = p.mode == 2 ? rows_bytes : 16384;
-  p.stage_bytes = p.gather_bytes + (p.mode == 2 ? 16384 : rows_bytes);
-  const int half = 110 * 1024, whole = kConvSmemMax - 2048;
-  const int budget = 3 * p.stage_bytes <= half ? half : whole;
-  p.stages = std::max(2, std::min(kMaxStages, budget / p.stage_bytes));
-  int cols = 32;
-  while (cols < p.bn) cols *= 2;
-  p.tmem_cols = cols;
-}
-
-// A persistent grid: as many CTAs as can be resident (shared memory, registers and the 512 columns
-// of tensor memory decide), each walking the work items with a stride of the grid.
+// A persistent grid: as many CTAs as can be resident, each walking the work items with a stride of the grid.
 template <class T, int MODE, bool FAST>
-void launch_mode(const CUtensorMap& map, const ConvParams& p, long long items, int sms, cudaStream_t st) {
+void launch_mode(const CUtensorMap& map, const ConvParams& p, const ConvPlan& plan, cudaStream_t st) {
   // The largest shared-memory carve-out, or a CTA that needs under half of it gets an SM configured for one CTA only.
   static const bool once = (cudaFuncSetAttribute(conv_tc05_kernel<T, MODE, FAST>, cudaFuncAttributeMaxDynamicSharedMemorySize, kConvSmemMax),
                             prefer_max_shared_carveout(conv_tc05_kernel<T, MODE, FAST>), true);
   (void)once;
-  const int smem = p.stages * p.stage_bytes + 1024 + 256;
-  // Registers allow two CTAs per SM (the launch bounds say so); shared memory and the 512 columns of tensor memory decide.
-  const int resident = std::max(1, std::min({2, kConvSmemMax / (smem + 1024), 512 / p.tmem_cols}));
-  const unsigned grid = static_cast<unsigned>(std::max<long long>(1, std::min<long long>(items, static_cast<long long>(sms) * resident)));
-  g_last_launch[0] = static_cast<int>(grid); g_last_launch[1] = smem; g_last_launch[2] = p.stages; g_last_launch[3] = resident;
-  conv_tc05_kernel<T, MODE, FAST><<<grid, kConvThreads, smem, st>>>(map, p);
-}
-// The fast gather needs groups of 8 pixels that never straddle an output row (for the input
-// gradient: a row of any stride class) and at most 8 horizontal taps.
-bool fast_gather(const ConvParams& p) {
-  if (p.S > 8) return false;
-  if (p.mode == 1) return p.W % (8 * p.sw) == 0;
-  return p.OW % 8 == 0;
+  g_last_launch[0] = plan.grid; g_last_launch[1] = plan.smem_bytes; g_last_launch[2] = plan.stages; g_last_launch[3] = plan.ctas_per_sm;
+  conv_tc05_kernel<T, MODE, FAST><<<static_cast<unsigned>(plan.grid), kConvThreads, plan.smem_bytes, st>>>(map, p);
 }
 
 template <class T>
-void launch(const CUtensorMap& map, ConvParams& p, long long items, int sms, cudaStream_t st) {
-  plan_ring(p);
-  const bool fast = fast_gather(p);
-  if (p.mode == 0) fast ? launch_mode<T, 0, true>(map, p, items, sms, st) : launch_mode<T, 0, false>(map, p, items, sms, st);
-  else if (p.mode == 1) fast ? launch_mode<T, 1, true>(map, p, items, sms, st) : launch_mode<T, 1, false>(map, p, items, sms, st);
-  else fast ? launch_mode<T, 2, true>(map, p, items, sms, st) : launch_mode<T, 2, false>(map, p, items, sms, st);
+void launch(const CUtensorMap& map, const ConvParams& p, const ConvPlan& plan, cudaStream_t st) {
+  const bool fast = plan.fast;
+  if (p.mode == 0) fast ? launch_mode<T, 0, true>(map, p, plan, st) : launch_mode<T, 0, false>(map, p, plan, st);
+  else if (p.mode == 1) fast ? launch_mode<T, 1, true>(map, p, plan, st) : launch_mode<T, 1, false>(map, p, plan, st);
+  else fast ? launch_mode<T, 2, true>(map, p, plan, st) : launch_mode<T, 2, false>(map, p, plan, st);
 }
 
 // Tensor map over `mats` row-major [rows, ld] matrices of 16-bit elements laid one after another:
@@ -615,28 +577,22 @@ template <class T>
 bool conv_fprop_tc05(OpCall& c) {
   const Tensor &x = c.in[0], &w = c.in[1];
   if (!route_allowed(x)) return false;
-  ConvParams p = base_params(x.shape(), w.shape(), c.i, x.device().index);
-  if (!fits_int32(p) || p.K < 1) return false;
-  cudaStream_t st = stream_of(c);
+  const ConvGeometry g = geometry_of(x.shape(), w.shape(), c.i);
   const int sms = sm_count_for(x);
-  const int CRS = p.C * p.R * p.S, ld = (CRS + 7) & ~7;
+  const ConvPlan plan = plan_conv(ConvPass::Forward, g, sms);
+  if (!plan.eligible) return false;
+  cudaStream_t st = stream_of(c);
   // The TMA row pitch must be a multiple of 16 bytes: weights whose rows are not get a padded copy.
   Tensor wp = w;
-  if (ld != CRS) {
-    wp = Tensor::empty({p.K, ld}, w.dtype(), w.device());
-    conv_pad_rows_kernel<T><<<ew_grid(wp.numel(), 256, sms), 256, 0, st>>>(w.data_as<T>(), wp.data_as<T>(), p.K, CRS, ld);
+  if (plan.pad_weights) {
+    wp = Tensor::empty({g.K, plan.weight_ld}, w.dtype(), w.device());
+    conv_pad_rows_kernel<T><<<ew_grid(wp.numel(), 256, sms), 256, 0, st>>>(w.data_as<T>(), wp.data_as<T>(), g.K, plan.rows_total, plan.weight_ld);
   }
-  p.mode = 0;
-  p.rows_total = CRS;
-  p.bn = std::min(256, round16(p.K));
-  p.classes = 1;
+  ConvParams p = params_of(g, plan, x.device().index);
   p.src = x.data(); p.out = c.out[0].data(); p.bias = c.in[2].defined() ? c.in[2].data() : nullptr;
   CUtensorMap map;
-  if (!matrix_map(&map, w.dtype(), const_cast<void*>(wp.data()), ld, p.K, 1, ld, p.bn)) return false;
-  const long long m_total = static_cast<long long>(p.N) * p.OH * p.OW;
-  p.tiles_m = static_cast<int>((m_total + 127) / 128);
-  p.tiles_n = (p.K + p.bn - 1) / p.bn;
-  launch<T>(map, p, static_cast<long long>(p.tiles_m) * p.tiles_n, sms, st);
+  if (!matrix_map(&map, w.dtype(), const_cast<void*>(wp.data()), plan.weight_ld, g.K, 1, plan.weight_ld, plan.bn)) return false;
+  launch<T>(map, p, plan, st);
   check_launch("conv2d (implicit GEMM)");
   return true;
 }
@@ -646,27 +602,20 @@ bool conv_dgrad_tc05(OpCall& c) {
   const Tensor &gy = c.in[0], &w = c.in[1];
   Tensor& dx = c.out[0];
   if (!route_allowed(gy)) return false;
-  ConvParams p = base_params(dx.shape(), w.shape(), c.i, gy.device().index);
-  if (!fits_int32(p)) return false;
-  cudaStream_t st = stream_of(c);
+  const ConvGeometry g = geometry_of(dx.shape(), w.shape(), c.i);
   const int sms = sm_count_for(gy);
-  p.mode = 1;
-  p.classes = p.sh * p.sw;
-  const int taps_max = ((p.R + p.sh - 1) / p.sh) * ((p.S + p.sw - 1) / p.sw);
-  const int ld = (p.K * taps_max + 7) & ~7;
-  Tensor wt = Tensor::empty({p.classes, p.C, ld}, w.dtype(), w.device());
-  conv_permute_weight_kernel<T><<<ew_grid(wt.numel(), 256, sms), 256, 0, st>>>(w.data_as<T>(), wt.data_as<T>(), p, ld);
+  const ConvPlan plan = plan_conv(ConvPass::InputGradient, g, sms);
+  if (!plan.eligible) return false;
+  cudaStream_t st = stream_of(c);
+  ConvParams p = params_of(g, plan, gy.device().index);
+  Tensor wt = Tensor::empty({plan.classes, g.C, plan.weight_ld}, w.dtype(), w.device());
+  conv_permute_weight_kernel<T><<<ew_grid(wt.numel(), 256, sms), 256, 0, st>>>(w.data_as<T>(), wt.data_as<T>(), p, plan.weight_ld);
   // A stride larger than the filter leaves input pixels that no tap reaches: their gradient is zero.
-  if (p.sh > p.R || p.sw > p.S) OB_CUDA(cudaMemsetAsync(dx.data(), 0, dx.nbytes(), st));
-  p.rows_total = 0;
-  p.bn = std::min(256, round16(p.C));
+  if (plan.zero_fill) OB_CUDA(cudaMemsetAsync(dx.data(), 0, dx.nbytes(), st));
   p.src = gy.data(); p.out = dx.data(); p.bias = nullptr;
   CUtensorMap map;
-  if (!matrix_map(&map, w.dtype(), wt.data(), ld, p.C, p.classes, ld, p.bn)) return false;
-  const long long m_class = static_cast<long long>(p.N) * ((p.H + p.sh - 1) / p.sh) * ((p.W + p.sw - 1) / p.sw);   // class (0, 0) is the largest
-  p.tiles_m = static_cast<int>((m_class + 127) / 128);
-  p.tiles_n = (p.C + p.bn - 1) / p.bn;
-  launch<T>(map, p, static_cast<long long>(p.tiles_m) * p.tiles_n * p.classes, sms, st);
+  if (!matrix_map(&map, w.dtype(), wt.data(), plan.weight_ld, g.C, plan.classes, plan.weight_ld, plan.bn)) return false;
+  launch<T>(map, p, plan, st);
   check_launch("conv2d input gradient (implicit GEMM)");
   return true;
 }
@@ -678,42 +627,27 @@ bool conv_wgrad_tc05(OpCall& c) {
   const Tensor &gy = c.in[0], &x = c.in[1];
   Tensor& dw = c.out[0];
   if (!route_allowed(gy)) return false;
-  ConvParams p = base_params(x.shape(), dw.shape(), c.i, gy.device().index);
-  const int P = p.OH * p.OW;
-  if (!fits_int32(p) || p.K > 128 || P % 8 != 0) return false;   // one 128-row M tile; the TMA row pitch needs 16-byte multiples
-  cudaStream_t st = stream_of(c);
+  const ConvGeometry g = geometry_of(x.shape(), dw.shape(), c.i);
   const int sms = sm_count_for(gy);
-  const int CRS = p.C * p.R * p.S, rows = CRS + 1;
-  p.mode = 2;
-  p.classes = 1;
-  p.rows_total = rows;
-  p.tiles_m = 1;
-  p.tiles_n = (rows + 255) / 256;
-  p.bn = round16((rows + p.tiles_n - 1) / p.tiles_n);
-  const int kb_img = (P + 63) / 64;
-  const long long kb_total = static_cast<long long>(p.N) * kb_img;
-  // One wave of (column tile, reduction slice) items; a slice is at least 4 blocks of 64 pixels.
-  plan_ring(p);
-  const int per_sm = 3 * p.stage_bytes <= 110 * 1024 ? 2 : 1;
-  int splits = static_cast<int>(std::max<long long>(1, std::min<long long>((kb_total + 3) / 4, (sms * per_sm) / p.tiles_n)));
-  p.kb_per_split = static_cast<int>((kb_total + splits - 1) / splits);
-  splits = static_cast<int>((kb_total + p.kb_per_split - 1) / p.kb_per_split);
-  p.splits = splits;
-  p.ldp = p.tiles_n * p.bn;
-  Tensor partial = Tensor::empty({splits, 128, p.ldp}, DType::F32, gy.device());
+  const ConvPlan plan = plan_conv(ConvPass::WeightGradient, g, sms);
+  if (!plan.eligible) return false;
+  cudaStream_t st = stream_of(c);
+  ConvParams p = params_of(g, plan, gy.device().index);
+  const int P = plan.out_h * plan.out_w, CRS = plan.rows_total - 1;
+  Tensor partial = Tensor::empty({plan.splits, 128, plan.ldp}, DType::F32, gy.device());
   p.src = x.data(); p.out = partial.data(); p.bias = nullptr;
   // gy as [N][K][P]: inner = pixel, rows = channel, outer = image; rows past K and images past N read zeros.
   CUtensorMap map;
   {
-    const uint64_t dims[3] = {static_cast<uint64_t>(P), static_cast<uint64_t>(p.K), static_cast<uint64_t>(p.N)};
-    const uint64_t strides[2] = {static_cast<uint64_t>(P) * 2, static_cast<uint64_t>(P) * 2 * static_cast<uint64_t>(p.K)};
+    const uint64_t dims[3] = {static_cast<uint64_t>(P), static_cast<uint64_t>(g.K), static_cast<uint64_t>(g.N)};
+    const uint64_t strides[2] = {static_cast<uint64_t>(P) * 2, static_cast<uint64_t>(P) * 2 * static_cast<uint64_t>(g.K)};
     const uint32_t box[3] = {64, 128, 1};
     if (!tc05_encode_map(&map, gy.dtype(), 3, const_cast<void*>(gy.data()), dims, strides, box)) return false;
   }
-  launch<T>(map, p, static_cast<long long>(p.tiles_n) * splits, sms, st);
+  launch<T>(map, p, plan, st);
   T* db = c.out[1].defined() ? c.out[1].data_as<T>() : nullptr;
-  conv_wgrad_finish_kernel<T><<<static_cast<unsigned>((static_cast<int64_t>(p.K) * rows + 31) / 32), 256, 0, st>>>(
-      partial.data_as<float>(), dw.data_as<T>(), db, splits, p.K, CRS, p.ldp);
+  conv_wgrad_finish_kernel<T><<<static_cast<unsigned>((static_cast<int64_t>(g.K) * plan.rows_total + 31) / 32), 256, 0, st>>>(
+      partial.data_as<float>(), dw.data_as<T>(), db, plan.splits, g.K, CRS, plan.ldp);
   if (db != nullptr) c.i[4] = 1;
   check_launch("conv2d weight gradient (implicit GEMM)");
   return true;
