@@ -90,6 +90,17 @@ class PeerReducer:
         return all(p.device.is_cuda() and p.device == first.device and p.dtype == first.dtype and p.is_contiguous
                    and p.dtype in ("float32", "float16", "bfloat16") for _, p in parameters)
 
+    @classmethod
+    def choose_variant(cls, world, nbytes, has_multicast):
+        """Which kernel reduces a bucket of `nbytes` across `world` ranks: "in_switch" (multimem
+        through the NVSwitch), "one_shot" (every rank reads every copy) or "two_shot"
+        (reduce-scatter by peer loads, all-gather by peer stores)."""
+        if has_multicast and nbytes >= cls.NVLS_MIN_BYTES and 0 < cls.NVLS_MIN_WORLD <= world:
+            return "in_switch"
+        if nbytes <= cls.ONESHOT_BYTES_BY_WORLD.get(world, cls.ONESHOT_BYTES_LARGE_WORLD):
+            return "one_shot"
+        return "two_shot"
+
     def __init__(self, parameters, group, bucket_size_mb=None, overlap=False):
         self.parameters = tuple(parameters)
         self.group = group
@@ -171,8 +182,8 @@ class PeerReducer:
         if b.seg is not None and self.mode != "average":
             hyper["seg_end"], hyper["seg_wd"] = b.seg
         nbytes = b.n * _ELEMENT_BYTES[b.dtype]
-        in_switch = bool(b.mc) and nbytes >= self.NVLS_MIN_BYTES and 0 < self.NVLS_MIN_WORLD <= self.world
-        oneshot = not in_switch and nbytes <= self.ONESHOT_BYTES_BY_WORLD.get(self.world, self.ONESHOT_BYTES_LARGE_WORLD)
+        variant = self.choose_variant(self.world, nbytes, bool(b.mc))
+        in_switch, oneshot = variant == "in_switch", variant == "one_shot"
         status, found_inf = self.backend.status_tensors()
         _C._stream_fence(self.device, 0, 1)  # communication stream waits for the gradients
         fused = self.mode != "average"

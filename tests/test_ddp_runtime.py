@@ -147,3 +147,35 @@ def test_amp_rounds_with_rank_local_gradients(mode):
         assert rounds[2]["params"] == [9.0, 18.0, 30.0]
     else:
         assert [r["params"] for r in rounds] == [[9.5, 19.0, 30.0], [9.0, 18.0, 30.0], [8.5, 17.0, 30.0]]
+
+
+def test_reducer_variant_follows_the_measured_crossovers():
+    """Which kernel reduces a bucket is a pure function of the group size, the bucket size and whether the
+    buckets could be bound to a multicast object."""
+    from orthon_b200.parallel.peer_reducer import PeerReducer as R
+    KB, MB = 1 << 10, 1 << 20
+    # two ranks: peer loads at every size, one-shot up to 512 KB
+    assert R.choose_variant(2, 25 * MB, True) == "two_shot"
+    assert R.choose_variant(2, 512 * KB, True) == "one_shot"
+    assert R.choose_variant(2, 512 * KB + 2, False) == "two_shot"
+    # four and eight ranks: in-switch from 8 KB on when the box has multicast
+    for world in (4, 8):
+        assert R.choose_variant(world, 25 * MB, True) == "in_switch"
+        assert R.choose_variant(world, 8 * KB, True) == "in_switch"
+        assert R.choose_variant(world, 4 * KB, True) == "one_shot"
+        assert R.choose_variant(world, 25 * MB, False) == "two_shot"
+    # without multicast the one-shot limit shrinks with the group
+    assert R.choose_variant(4, 32 * KB, False) == "one_shot" and R.choose_variant(4, 64 * KB, False) == "two_shot"
+    assert R.choose_variant(8, 16 * KB, False) == "one_shot" and R.choose_variant(8, 32 * KB, False) == "two_shot"
+    assert R.choose_variant(6, 16 * KB, False) == "one_shot"
+    assert R.choose_variant(3, 32 * KB, False) == "one_shot"
+
+
+def test_reducer_variant_thresholds_can_be_moved(monkeypatch):
+    from orthon_b200.parallel.peer_reducer import PeerReducer as R
+    monkeypatch.setattr(R, "NVLS_MIN_WORLD", 0)
+    assert R.choose_variant(8, 1 << 26, True) == "two_shot"
+    monkeypatch.setattr(R, "NVLS_MIN_WORLD", 2)
+    assert R.choose_variant(2, 1 << 26, True) == "in_switch"
+    monkeypatch.setattr(R, "NVLS_MIN_BYTES", 1 << 27)
+    assert R.choose_variant(2, 1 << 26, True) == "two_shot"
