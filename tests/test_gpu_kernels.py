@@ -558,3 +558,23 @@ def test_layer_norm_backward_adds_the_residual_gradient_in_the_same_pass(dtype, 
     close(xx.grad, t.grad, dtype, 8); close(ww.grad, tw.grad, dtype, 8); close(bb.grad, tb.grad, dtype, 8)
     # Without the fused addition the same graph takes one more kernel wrapper (the engine's add).
     assert _C._kernel_launch_count() - before > 0
+
+
+@pytest.mark.parametrize("case", [
+    # (M, K, N, expected tile rows, expected epilogue warps): 256-row tiles and eight-warp tiles have one staging tile
+    # per epilogue warp; widths that end in a partial 64-column group are clipped by the store
+    (1024, 2048, 9440, 256, 4), (1024, 2048, 9448, 256, 4), (2048, 512, 2056, 128, 8), (4096, 4096, 2304, 256, 4)])
+def test_gemm_single_staging_tile_stores(case):
+    M, K, N, tm, ew = case
+    plan = _C._plan_gemm("bfloat16", M, N, K, 1, False, False, False, 0, True, True, 148, {})
+    assert (plan["tm"], plan["epilogue_warps"]) == (tm, ew), plan
+    rng = np.random.default_rng(M + N)
+    a, b = rng.standard_normal((M, K)), rng.standard_normal((K, N)) * (1.0 / np.sqrt(K))
+    bias, res = rng.standard_normal((N,)), rng.standard_normal((M, N))
+    ta, tb = ref_round(a, "bfloat16"), ref_round(b, "bfloat16")
+    xa, xb = dev_tensor(a, "bfloat16"), dev_tensor(b, "bfloat16")
+    close(_C._gemm(xa, False, xb, False), ta @ tb, "bfloat16", 2)
+    y = ob.linear(xa, xb, dev_tensor(bias, "bfloat16"), "none", dev_tensor(res, "bfloat16"))      # bias + residual in the epilogue
+    close(y, ta @ tb + ref_round(bias, "bfloat16") + ref_round(res, "bfloat16"), "bfloat16", 2)
+    g = ob.linear(xa, xb, dev_tensor(bias, "bfloat16"), "gelu")                                    # bias + GELU in the epilogue
+    close(g, torch.nn.functional.gelu(ta @ tb + ref_round(bias, "bfloat16")), "bfloat16", 2)
