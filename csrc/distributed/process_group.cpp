@@ -434,6 +434,26 @@ void bind_process_group(py::module_& m) {
       .def("shutdown", &NcclProcessGroup::shutdown);
 
   // Host-only test seams.
+  // Function-style access to the same group object (the spelling Orthon's private NCCL bindings use).
+  using GroupPtr = std::shared_ptr<NcclProcessGroup>;
+  m.def("_nccl_init", [](const py::bytes& id, int rank, int world, int device) {
+    return std::make_shared<NcclProcessGroup>(rank, world, device, std::string(id), std::make_shared<SystemTransport>());
+  }, py::arg("unique_id_bytes"), py::arg("rank"), py::arg("world_size"), py::arg("device_index"));
+  m.def("_nccl_all_reduce_sum_async", [](const GroupPtr& group, Tensor& t) { return group->all_reduce(t); });
+  m.def("_nccl_all_reduce_sum", [](const GroupPtr& group, Tensor& t) {
+    auto work = group->all_reduce(t);
+    py::gil_scoped_release nogil;
+    work->wait();
+  });
+  m.def("_nccl_broadcast_async", [](const GroupPtr& group, Tensor& t, int src) { return group->broadcast(t, src); });
+  m.def("_nccl_broadcast", [](const GroupPtr& group, Tensor& t, int src) {
+    auto work = group->broadcast(t, src);
+    py::gil_scoped_release nogil;
+    work->wait();
+  });
+  m.def("_nccl_barrier", [](const GroupPtr& group) { group->barrier(); }, py::call_guard<py::gil_scoped_release>());
+  m.def("_nccl_shutdown", [](const GroupPtr& group) { group->shutdown(); });
+
   m.def("_testing_use_fake_cuda", [](int devices) {
     Runtime::instance().inject_resources(devices > 0 ? std::shared_ptr<CudaResources>(std::make_shared<FakeCudaResources>(devices))
                                                      : system_cuda_resources());

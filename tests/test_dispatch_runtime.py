@@ -121,3 +121,31 @@ def test_env_defaults_and_backend_registry(monkeypatch):
         get_backend_factory("nope")
     register_backend("mine", lambda **kw: None)
     assert get_backend_factory("mine") is not None
+
+
+def test_function_style_nccl_entry_points_drive_the_same_group(fake_cuda):
+    """`_nccl_all_reduce_sum(group, t)` and friends are the spelling Orthon's private bindings use; they act on the
+    same group object as the methods."""
+    g = _C._NcclGroup(0, 2, 0, bytes(128), True)
+    t = _C._empty_on([8], "float32", "cuda:0")
+    _C._testing_fake_clear()
+    w = _C._nccl_all_reduce_sum_async(g, t)
+    assert isinstance(w, _C._NcclWork) and w.wait() is True
+    _C._nccl_all_reduce_sum(g, t)
+    _C._nccl_broadcast(g, t, 1)
+    assert _C._nccl_broadcast_async(g, t, 0).wait() is True
+    kinds = [e.split(":")[0] for e in _C._testing_fake_log()]
+    assert kinds.count("all_reduce") == 2 and kinds.count("broadcast") == 2
+    assert callable(_C._nccl_barrier)     # a one-float all-reduce on the device: exercised on real GPUs only
+    with pytest.raises(Exception):
+        _C._nccl_broadcast(g, t, 2)
+    _C._nccl_shutdown(g)
+    with pytest.raises(RuntimeError, match="shut down"):
+        _C._nccl_all_reduce_sum(g, t)
+
+
+def test_nccl_init_without_the_library_or_a_device_fails_with_a_reason():
+    if _C.cuda_enabled() and _C.cuda_available():
+        pytest.skip("a real device is present")
+    with pytest.raises(Exception):
+        _C._nccl_init(bytes(128), 0, 1, 0)
