@@ -1,29 +1,50 @@
-"""Inverted dropout with a stateless splitmix64 mask: element i of call c uses
-splitmix64(seed + c * 0x9E3779B97F4A7C15 + i), identical on CPU and CUDA.
-(reference project: python/orthon/nn/dropout.py:9-31)"""
+"""Inverted dropout whose mask is a pure function of (seed, call number, element index).
+
+The mask of element i in the c-th training call of a module is drawn from
+splitmix64(seed + c * 0x9E3779B97F4A7C15 + i): nothing is stored between forward and backward
+(the CUDA kernel recomputes the mask from the per-call seed), and the CPU and CUDA kernels agree
+bit for bit.  (reference project: python/orthon/nn/dropout.py:9-31)"""
 from .. import _C
 from .._random import randbits
 from .module import Module
 
-_GOLDEN = 0x9E3779B97F4A7C15
-_MASK64 = (1 << 64) - 1
+
+class _CallSeeds:
+    """The per-call seed stream of one module: seed + n * golden ratio, modulo 2^64."""
+
+    STEP = 0x9E3779B97F4A7C15
+    WRAP = 1 << 64
+
+    def __init__(self, base):
+        self.base = int(base) % self.WRAP
+        self.calls = 0
+
+    def take(self):
+        value = (self.base + self.calls * self.STEP) % self.WRAP
+        self.calls += 1
+        return value
 
 
 class Dropout(Module):
     def __init__(self, p: float = 0.5, seed=None):
         super().__init__()
-        if p < 0.0 or p >= 1.0:
+        if not 0.0 <= p < 1.0:
             raise ValueError("Dropout p must be in [0, 1)")
         self.p = float(p)
-        self.seed = int(seed) if seed is not None else randbits(64)
-        self._counter = 0
+        self._seeds = _CallSeeds(randbits(64) if seed is None else seed)
+
+    # The reference exposes the base seed and the call counter as attributes; keep both readable.
+    @property
+    def seed(self):
+        return self._seeds.base
+
+    @property
+    def _counter(self):
+        return self._seeds.calls
 
     def _next_seed(self):
-        seed = (self.seed + self._counter * _GOLDEN) & _MASK64
-        self._counter += 1
-        return seed
+        return self._seeds.take()
 
     def forward(self, x):
-        if not self.training or self.p == 0.0:
-            return x
-        return _C.dropout(x, self.p, self._next_seed())
+        active = self.training and self.p > 0.0
+        return _C.dropout(x, self.p, self._seeds.take()) if active else x
