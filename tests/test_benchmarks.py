@@ -135,3 +135,32 @@ def test_ddp_benchmark_under_the_launcher_with_local_backend():
     out = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=240)
     assert out.returncode == 0, out.stderr[-2000:]
     assert "ddp/bucketed" in out.stdout and "ranks=2" in out.stdout
+
+
+GPU_SCRIPTS = ["bench_matmul.py", "bench_gemm_shapes.py", "bench_attention.py", "bench_conv.py", "bench_reducer.py",
+               "bench_configs.py", "trace_step.py", "profile_kernels.py"]
+
+
+@pytest.mark.parametrize("script", GPU_SCRIPTS)
+def test_gpu_benchmark_scripts_parse_their_arguments_without_a_device(script):
+    """Every benchmark script imports and documents its options on a machine without a GPU (`--help` exits 0);
+    each one also explains itself in a module docstring that gives at least one command line."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    path = os.path.join(root, "benchmarks", script)
+    out = subprocess.run([sys.executable, path, "--help"], capture_output=True, text=True, cwd=root, timeout=300)
+    assert out.returncode == 0, out.stderr[-400:]
+    assert "usage" in out.stdout.lower()
+    source = open(path).read()
+    assert source.lstrip().startswith('"""') and "python " in source.split('"""')[1]
+
+
+def test_bench_py_help_names_both_arms_and_the_bucket_option():
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--help"], capture_output=True, text=True, cwd=root, timeout=300)
+    assert out.returncode == 0, out.stderr[-400:]
+    for word in ("--gpus", "--steps", "--warmup", "--impl", "--bucket-mb", "--no-anchor", "reference"):
+        assert word in out.stdout
